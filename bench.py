@@ -1,0 +1,636 @@
+#!/usr/bin/env python
+"""Benchmark of the channels-last GroupNorm hot path on B200.
+
+    python bench.py [--gpus N --steps K --warmup W]          # one JSON line (rank 0)
+    python bench.py --impl reference ...                      # the CPU reference arm
+    python bench.py --sweep [--out FILE]                      # every benchmark shape, one JSON line each
+
+Workload of the headline line ("cfg4"): GroupNorm + GELU(erf), bf16, NHWC, global batch 64 of
+256 x 64 x 64, 32 groups, eps 1e-5, forward + backward; the batch is split evenly over the ranks
+(strong scaling) and the packed fp32 [dgamma | dbeta] buffer is all-reduced with NCCL.  A step is
+one forward + one backward over the rank's samples.  Inputs are seeded synthetic tensors
+(x ~ N(0,1), gamma ~ U(0.5,1.5), beta ~ N(0,0.01), dy ~ N(0,1)).
+
+value      aggregate algorithmic bytes (5 * E * sizeof: read x, write y | read x, dy, write dx)
+           of all ranks / max-over-ranks device time per step, inputs resident in HBM, through the
+           C ABI (gnb200_fwd / gnb200_bwd).  Buffers rotate over enough copies that no step finds
+           its inputs in L2.
+e2e        same metric through the public module (GN_NHWC + autograd) with the step's x and dy
+           copied from pinned host memory and y, dx, dgamma, dbeta copied back, all inside the
+           timed region.
+roofline   the backward call (the dominant kernel plus its 2-microsecond parameter-gradient
+           kernel) and, as `roofline_fwd`, the forward kernel: algorithmic bytes / CUDA-event
+           duration against the measured copy bandwidth in MEASURED_PEAKS.json.
+cpu_baseline  torch.nn.functional.group_norm + activation on the host cores (channels_last, same
+           dtype, autograd backward) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+DT = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+DT_SHORT = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_HBM_GBS = 6650.0
+
+WORKLOADS = {
+    # name: N, C, H, W, G, eps, act, dtype, x scale, backward?, x distribution
+    "cfg1": (2, 128, 32, 32, 32, 1e-5, "identity", "float32", 1.0, True, "normal"),
+    "cfg2_320x64": (1, 320, 64, 64, 32, 1e-5, "silu", "float16", 1.0, False, "normal"),
+    "cfg2_640x32": (1, 640, 32, 32, 32, 1e-5, "silu", "float16", 1.0, False, "normal"),
+    "cfg2_1280x16": (1, 1280, 16, 16, 32, 1e-5, "silu", "float16", 1.0, False, "normal"),
+    "cfg2_1280x8": (1, 1280, 8, 8, 32, 1e-5, "silu", "float16", 1.0, False, "normal"),
+    "cfg3_512x128": (1, 512, 128, 128, 32, 1e-6, "silu", "float16", 2.0, True, "normal"),
+    "cfg3_512x256": (1, 512, 256, 256, 32, 1e-6, "silu", "float16", 2.0, True, "normal"),
+    "cfg3_256x512": (1, 256, 512, 512, 32, 1e-6, "silu", "float16", 2.0, True, "normal"),
+    "cfg3_128x1024": (1, 128, 1024, 1024, 32, 1e-6, "silu", "float16", 2.0, True, "normal"),
+    "cfg4": (64, 256, 64, 64, 32, 1e-5, "gelu", "bfloat16", 1.0, True, "normal"),
+    "cfg4_n32": (32, 256, 64, 64, 32, 1e-5, "gelu", "bfloat16", 1.0, True, "normal"),
+    "cfg4_n16": (16, 256, 64, 64, 32, 1e-5, "gelu", "bfloat16", 1.0, True, "normal"),
+    "cfg4_n8": (8, 256, 64, 64, 32, 1e-5, "gelu", "bfloat16", 1.0, True, "normal"),
+    "cfg5_96x7_f32": (8, 96, 7, 7, 3, 1e-5, "gelu_tanh", "float32", 1.0, True, "uniform3"),
+    "cfg5_64x56_f32": (4, 64, 56, 56, 64, 1e-5, "gelu_tanh", "float32", 1.0, True, "uniform3"),
+    "cfg5_2048x7_f32": (16, 2048, 7, 7, 32, 1e-5, "relu", "float32", 1.0, True, "uniform3"),
+    "cfg5_40x17x33_f32": (3, 40, 17, 33, 8, 1e-5, "gelu_tanh", "float32", 1.0, True, "uniform3"),
+    "cfg5_2048x7_bf16": (16, 2048, 7, 7, 32, 1e-5, "gelu_tanh", "bfloat16", 1.0, True, "uniform3"),
+    "cfg5_64x56_bf16": (4, 64, 56, 56, 64, 1e-5, "relu", "bfloat16", 1.0, True, "uniform3"),
+}
+HEADLINE = "cfg4"
+ACT_CODES = {"identity": 0, "relu": 1, "silu": 2, "gelu": 3, "gelu_tanh": 4}
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# seeded synthetic inputs (same generator order as the tests: x, gamma, beta, dy)
+# ------------------------------------------------------------------------------------------------
+def make_inputs(N, C, H, W, dtype, seed=0, x_scale=1.0, dist="normal"):
+    g = torch.Generator().manual_seed(seed)
+    if dist == "uniform3":
+        x = torch.rand((N, H, W, C), generator=g) * 6.0 - 3.0
+    else:
+        x = torch.randn((N, H, W, C), generator=g) * x_scale
+    gamma = torch.rand(C, generator=g) + 0.5
+    beta = torch.randn(C, generator=g) * 0.1
+    dy = torch.randn((N, H, W, C), generator=g)
+    return x.to(dtype), gamma.to(dtype), beta.to(dtype), dy.to(dtype)  # NHWC-contiguous
+
+
+def torch_act(name):
+    import torch.nn.functional as F
+
+    return {"identity": lambda t: t, "relu": F.relu, "silu": F.silu, "gelu": F.gelu,
+            "gelu_tanh": lambda t: F.gelu(t, approximate="tanh")}[name]
+
+
+# ------------------------------------------------------------------------------------------------
+# clock sampling during the timed region
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0=None, t1=None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ts, line in self.lines:
+            if t0 is not None and not (t0 - 0.05 <= ts <= t1 + 0.15):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                 parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:  # region shorter than one sample: fall back to everything that was seen
+            return self.stop_all()
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+    def stop_all(self):
+        sm, mx = [], []
+        for _, line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except (ValueError, IndexError):
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": [], "samples": len(sm), "note": "timed region shorter than the sampling period"}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: torch group_norm + activation on the host cores (bounded sample)
+# ------------------------------------------------------------------------------------------------
+def cpu_step_fn(wl, n_sample):
+    import torch.nn.functional as F
+
+    N, C, H, W, G, eps, act, dt, xs, bwd, dist = WORKLOADS[wl]
+    dtype = DT[dt]
+    x, ga, be, dy = make_inputs(n_sample, C, H, W, dtype, 0, xs, dist)
+    x = x.permute(0, 3, 1, 2).requires_grad_(bwd)  # channels_last strides
+    dy = dy.permute(0, 3, 1, 2)
+    ga.requires_grad_(bwd)
+    be.requires_grad_(bwd)
+    fn = torch_act(act)
+
+    def step():
+        y = fn(F.group_norm(x, G, ga, be, eps))
+        if bwd:
+            torch.autograd.grad(y, (x, ga, be), dy)
+        return y
+
+    elems = n_sample * C * H * W
+    alg_bytes = (5 if bwd else 2) * elems * x.element_size()
+    return step, alg_bytes
+
+
+def time_cpu(wl, n_sample, budget_s=12.0, min_iters=3, warmup=2):
+    torch.set_num_threads(os.cpu_count() or 1)
+    step, alg_bytes = cpu_step_fn(wl, n_sample)
+    for _ in range(warmup):
+        step()
+    times = []
+    t_end = time.time() + budget_s
+    while len(times) < min_iters or (time.time() < t_end and len(times) < 200):
+        t = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t)
+    med = statistics.median(times)
+    return alg_bytes / med / 1e9, med, len(times)
+
+
+def reference_arm(args):
+    """CPU reference arm: every step is a bounded sample of the headline workload on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = args.workload
+    N, C, H, W, G, eps, act, dt, xs, bwd, dist = WORKLOADS[wl]
+    n_sample = min(N, 8)
+    torch.set_num_threads(os.cpu_count() or 1)
+    step, alg_bytes = cpu_step_fn(wl, n_sample)
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt_s = (time.perf_counter() - t0) / args.steps
+    value = alg_bytes / dt_s / 1e9
+    sample = "%d of %d samples per step, torch.nn.functional.group_norm + %s, channels_last %s, autograd backward" % (
+        n_sample, N, act, dt)
+    line = {
+        "impl": "reference", "metric": "gn_nhwc_fwd_bwd_achieved_GBps", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt_s * 1e3,
+        "us_per_call_scaled_to_full_batch": dt_s * 1e6 * N / n_sample,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DT_SHORT[dt],
+        "data": "synthetic", "config": workload_config(wl, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(wl, gpus):
+    N, C, H, W, G, eps, act, dt, xs, bwd, dist = WORKLOADS[wl]
+    return {"workload": "%s: GroupNorm+%s %s NHWC N=%d C=%d %dx%d G=%d eps=%g %s" % (
+        wl, act, dt, N, C, H, W, G, eps, "fwd+bwd" if bwd else "fwd"),
+        "global_batch": N, "per_gpu_batch": N // gpus, "parallelism": "batch-sharded x%d" % gpus,
+        "l2_policy": "buffers rotate over copies totalling > 1 GiB, so inputs are never L2-resident"}
+
+
+# ------------------------------------------------------------------------------------------------
+# device arm
+# ------------------------------------------------------------------------------------------------
+class DeviceProblem:
+    """Preallocated buffers for one workload on the current device, rotated to defeat L2 reuse."""
+
+    def __init__(self, wl, n_local, x, ga, be, dy, min_total_bytes=1 << 30):
+        from channels_last_groupnorm_b200 import _native as nt
+
+        self.nt = nt
+        N, C, H, W, G, eps, act, dt, xs, bwd, dist = WORKLOADS[wl]
+        self.n, self.C, self.R, self.G, self.eps, self.act, self.bwd = n_local, C, H * W, G, eps, ACT_CODES[act], bwd
+        self.dtype = DT[dt]
+        self.code = nt.DTYPE_CODES[self.dtype]
+        dev = torch.device("cuda", torch.cuda.current_device())
+        per_set = x.numel() * x.element_size() * (4 if bwd else 2)
+        self.nsets = max(2, min(64, -(-min_total_bytes // per_set)))
+        self.sets = []
+        for _ in range(self.nsets):
+            s = {"x": x.to(dev).contiguous(), "y": torch.empty(x.shape, dtype=self.dtype, device=dev)}
+            if bwd:
+                s["dy"] = dy.to(dev).contiguous()
+                s["dx"] = torch.empty(x.shape, dtype=self.dtype, device=dev)
+            self.sets.append(s)
+        self.ga, self.be = ga.to(dev), be.to(dev)
+        self.mean = torch.empty((n_local, G), dtype=torch.float32, device=dev)
+        self.rstd = torch.empty((n_local, G), dtype=torch.float32, device=dev)
+        self.dparam = torch.empty((2, C), dtype=torch.float32, device=dev)
+        self.dgamma = torch.empty(C, dtype=self.dtype, device=dev)
+        self.dbeta = torch.empty(C, dtype=self.dtype, device=dev)
+        wf = nt.lib.gnb200_fwd_workspace_bytes(n_local, self.R, C, G, self.code)
+        wb = nt.lib.gnb200_bwd_workspace_bytes(n_local, self.R, C, G, self.code)
+        self.ws_f = torch.empty(max(wf, 16), dtype=torch.uint8, device=dev)
+        self.ws_b = torch.empty(max(wb, 16), dtype=torch.uint8, device=dev)
+        self.wf, self.wb = wf, wb
+        self.elems = x.numel()
+        self.esize = x.element_size()
+        self.launches_fwd = nt.launch_count(n_local, self.R, C, G, self.dtype, 0)
+        self.launches_bwd = nt.launch_count(n_local, self.R, C, G, self.dtype, 1) if bwd else 0
+
+    def fwd(self, i, stream):
+        s = self.sets[i % self.nsets]
+        lib = self.nt.lib
+        self.nt.check(lib.gnb200_fwd(s["x"].data_ptr(), self.ga.data_ptr(), self.be.data_ptr(), self.n, self.R, self.C,
+                                     self.G, self.eps, self.act, self.code, s["y"].data_ptr(), self.mean.data_ptr(),
+                                     self.rstd.data_ptr(), self.ws_f.data_ptr() if self.wf else None, self.wf, stream))
+
+    def bwd_(self, i, stream, typed):
+        s = self.sets[i % self.nsets]
+        lib = self.nt.lib
+        self.nt.check(lib.gnb200_bwd(s["dy"].data_ptr(), s["x"].data_ptr(), self.ga.data_ptr(), self.be.data_ptr(),
+                                     self.mean.data_ptr(), self.rstd.data_ptr(), self.n, self.R, self.C, self.G,
+                                     self.act, self.code, s["dx"].data_ptr(), self.dparam.data_ptr(),
+                                     self.dgamma.data_ptr() if typed else None,
+                                     self.dbeta.data_ptr() if typed else None,
+                                     self.ws_b.data_ptr() if self.wb else None, self.wb, stream))
+
+
+def run_device_steps(prob, steps, warmup, world, barrier):
+    """Returns (seconds per step max over ranks, mean fwd seconds, mean bwd seconds)."""
+    import torch.distributed as dist
+
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def one(i, ev=None):
+        if ev:
+            ev[0].record()
+        prob.fwd(i, stream)
+        if ev:
+            ev[1].record()
+        if prob.bwd:
+            prob.bwd_(i, stream, typed=(world == 1))
+            if ev:
+                ev[2].record()
+            if world > 1:
+                dist.all_reduce(prob.dparam)
+                prob.dgamma.copy_(prob.dparam[0])
+                prob.dbeta.copy_(prob.dparam[1])
+
+    for i in range(warmup):
+        one(i)
+    barrier()
+    torch.cuda.synchronize()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    start.record()
+    for i in range(steps):
+        one(warmup + i, evs[i])
+    stop.record()
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    barrier()
+    total = start.elapsed_time(stop) * 1e-3
+    fwd_t = sum(e[0].elapsed_time(e[1]) for e in evs) * 1e-3 / steps
+    bwd_t = sum(e[1].elapsed_time(e[2]) for e in evs) * 1e-3 / steps if prob.bwd else 0.0
+    per_step = total / steps
+    if world > 1:
+        t = torch.tensor([per_step], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        per_step = float(t.item())
+    return per_step, fwd_t, bwd_t, (t_wall0, t_wall1)
+
+
+def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
+    """Public API (module + autograd) with host buffers; copies inside the timed region."""
+    import torch.distributed as dist
+
+    import channels_last_groupnorm_b200 as pkg
+
+    N, C, H, W, G, eps, act, dt, xs, bwd, dist_name = WORKLOADS[wl]
+    dtype = DT[dt]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    m = pkg.GN_NHWC(G, C, activation=act, eps=eps,
+                    process_group=(dist.group.WORLD if world > 1 else None)).to(dev).to(dtype)
+    with torch.no_grad():
+        m.weight.copy_(ga)
+        m.bias.copy_(be)
+    xh, dyh = x.pin_memory(), dy.pin_memory()
+    yh = torch.empty_like(xh).pin_memory()
+    dxh = torch.empty_like(xh).pin_memory()
+    dgh = torch.empty(C, dtype=dtype).pin_memory()
+    dbh = torch.empty(C, dtype=dtype).pin_memory()
+    xd = torch.empty(x.shape, dtype=dtype, device=dev)
+    dyd = torch.empty(x.shape, dtype=dtype, device=dev)
+
+    def one():
+        xd.copy_(xh, non_blocking=True)
+        xin = xd.permute(0, 3, 1, 2).detach().requires_grad_(bwd)
+        y = m(xin)
+        yh.copy_(y.detach().permute(0, 2, 3, 1), non_blocking=True)
+        if bwd:
+            dyd.copy_(dyh, non_blocking=True)
+            m.weight.grad = None
+            m.bias.grad = None
+            y.backward(dyd.permute(0, 3, 1, 2))
+            dxh.copy_(xin.grad.permute(0, 2, 3, 1), non_blocking=True)
+            dgh.copy_(m.weight.grad, non_blocking=True)
+            dbh.copy_(m.bias.grad, non_blocking=True)
+
+    for _ in range(warmup):
+        one()
+    barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one()
+    stop.record()
+    torch.cuda.synchronize()
+    barrier()
+    per_step = start.elapsed_time(stop) * 1e-3 / steps
+    if world > 1:
+        t = torch.tensor([per_step], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        per_step = float(t.item())
+    nbytes = x.numel() * x.element_size()
+    h2d = nbytes * (2 if bwd else 1)
+    d2h = nbytes * (2 if bwd else 1) + (2 * C * x.element_size() if bwd else 0)
+    return per_step, h2d, d2h
+
+
+def device_arm(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    from channels_last_groupnorm_b200 import _native as nt
+    from channels_last_groupnorm_b200.dist import shard_bounds
+
+    wl = args.workload
+    N, C, H, W, G, eps, act, dt, xs, bwd, dist_name = WORKLOADS[wl]
+    dtype = DT[dt]
+    x, ga, be, dy = make_inputs(N, C, H, W, dtype, 0, xs, dist_name)  # the global seeded batch
+    lo, hi = shard_bounds(N, rank, world)
+    x, dy = x[lo:hi].contiguous(), dy[lo:hi].contiguous()
+    n_local = hi - lo
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    prob = DeviceProblem(wl, n_local, x, ga, be, dy)
+    per_step, fwd_t, bwd_t, wall = run_device_steps(prob, args.steps, args.warmup, world, barrier)
+    clocks = sampler.stop(*wall) if rank == 0 else None
+    del prob
+    torch.cuda.empty_cache()
+    e2e_steps = max(3, min(args.steps, 20))
+    e2e_t, h2d, d2h = run_e2e(wl, n_local, x, ga, be, dy, e2e_steps, max(3, min(args.warmup, 5)), world, barrier)
+
+    if rank == 0:
+        esize = x.element_size()
+        elems_global = N * C * H * W
+        elems_local = n_local * C * H * W
+        alg_global = (5 if bwd else 2) * elems_global * esize
+        peak, peak_kind = measured_hbm_peak()
+        bwd_bytes = 3 * elems_local * esize
+        fwd_bytes = 2 * elems_local * esize
+        dom_bytes, dom_t, dom_name = (bwd_bytes, bwd_t, "backward") if bwd else (fwd_bytes, fwd_t, "forward")
+        roof = {"bound": "hbm", "kernel": "%s (%s)" % (dom_name, nt.describe_plan(n_local, H * W, C, G, dtype, 1 if bwd else 0)),
+                "achieved": dom_bytes / dom_t / 1e9, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": dom_bytes / dom_t / 1e9 / peak, "traffic": NCU_TRAFFIC.get((wl, world, dom_name)),
+                "us_per_launch": dom_t * 1e6, "algorithmic_bytes": dom_bytes}
+        roof_fwd = {"bound": "hbm", "kernel": "forward (%s)" % nt.describe_plan(n_local, H * W, C, G, dtype, 0),
+                    "achieved": fwd_bytes / fwd_t / 1e9, "peak": peak, "unit": "GB/s",
+                    "frac": fwd_bytes / fwd_t / 1e9 / peak, "traffic": NCU_TRAFFIC.get((wl, world, "forward")),
+                    "us_per_launch": fwd_t * 1e6, "algorithmic_bytes": fwd_bytes}
+        line = {
+            "metric": "gn_nhwc_fwd_bwd_achieved_GBps", "value": alg_global / per_step / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
+            "us_per_call": per_step * 1e6, "us_fwd": fwd_t * 1e6, "us_bwd": bwd_t * 1e6,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DT_SHORT[dt],
+            "data": "synthetic", "config": workload_config(wl, world),
+            "frac_of_hbm_peak": alg_global / per_step / 1e9 / (peak * world),
+            "roofline": roof, "roofline_fwd": roof_fwd,
+            "e2e": {"value": alg_global / e2e_t / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_t * 1e3, "steps": e2e_steps,
+                    "api": "GN_NHWC module + autograd, pinned host buffers"},
+            "gpu_launches": args.steps * (nt.launch_count(n_local, H * W, C, G, dtype, 0)
+                                          + (nt.launch_count(n_local, H * W, C, G, dtype, 1) if bwd else 0)),
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            n_sample = min(N, 8)
+            v, med, iters = time_cpu(wl, n_sample, budget_s=args.cpu_seconds)
+            line["cpu_baseline"] = {
+                "value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                "ms_per_sample_step": med * 1e3, "iters": iters,
+                "sample": "%d of %d samples, torch.nn.functional.group_norm + %s on CPU, channels_last %s, "
+                          "autograd backward, median of %d runs" % (n_sample, N, act, dt, iters)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; keyed by (workload, ranks, direction)
+NCU_TRAFFIC = {}
+
+
+# ------------------------------------------------------------------------------------------------
+# sweep over every benchmark shape (1 GPU): ours vs torch CUDA vs reference kernels vs CPU
+# ------------------------------------------------------------------------------------------------
+def time_cuda(fn, iters=20, reps=5, warmup=5):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    out = []
+    k = warmup
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn(k)
+            k += 1
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b) * 1e-3 / iters)
+    return statistics.median(out), min(out)
+
+
+def sweep(args):
+    from channels_last_groupnorm_b200 import _native as nt
+    import torch.nn.functional as F
+
+    torch.cuda.set_device(0)
+    peak, peak_kind = measured_hbm_peak()
+    ref_lib = os.path.join(ROOT, "oracle", "_ref", "gn_op.so")
+    have_ref = os.path.exists(ref_lib) and not args.no_ref
+    if have_ref:
+        torch.ops.load_library(ref_lib)
+    names = args.only.split(",") if args.only else list(WORKLOADS)
+    out_f = open(args.out, "a") if args.out else None
+    stream = torch.cuda.current_stream().cuda_stream
+    for wl in names:
+        N, C, H, W, G, eps, act, dt, xs, bwd, dist_name = WORKLOADS[wl]
+        dtype = DT[dt]
+        x, ga, be, dy = make_inputs(N, C, H, W, dtype, 0, xs, dist_name)
+        prob = DeviceProblem(wl, N, x, ga, be, dy)
+        esize = x.element_size()
+        E = x.numel()
+        rec = {"workload": wl, "config": workload_config(wl, 1)["workload"], "plan_fwd": nt.describe_plan(N, H * W, C, G, dtype, 0),
+               "plan_bwd": nt.describe_plan(N, H * W, C, G, dtype, 1) if bwd else None, "nsets": prob.nsets,
+               "peak_GBps": peak, "peak_kind": peak_kind}
+        t, tmin = time_cuda(lambda i: prob.fwd(i, stream))
+        rec["ours_fwd_us"] = t * 1e6
+        rec["ours_fwd_GBps"] = 2 * E * esize / t / 1e9
+        rec["ours_fwd_frac"] = rec["ours_fwd_GBps"] / peak
+        if bwd:
+            t, tmin = time_cuda(lambda i: prob.bwd_(i, stream, True))
+            rec["ours_bwd_us"] = t * 1e6
+            rec["ours_bwd_GBps"] = 3 * E * esize / t / 1e9
+            rec["ours_bwd_frac"] = rec["ours_bwd_GBps"] / peak
+        # torch CUDA group_norm + activation (context)
+        fn = torch_act(act)
+        sets = prob.sets
+        gat, bet = prob.ga, prob.be
+
+        def torch_fwd(i):
+            s = sets[i % len(sets)]
+            return fn(F.group_norm(s["x"].permute(0, 3, 1, 2), G, gat, bet, eps))
+
+        try:
+            t, _ = time_cuda(torch_fwd, iters=10, reps=3, warmup=3)
+            rec["torch_cuda_fwd_us"] = t * 1e6
+        except Exception as exc:  # pragma: no cover
+            rec["torch_cuda_fwd_us"] = None
+            rec["torch_cuda_error"] = str(exc)[:200]
+        if have_ref:
+            code = ACT_CODES[act]
+
+            def ref_fwd(i):
+                s = sets[i % len(sets)]
+                xf = s["x"].view(N, H * W, C).permute(0, 2, 1)
+                return torch.ops.gnop.fwd(xf, gat, bet, G, eps, code)
+
+            t, _ = time_cuda(ref_fwd, iters=10, reps=3, warmup=3)
+            rec["ref_fwd_us"] = t * 1e6
+            if bwd:
+                _, means, rstds = ref_fwd(0)
+
+                def ref_bwd(i):
+                    s = sets[i % len(sets)]
+                    xf = s["x"].view(N, H * W, C).permute(0, 2, 1)
+                    df = s["dy"].view(N, H * W, C).permute(0, 2, 1)
+                    return torch.ops.gnop.bwd(df, xf, gat, bet, means, rstds, G, code)
+
+                t, _ = time_cuda(ref_bwd, iters=10, reps=3, warmup=3)
+                rec["ref_bwd_us"] = t * 1e6
+        del prob, sets
+        torch.cuda.empty_cache()
+        if not args.no_cpu:
+            n_sample = min(N, 8)
+            v, med, iters = time_cpu(wl, n_sample, budget_s=2.0, min_iters=2, warmup=1)
+            rec["cpu_us_scaled"] = med * 1e6 * N / n_sample
+            rec["cpu_cores"] = torch.get_num_threads()
+        print(json.dumps(rec), flush=True)
+        if out_f:
+            out_f.write(json.dumps(rec) + "\n")
+            out_f.flush()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=HEADLINE, choices=list(WORKLOADS))
+    ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--only", default="")
+    ap.add_argument("--out", default="")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-ref", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.sweep:
+        return sweep(args)
+    if args.impl == "reference":
+        return reference_arm(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        # launched without torchrun: re-launch one process per GPU on this node
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
+               "--master-addr", "127.0.0.1", "--master-port", "29531"] + sys.argv
+        raise SystemExit(subprocess.call(cmd))
+    device_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,4 @@
+"""B200-native channels-last GroupNorm with fused activation (drop-in for `gnnhwc`)."""
+from .gn_nhwc import ACTIVATION_CODES, GN_NHWC, GN_NHWC_Func
+
+__all__ = ["GN_NHWC", "GN_NHWC_Func", "ACTIVATION_CODES"]

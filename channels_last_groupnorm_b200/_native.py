@@ -1,0 +1,125 @@
+"""Loads the native libraries and exposes the C ABI through ctypes.
+
+There is no Python, PyTorch-eager or CPU fallback anywhere in this package: if the libraries
+cannot be loaded (or built from the in-tree sources), importing the package raises.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+_c_int64 = ctypes.c_int64
+_c_void_p = ctypes.c_void_p
+
+DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def _load():
+    try:
+        core_path, torch_path = _build.build_all()
+    except Exception as exc:  # pragma: no cover - depends on the toolchain of the machine
+        if not (os.path.exists(_build.CORE_LIB) and os.path.exists(_build.TORCH_LIB)):
+            raise ImportError(
+                "channels_last_groupnorm_b200: the native libraries are missing and could not be built "
+                "(run `python -m channels_last_groupnorm_b200.build`): %s" % exc) from exc
+        core_path, torch_path = _build.CORE_LIB, _build.TORCH_LIB
+    core = ctypes.CDLL(core_path, mode=ctypes.RTLD_GLOBAL)
+    torch.ops.load_library(torch_path)
+    return core
+
+
+lib = _load()
+
+lib.gnb200_version.restype = ctypes.c_int
+lib.gnb200_last_error.restype = ctypes.c_char_p
+lib.gnb200_act_code.restype = ctypes.c_int
+lib.gnb200_act_code.argtypes = [ctypes.c_char_p]
+for _name in ("gnb200_fwd_workspace_bytes", "gnb200_bwd_workspace_bytes"):
+    getattr(lib, _name).restype = ctypes.c_size_t
+    getattr(lib, _name).argtypes = [_c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int]
+lib.gnb200_fwd.restype = ctypes.c_int
+lib.gnb200_fwd.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int64, _c_int64, _c_int64, _c_int64,
+                           ctypes.c_double, ctypes.c_int, ctypes.c_int, _c_void_p, _c_void_p, _c_void_p,
+                           _c_void_p, ctypes.c_size_t, _c_void_p]
+lib.gnb200_bwd.restype = ctypes.c_int
+lib.gnb200_bwd.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                           _c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
+                           _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_size_t, _c_void_p]
+lib.gnb200_describe_plan.restype = ctypes.c_int
+lib.gnb200_describe_plan.argtypes = [_c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
+                                     ctypes.c_char_p, ctypes.c_int]
+lib.gnb200_launch_count.restype = ctypes.c_int
+lib.gnb200_launch_count.argtypes = [_c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int]
+
+
+class Gnb200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status, message):
+        super().__init__("%s (status %d)" % (message, status))
+        self.status = status
+
+
+def check(status):
+    if status != 0:
+        raise Gnb200Error(status, lib.gnb200_last_error().decode())
+
+
+def describe_plan(N, R, C, G, dtype, direction):
+    """Text description of the launch plan for a problem (direction 0 = forward, 1 = backward)."""
+    buf = ctypes.create_string_buffer(512)
+    lib.gnb200_describe_plan(N, R, C, G, DTYPE_CODES[dtype], direction, buf, 512)
+    return buf.value.decode()
+
+
+def launch_count(N, R, C, G, dtype, direction):
+    return lib.gnb200_launch_count(N, R, C, G, DTYPE_CODES[dtype], direction)
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def fwd_raw(x_nhwc, gamma, beta, G, eps, act, y=None, workspace=None, stream=None):
+    """Calls gnb200_fwd on torch CUDA tensors by raw pointer (used by tests and benchmarks).
+
+    x_nhwc: contiguous (N, R, C) tensor.  Returns (y, mean, rstd).  `workspace`, if given, is a
+    uint8 tensor that is reused instead of allocating one.
+    """
+    N, R, C = x_nhwc.shape
+    code = DTYPE_CODES[x_nhwc.dtype]
+    if y is None:
+        y = torch.empty_like(x_nhwc)
+    mean = torch.empty((N, G), device=x_nhwc.device, dtype=torch.float32)
+    rstd = torch.empty((N, G), device=x_nhwc.device, dtype=torch.float32)
+    need = lib.gnb200_fwd_workspace_bytes(N, R, C, G, code)
+    if workspace is None and need:
+        workspace = torch.empty(need, device=x_nhwc.device, dtype=torch.uint8)
+    s = torch.cuda.current_stream(x_nhwc.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_fwd(_ptr(x_nhwc), _ptr(gamma), _ptr(beta), N, R, C, G, float(eps), int(act), code,
+                         _ptr(y), _ptr(mean), _ptr(rstd), _ptr(workspace) if need else None,
+                         workspace.numel() if (need and workspace is not None) else 0, s))
+    return y, mean, rstd
+
+
+def bwd_raw(dy_nhwc, x_nhwc, gamma, beta, mean, rstd, G, act, dx=None, workspace=None, stream=None,
+            typed=True):
+    """Calls gnb200_bwd by raw pointer. Returns (dx, dparam_f32[2, C], dgamma, dbeta)."""
+    N, R, C = x_nhwc.shape
+    code = DTYPE_CODES[x_nhwc.dtype]
+    if dx is None:
+        dx = torch.empty_like(x_nhwc)
+    dparam = torch.empty((2, C), device=x_nhwc.device, dtype=torch.float32)
+    dgamma = torch.empty(C, device=x_nhwc.device, dtype=x_nhwc.dtype) if typed else None
+    dbeta = torch.empty(C, device=x_nhwc.device, dtype=x_nhwc.dtype) if typed else None
+    need = lib.gnb200_bwd_workspace_bytes(N, R, C, G, code)
+    if workspace is None and need:
+        workspace = torch.empty(need, device=x_nhwc.device, dtype=torch.uint8)
+    s = torch.cuda.current_stream(x_nhwc.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_bwd(_ptr(dy_nhwc), _ptr(x_nhwc), _ptr(gamma), _ptr(beta), _ptr(mean), _ptr(rstd),
+                         N, R, C, G, int(act), code, _ptr(dx), _ptr(dparam), _ptr(dgamma), _ptr(dbeta),
+                         _ptr(workspace) if need else None,
+                         workspace.numel() if (need and workspace is not None) else 0, s))
+    return dx, dparam, dgamma, dbeta

@@ -1,0 +1,502 @@
+// Backward GroupNorm (+activation) kernels for NHWC tensors, sm_100a.
+//
+// With  xh = (x - mean) * rstd,  yh = gamma * xh + beta,  dyh = dy * act'(yh)  (recomputed in
+// registers, never stored) the per-(sample, channel) sums are
+//     S1[n,c] = sum_r dyh          S2[n,c] = sum_r dyh * xh
+// and  dbeta_c = sum_n S1,  dgamma_c = sum_n S2,
+//      A[n,g] = sum_{c in g} gamma_c S1 / (D R),   B[n,g] = sum_{c in g} gamma_c S2 / (D R),
+//      dx = rstd * (gamma_c * dyh - A - xh * B).
+// This is the reference's formula (src/gnnhwc/csrc/gn_kernel.cu:613-618, 723-727, 786-800,
+// 868-872) rewritten in terms of xh so that no large terms cancel when |mean| >> 1/rstd.
+//
+//  fused   one launch + a tiny parameter-gradient kernel.  A cluster of k CTAs keeps the x and dy
+//          rows of one (sample, column block) slab in shared memory, reduces S1/S2, exchanges the
+//          group sums through distributed shared memory and writes dx from shared memory:
+//          x and dy are read from HBM once, dx is written once.
+//  two-pass  reduce kernel (per-tile channel sums to scratch) -> finalize (fixed-order sums, A, B)
+//          -> parameter-gradient kernel -> apply kernel (reverse tile order for L2 reuse).
+//
+// Every sum is formed in an order fixed by the launch geometry: no atomics, bit-identical reruns.
+#include "gn_kernels.h"
+
+namespace gnb200 {
+
+template <typename T, int VE>
+struct BwdLane {
+  float r[VE];    // rstd of the lane's group
+  float nmr[VE];  // -mean * rstd
+  float ga[VE];   // gamma
+  float be[VE];   // beta
+};
+
+template <typename T, int VE>
+__device__ __forceinline__ void lane_setup(const T* gamma, const T* beta, const float* mean_n, const float* rstd_n,
+                                           int c_first, int D, BwdLane<T, VE>& L) {
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    const int c = c_first + e;
+    const int grp = c / D;
+    const float rs = rstd_n[grp];
+    L.r[e] = rs;
+    L.nmr[e] = -mean_n[grp] * rs;
+    L.ga[e] = load_param<T>(gamma, c);
+    L.be[e] = load_param<T>(beta, c);
+  }
+}
+
+// Phase 1: accumulate S1, S2 for the thread's channels over its rows; optionally stash x, dy.
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ void stream_bwd_sums(const Pack<T, VE>* __restrict__ xs, const Pack<T, VE>* __restrict__ dys,
+                                                size_t row_stride_vec, int nrows, int ty, int TY, Pack<T, VE>* stash_x,
+                                                Pack<T, VE>* stash_dy, int stash_stride_vec, const BwdLane<T, VE>& L,
+                                                float (&s1)[VE], float (&s2)[VE]) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int U = 2;
+  int r = ty;
+  for (; r + (U - 1) * TY < nrows; r += U * TY) {
+    Pack<T, VE> vx[U], vd[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      vx[u] = ld_stream(xs + (size_t)(r + u * TY) * row_stride_vec);
+      vd[u] = ld_stream(dys + (size_t)(r + u * TY) * row_stride_vec);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (stash_x) {
+        stash_x[(size_t)(r + u * TY) * stash_stride_vec] = vx[u];
+        stash_dy[(size_t)(r + u * TY) * stash_stride_vec] = vd[u];
+      }
+      float fx[VE], fd[VE];
+      unpack<T, VE>(vx[u], fx);
+      unpack<T, VE>(vd[u], fd);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+        const float yh = fmaf(xh, L.ga[e], L.be[e]);
+        const float dyh = fd[e] * act_grad<ACT, FAST>(yh);
+        s1[e] += dyh;
+        s2[e] = fmaf(dyh, xh, s2[e]);
+      }
+    }
+  }
+  for (; r < nrows; r += TY) {
+    const Pack<T, VE> vx = ld_stream(xs + (size_t)r * row_stride_vec);
+    const Pack<T, VE> vd = ld_stream(dys + (size_t)r * row_stride_vec);
+    if (stash_x) {
+      stash_x[(size_t)r * stash_stride_vec] = vx;
+      stash_dy[(size_t)r * stash_stride_vec] = vd;
+    }
+    float fx[VE], fd[VE];
+    unpack<T, VE>(vx, fx);
+    unpack<T, VE>(vd, fd);
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+      const float yh = fmaf(xh, L.ga[e], L.be[e]);
+      const float dyh = fd[e] * act_grad<ACT, FAST>(yh);
+      s1[e] += dyh;
+      s2[e] = fmaf(dyh, xh, s2[e]);
+    }
+  }
+}
+
+// Phase 2: dx = rstd * (gamma * dyh - A - xh * B); sources may be shared or global memory.
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<T, VE>* dys, size_t src_stride_vec,
+                                              Pack<T, VE>* __restrict__ dst, size_t dst_stride_vec, int nrows, int ty,
+                                              int TY, const BwdLane<T, VE>& L, const float (&A)[VE],
+                                              const float (&B)[VE]) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int U = 2;
+  int r = ty;
+  for (; r + (U - 1) * TY < nrows; r += U * TY) {
+    Pack<T, VE> vx[U], vd[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      vx[u] = xs[(size_t)(r + u * TY) * src_stride_vec];
+      vd[u] = dys[(size_t)(r + u * TY) * src_stride_vec];
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float fx[VE], fd[VE];
+      unpack<T, VE>(vx[u], fx);
+      unpack<T, VE>(vd[u], fd);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+        const float yh = fmaf(xh, L.ga[e], L.be[e]);
+        const float dyh = fd[e] * act_grad<ACT, FAST>(yh);
+        fx[e] = L.r[e] * fmaf(L.ga[e], dyh, fmaf(-B[e], xh, -A[e]));
+      }
+      st_stream(dst + (size_t)(r + u * TY) * dst_stride_vec, pack<T, VE>(fx));
+    }
+  }
+  for (; r < nrows; r += TY) {
+    float fx[VE], fd[VE];
+    unpack<T, VE>(xs[(size_t)r * src_stride_vec], fx);
+    unpack<T, VE>(dys[(size_t)r * src_stride_vec], fd);
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+      const float yh = fmaf(xh, L.ga[e], L.be[e]);
+      const float dyh = fd[e] * act_grad<ACT, FAST>(yh);
+      fx[e] = L.r[e] * fmaf(L.ga[e], dyh, fmaf(-B[e], xh, -A[e]));
+    }
+    st_stream(dst + (size_t)r * dst_stride_vec, pack<T, VE>(fx));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// fused kernel.  grid.x = N * ncb * k, cluster (k,1,1).
+// dynamic smem: [x tile][dy tile][red 2*TY*CW][chan 2*CW][slot partial 2*slots][coef 2*slots]
+// scratch out : sums[(n * C + c) * 2 + {0,1}] = S1, S2 of the whole sample
+// ------------------------------------------------------------------------------------------------
+template <typename T, int VE, int ACT>
+__global__ void __launch_bounds__(kMaxThreads)
+    gn_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                        const T* __restrict__ beta, const float* __restrict__ mean_in,
+                        const float* __restrict__ rstd_in, T* __restrict__ dx, float* __restrict__ sums, const Geom g) {
+  extern __shared__ uint4 smem_raw[];
+  using P = Pack<T, VE>;
+  const unsigned k = cluster_nctarank(), rank = cluster_ctarank();
+  const int item = blockIdx.x / k;
+  const int n = item / g.ncb, cb = item - n * g.ncb;
+  const int c0 = cb * g.CW;
+  const int r0 = min((int)rank * g.rows_per_cta, g.R);
+  const int nrows = min(g.rows_per_cta, g.R - r0);
+
+  const size_t tile_bytes = ((size_t)g.rows_per_cta * g.CV * sizeof(P) + 15) & ~(size_t)15;
+  P* tile_x = reinterpret_cast<P*>(smem_raw);
+  P* tile_dy = reinterpret_cast<P*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
+  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + 2 * tile_bytes);
+  float* chan = red + 2 * g.TY * g.CW;
+  float* spart = chan + 2 * g.CW;  // [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 over this CTA's rows
+  float* coef = spart + 2 * g.slots;  // A[s], B[slots + s]
+
+  const int tid = threadIdx.x;
+  const int tx = tid % g.CV, ty = tid / g.CV;
+  const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
+  const size_t row_stride_vec = (size_t)g.C / VE;
+  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
+
+  BwdLane<T, VE> L;
+  float s1[VE], s2[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
+  if (streaming) {
+    lane_setup<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.D, L);
+    stream_bwd_sums<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base),
+                                row_stride_vec, nrows, ty, g.TY, tile_x + tx, tile_dy + tx, g.CV, L, s1, s2);
+  }
+  cta_fold_sums<VE>(g, s1, s2, tx, ty, (ty < g.TY), c0, red, chan);
+
+  int g_lo, n_slots;
+  cb_groups(g, c0, g_lo, n_slots);
+  const int c_valid = min(g.CW, g.C - c0);
+  {  // gamma-weighted group sums of this CTA's rows: one warp per group, fixed lane order
+    const int warp = tid >> 5, lane = tid & 31, nwarps = (blockDim.x + 31) >> 5;
+    for (int s = warp; s < n_slots; s += nwarps) {
+      const int lo = max((g_lo + s) * g.D, c0) - c0;
+      const int hi = min((g_lo + s + 1) * g.D, c0 + c_valid) - c0;
+      float a1 = 0.f, a2 = 0.f;
+      for (int c = lo + lane; c < hi; c += 32) {
+        const float ga = load_param<T>(gamma, c0 + c);
+        a1 = fmaf(ga, chan[c], a1);
+        a2 = fmaf(ga, chan[g.CW + c], a2);
+      }
+      a1 = warp_sum(a1);
+      a2 = warp_sum(a2);
+      if (lane == 0) {
+        spart[2 * s] = a1;
+        spart[2 * s + 1] = a2;
+      }
+    }
+  }
+  cluster_sync_all();
+
+  const float inv_m = 1.0f / ((float)g.D * (float)g.R);
+  for (int s = tid; s < n_slots; s += blockDim.x) {
+    float a1 = 0.f, a2 = 0.f;
+    for (unsigned q = 0; q < k; ++q) {
+      a1 += dsmem_ld_f32(spart + 2 * s, q);
+      a2 += dsmem_ld_f32(spart + 2 * s + 1, q);
+    }
+    coef[s] = a1 * inv_m;
+    coef[g.slots + s] = a2 * inv_m;
+  }
+  // whole-sample channel sums: channel c is summed (rank order) by CTA c % k
+  for (int c = tid; c < c_valid; c += blockDim.x) {
+    if ((unsigned)c % k != rank) continue;
+    float t1 = 0.f, t2 = 0.f;
+    for (unsigned q = 0; q < k; ++q) {
+      t1 += dsmem_ld_f32(chan + c, q);
+      t2 += dsmem_ld_f32(chan + g.CW + c, q);
+    }
+    float2* out = reinterpret_cast<float2*>(sums) + ((size_t)n * g.C + c0 + c);
+    *out = make_float2(t1, t2);
+  }
+  cluster_arrive();
+  __syncthreads();
+
+  if (streaming) {
+    float A[VE], B[VE];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const int s = (c0 + tx * VE + e) / g.D - g_lo;
+      A[e] = coef[s];
+      B[e] = coef[g.slots + s];
+    }
+    stream_bwd_dx<T, VE, ACT>(tile_x + tx, tile_dy + tx, g.CV, reinterpret_cast<P*>(dx + base), row_stride_vec, nrows,
+                              ty, g.TY, L, A, B);
+  }
+  cluster_wait();
+}
+
+// ------------------------------------------------------------------------------------------------
+// parameter gradients:  dbeta_c = sum_n S1[n,c],  dgamma_c = sum_n S2[n,c]  (n ascending per lane,
+// then a fixed tree over the 8 row lanes).  block (32, 8), grid ceil(C / 32).
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gn_bwd_param_kernel(const float* __restrict__ sums, int N, int C, float* __restrict__ dparam_f32,
+                                    T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  __shared__ float sm1[8][33], sm2[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float a1 = 0.f, a2 = 0.f;
+  if (c < C) {
+    for (int n = threadIdx.y; n < N; n += 8) {
+      const float2 v = reinterpret_cast<const float2*>(sums)[(size_t)n * C + c];
+      a1 += v.x;
+      a2 += v.y;
+    }
+  }
+  sm1[threadIdx.y][threadIdx.x] = a1;
+  sm2[threadIdx.y][threadIdx.x] = a2;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    float t1 = 0.f, t2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      t1 += sm1[j][threadIdx.x];
+      t2 += sm2[j][threadIdx.x];
+    }
+    dparam_f32[c] = t2;      // dgamma
+    dparam_f32[C + c] = t1;  // dbeta
+    if (dgamma) dgamma[c] = store_param<T>(t2);
+    if (dbeta) dbeta[c] = store_param<T>(t1);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// two-pass, kernel 1: per-tile channel sums.  grid.x = N * chunks * ncb.
+// scratch: tpart[((n * chunks + chunk) * C + c) * 2 + {0,1}]
+// ------------------------------------------------------------------------------------------------
+template <typename T, int VE, int ACT>
+__global__ void __launch_bounds__(kMaxThreads)
+    gn_bwd_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                         const T* __restrict__ beta, const float* __restrict__ mean_in,
+                         const float* __restrict__ rstd_in, float* __restrict__ tpart, const Geom g) {
+  extern __shared__ uint4 smem_raw[];
+  using P = Pack<T, VE>;
+  float* red = reinterpret_cast<float*>(smem_raw);
+  float* chan = red + 2 * g.TY * g.CW;
+  const int tile_id = blockIdx.x;
+  const int cb = tile_id % g.ncb;
+  const int chunk = (tile_id / g.ncb) % g.chunks;
+  const int n = tile_id / (g.ncb * g.chunks);
+  const int c0 = cb * g.CW;
+  const int r0 = chunk * g.rows_per_cta;
+  const int nrows = min(g.rows_per_cta, g.R - r0);
+  const int tid = threadIdx.x;
+  const int tx = tid % g.CV, ty = tid / g.CV;
+  const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
+  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
+
+  BwdLane<T, VE> L;
+  float s1[VE], s2[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
+  if (streaming) {
+    lane_setup<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.D, L);
+    stream_bwd_sums<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base),
+                                (size_t)g.C / VE, nrows, ty, g.TY, (P*)nullptr, (P*)nullptr, 0, L, s1, s2);
+  }
+  cta_fold_sums<VE>(g, s1, s2, tx, ty, (ty < g.TY), c0, red, chan);
+  const int c_valid = min(g.CW, g.C - c0);
+  float2* out = reinterpret_cast<float2*>(tpart) + ((size_t)n * g.chunks + chunk) * g.C + c0;
+  for (int c = tid; c < c_valid; c += blockDim.x) out[c] = make_float2(chan[c], chan[g.CW + c]);
+}
+
+// two-pass, kernel 2: block per (n, group): sums over tiles (ascending) -> S1, S2 per channel, and
+// A, B of the group.  block (32, 8): x over the group's channels, y over tile lanes.
+template <typename T>
+__global__ void gn_bwd_finalize_kernel(const float* __restrict__ tpart, const T* __restrict__ gamma,
+                                       float* __restrict__ sums, float* __restrict__ coef, const Geom g) {
+  __shared__ float sm1[8][33], sm2[8][33];
+  __shared__ float gs1[32], gs2[32];
+  const int n = blockIdx.x / g.G, grp = blockIdx.x - n * g.G;
+  const int lx = threadIdx.x, ly = threadIdx.y;
+  float w1 = 0.f, w2 = 0.f;  // gamma-weighted sums held by the (lx, ly == 0) threads
+  for (int cbase = 0; cbase < g.D; cbase += 32) {
+    const int cin = cbase + lx;
+    const bool valid = cin < g.D;
+    const int c = grp * g.D + cin;
+    float a1 = 0.f, a2 = 0.f;
+    if (valid) {
+      for (int chunk = ly; chunk < g.chunks; chunk += 8) {
+        const float2 v = reinterpret_cast<const float2*>(tpart)[((size_t)n * g.chunks + chunk) * g.C + c];
+        a1 += v.x;
+        a2 += v.y;
+      }
+    }
+    sm1[ly][lx] = a1;
+    sm2[ly][lx] = a2;
+    __syncthreads();
+    if (ly == 0 && valid) {
+      float t1 = 0.f, t2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        t1 += sm1[j][lx];
+        t2 += sm2[j][lx];
+      }
+      reinterpret_cast<float2*>(sums)[(size_t)n * g.C + c] = make_float2(t1, t2);
+      const float ga = load_param<T>(gamma, c);
+      w1 = fmaf(ga, t1, w1);
+      w2 = fmaf(ga, t2, w2);
+    }
+    __syncthreads();
+  }
+  if (ly == 0) {
+    gs1[lx] = w1;
+    gs2[lx] = w2;
+  }
+  __syncthreads();
+  if (ly == 0 && lx == 0) {
+    float t1 = 0.f, t2 = 0.f;
+    for (int j = 0; j < 32; ++j) {
+      t1 += gs1[j];
+      t2 += gs2[j];
+    }
+    const float inv_m = 1.0f / ((float)g.D * (float)g.R);
+    coef[((size_t)n * g.G + grp) * 2] = t1 * inv_m;
+    coef[((size_t)n * g.G + grp) * 2 + 1] = t2 * inv_m;
+  }
+}
+
+// two-pass, kernel 4: dx.  Reverse tile order relative to the reduce kernel.
+template <typename T, int VE, int ACT>
+__global__ void __launch_bounds__(kMaxThreads)
+    gn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                        const T* __restrict__ beta, const float* __restrict__ mean_in,
+                        const float* __restrict__ rstd_in, const float* __restrict__ coef, T* __restrict__ dx,
+                        const Geom g) {
+  using P = Pack<T, VE>;
+  const int tile_id = gridDim.x - 1 - blockIdx.x;
+  const int cb = tile_id % g.ncb;
+  const int chunk = (tile_id / g.ncb) % g.chunks;
+  const int n = tile_id / (g.ncb * g.chunks);
+  const int c0 = cb * g.CW;
+  const int r0 = chunk * g.rows_per_cta;
+  const int nrows = min(g.rows_per_cta, g.R - r0);
+  const int tid = threadIdx.x;
+  const int tx = tid % g.CV, ty = tid / g.CV;
+  if (ty >= g.TY || c0 + tx * VE >= g.C) return;
+  BwdLane<T, VE> L;
+  lane_setup<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.D, L);
+  float A[VE], B[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    const int grp = (c0 + tx * VE + e) / g.D;
+    A[e] = coef[((size_t)n * g.G + grp) * 2];
+    B[e] = coef[((size_t)n * g.G + grp) * 2 + 1];
+  }
+  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
+  const size_t rs = (size_t)g.C / VE;
+  stream_bwd_dx<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base), rs,
+                            reinterpret_cast<P*>(dx + base), rs, nrows, ty, g.TY, L, A, B);
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side launchers
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+static cudaError_t launch_param(const BwdCall& c, const float* sums, const Geom& g, cudaStream_t stream) {
+  const dim3 block(32, 8, 1);
+  const unsigned blocks = (unsigned)((g.C + 31) / 32);
+  gn_bwd_param_kernel<T><<<blocks, block, 0, stream>>>(sums, g.N, g.C, c.dparam_f32, (T*)c.dgamma, (T*)c.dbeta);
+  return cudaGetLastError();
+}
+
+template <typename T, int VE, int ACT>
+static cudaError_t launch_bwd_t(const BwdCall& c, const Plan& p, cudaStream_t stream) {
+  const Geom& g = p.geom;
+  if (p.fused) {
+    float* sums = reinterpret_cast<float*>(c.workspace);
+    auto kern = gn_bwd_fused_kernel<T, VE, ACT>;
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem_bytes);
+    if (err != cudaSuccess) return err;
+    if (g.k > 8) {
+      err = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (err != cudaSuccess) return err;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)p.threads, 1, 1);
+    cfg.dynamicSmemBytes = p.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)g.k;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    err = cudaLaunchKernelEx(&cfg, kern, (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean,
+                             c.rstd, (T*)c.dx, sums, g);
+    if (err != cudaSuccess) return err;
+    return launch_param<T>(c, sums, g, stream);
+  }
+  // two-pass scratch: [tile partials N*chunks*C*2][sums N*C*2][coef N*G*2]
+  float* tpart = reinterpret_cast<float*>(c.workspace);
+  float* sums = tpart + (size_t)g.N * g.chunks * g.C * 2;
+  float* coef = sums + (size_t)g.N * g.C * 2;
+  gn_bwd_reduce_kernel<T, VE, ACT><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>(
+      (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, tpart, g);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  gn_bwd_finalize_kernel<T><<<(unsigned)(g.N * g.G), dim3(32, 8, 1), 0, stream>>>(tpart, (const T*)c.gamma, sums, coef,
+                                                                                 g);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  err = launch_param<T>(c, sums, g, stream);
+  if (err != cudaSuccess) return err;
+  gn_bwd_apply_kernel<T, VE, ACT><<<(unsigned)p.grid, p.threads, 0, stream>>>(
+      (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, coef, (T*)c.dx, g);
+  return cudaGetLastError();
+}
+
+template <typename T, int VE>
+static cudaError_t launch_bwd_act(const BwdCall& c, const Plan& p, cudaStream_t stream) {
+  switch (c.act) {
+    case kActIdentity: return launch_bwd_t<T, VE, kActIdentity>(c, p, stream);
+    case kActRelu: return launch_bwd_t<T, VE, kActRelu>(c, p, stream);
+    case kActSilu: return launch_bwd_t<T, VE, kActSilu>(c, p, stream);
+    case kActGelu: return launch_bwd_t<T, VE, kActGelu>(c, p, stream);
+    default: return launch_bwd_t<T, VE, kActGeluTanh>(c, p, stream);
+  }
+}
+
+template <typename T>
+static cudaError_t launch_bwd_ve(const BwdCall& c, const Plan& p, cudaStream_t stream) {
+  constexpr int VFULL = 16 / sizeof(T);
+  return p.ve == 1 ? launch_bwd_act<T, 1>(c, p, stream) : launch_bwd_act<T, VFULL>(c, p, stream);
+}
+
+cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream) {
+  switch (c.dtype) {
+    case 0: return launch_bwd_ve<float>(c, p, stream);
+    case 1: return launch_bwd_ve<__half>(c, p, stream);
+    default: return launch_bwd_ve<__nv_bfloat16>(c, p, stream);
+  }
+}
+
+}  // namespace gnb200

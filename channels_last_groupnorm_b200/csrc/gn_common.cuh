@@ -1,0 +1,425 @@
+// Device-side building blocks shared by the forward and backward GroupNorm kernels (sm_100a).
+//
+// Conventions used throughout:
+//   T    element type of the tensors (float, __half, __nv_bfloat16); all arithmetic is fp32
+//   VE   elements per thread-vector: 16 bytes worth (4 fp32 / 8 half) on the fast path, 1 on the
+//        any-shape fallback
+//   a CTA works on a tile of `rows` pixels x CW channels ("column block") of one sample;
+//   inside it thread `tid` owns column vector tx = tid % CV and rows ty, ty+TY, ty+2*TY ...
+//   (CV = CW / VE, TY = row lanes), so a thread keeps the same channels for its whole loop and
+//   consecutive threads touch consecutive 16-byte vectors (coalesced along C).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <type_traits>
+
+namespace gnb200 {
+
+enum : int { kActIdentity = 0, kActRelu = 1, kActSilu = 2, kActGelu = 3, kActGeluTanh = 4 };
+
+constexpr int kMaxThreads = 512;
+
+// ---------------------------------------------------------------------------------------------
+// Welford / Chan running moments (what Welford.h:24-76 of the reference provides via a struct of
+// four fields; here: mean, sum of squared deviations, count as float)
+// ---------------------------------------------------------------------------------------------
+struct Moments {
+  float mean, m2, n;
+};
+
+__device__ __forceinline__ Moments moments_merge(const Moments a, const Moments b) {
+  const float n = a.n + b.n;
+  const float w = (n > 0.f) ? __fdiv_rn(b.n, n) : 0.f;
+  const float d = b.mean - a.mean;
+  Moments r;
+  r.mean = fmaf(d, w, a.mean);
+  r.m2 = a.m2 + b.m2 + d * d * a.n * w;
+  r.n = n;
+  return r;
+}
+
+__device__ __forceinline__ Moments moments_shfl_down(const Moments v, int delta) {
+  Moments o;
+  o.mean = __shfl_down_sync(0xffffffffu, v.mean, delta);
+  o.m2 = __shfl_down_sync(0xffffffffu, v.m2, delta);
+  o.n = __shfl_down_sync(0xffffffffu, v.n, delta);
+  return o;
+}
+
+// Fixed-order warp tree; the full result is valid in lane 0.
+__device__ __forceinline__ Moments moments_warp_reduce(Moments v) {
+#pragma unroll
+  for (int delta = 16; delta >= 1; delta >>= 1) v = moments_merge(v, moments_shfl_down(v, delta));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int delta = 16; delta >= 1; delta >>= 1) v += __shfl_down_sync(0xffffffffu, v, delta);
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// 16-byte (or scalar) vectors of T and conversion to / from fp32 lanes
+// ---------------------------------------------------------------------------------------------
+template <typename T, int VE>
+struct alignas(sizeof(T) * VE) Pack {
+  T v[VE];
+};
+
+template <typename T, int VE>
+__device__ __forceinline__ void unpack(const Pack<T, VE>& p, float (&f)[VE]) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) f[e] = p.v[e];
+  } else if constexpr (VE % 2 == 0) {
+#pragma unroll
+    for (int e = 0; e < VE; e += 2) {
+      float2 t;
+      if constexpr (std::is_same<T, __half>::value)
+        t = __half22float2(*reinterpret_cast<const __half2*>(&p.v[e]));
+      else
+        t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&p.v[e]));
+      f[e] = t.x;
+      f[e + 1] = t.y;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      if constexpr (std::is_same<T, __half>::value)
+        f[e] = __half2float(p.v[e]);
+      else
+        f[e] = __bfloat162float(p.v[e]);
+    }
+  }
+}
+
+template <typename T, int VE>
+__device__ __forceinline__ Pack<T, VE> pack(const float (&f)[VE]) {
+  Pack<T, VE> p;
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) p.v[e] = f[e];
+  } else if constexpr (VE % 2 == 0) {
+#pragma unroll
+    for (int e = 0; e < VE; e += 2) {
+      if constexpr (std::is_same<T, __half>::value)
+        *reinterpret_cast<__half2*>(&p.v[e]) = __floats2half2_rn(f[e], f[e + 1]);
+      else
+        *reinterpret_cast<__nv_bfloat162*>(&p.v[e]) = __floats2bfloat162_rn(f[e], f[e + 1]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      if constexpr (std::is_same<T, __half>::value)
+        p.v[e] = __float2half_rn(f[e]);
+      else
+        p.v[e] = __float2bfloat16_rn(f[e]);
+    }
+  }
+  return p;
+}
+
+template <typename T>
+__device__ __forceinline__ float load_param(const T* p, int i) {
+  if constexpr (sizeof(T) == 4)
+    return p[i];
+  else if constexpr (std::is_same<T, __half>::value)
+    return __half2float(p[i]);
+  else
+    return __bfloat162float(p[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ T store_param(float v) {
+  if constexpr (sizeof(T) == 4)
+    return v;
+  else if constexpr (std::is_same<T, __half>::value)
+    return __float2half_rn(v);
+  else
+    return __float2bfloat16_rn(v);
+}
+
+// Global loads / stores with cache hints.  Streaming data is read once per pass; results are
+// written once and not read again by this library.
+template <typename V>
+__device__ __forceinline__ V ld_stream(const V* p) {
+  if constexpr (sizeof(V) == 16) {
+    V out;
+    *reinterpret_cast<uint4*>(&out) = *reinterpret_cast<const uint4*>(p);
+    return out;
+  } else {
+    return *p;
+  }
+}
+template <typename V>
+__device__ __forceinline__ void st_stream(V* p, const V& v) {
+  if constexpr (sizeof(V) == 16)
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&v);
+  else
+    *p = v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Activations and their derivatives, evaluated in fp32.
+//   FAST = false (fp32 tensors): libdevice expf / tanhf / erff, IEEE division -> meets 1e-5.
+//   FAST = true  (16-bit tensors): hardware approximations (tanh.approx, ex2.approx, rcp.approx)
+//                whose error (<= ~5e-4) sits below the rounding of a 16-bit result.
+// Formulas: relu / silu / gelu(erf) / gelu(tanh) and derivatives as in gn_kernel.cu:62-106 of the
+// reference; the fast erf is Abramowitz & Stegun 7.1.26 (|err| <= 1.5e-7).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float tanh_fast(float v) {
+  float r;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float ex2_fast(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float rcp_fast(float v) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// erf(v / sqrt(2)) and exp(-v*v/2) from one exponential (fast path)
+__device__ __forceinline__ void erf_exp_fast(float v, float& erf_out, float& gauss_out) {
+  const float z = fabsf(v) * 0.70710678118654752f;
+  const float t = rcp_fast(fmaf(0.3275911f, z, 1.0f));
+  const float e = ex2_fast(v * v * -0.72134752044448170f);  // exp(-v^2/2) = 2^(-v^2/2 * log2 e)
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  p = p * t;
+  const float r = fmaf(-p, e, 1.0f);
+  erf_out = copysignf(r, v);
+  gauss_out = e;
+}
+
+template <int ACT, bool FAST>
+__device__ __forceinline__ float act_fwd(float v) {
+  if constexpr (ACT == kActIdentity) {
+    return v;
+  } else if constexpr (ACT == kActRelu) {
+    return v > 0.f ? v : 0.f;
+  } else if constexpr (ACT == kActSilu) {
+    if constexpr (FAST) {
+      const float h = 0.5f * v;  // v * sigmoid(v) = h * tanh(h) + h
+      return fmaf(h, tanh_fast(h), h);
+    } else {
+      return v / (1.0f + expf(-v));
+    }
+  } else if constexpr (ACT == kActGelu) {
+    if constexpr (FAST) {
+      float er, ga;
+      erf_exp_fast(v, er, ga);
+      const float h = 0.5f * v;
+      return fmaf(h, er, h);
+    } else {
+      return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    }
+  } else {
+    const float kBeta = 0.79788456080286536f;  // sqrt(2/pi)
+    const float inner = kBeta * fmaf(0.044715f * v * v, v, v);
+    const float h = 0.5f * v;
+    if constexpr (FAST)
+      return fmaf(h, tanh_fast(inner), h);
+    else
+      return fmaf(h, tanhf(inner), h);
+  }
+}
+
+// d act(v) / dv
+template <int ACT, bool FAST>
+__device__ __forceinline__ float act_grad(float v) {
+  if constexpr (ACT == kActIdentity) {
+    return 1.0f;
+  } else if constexpr (ACT == kActRelu) {
+    return v > 0.f ? 1.0f : 0.f;
+  } else if constexpr (ACT == kActSilu) {
+    float s;
+    if constexpr (FAST)
+      s = fmaf(0.5f, tanh_fast(0.5f * v), 0.5f);
+    else
+      s = 1.0f / (1.0f + expf(-v));
+    return s * fmaf(v, 1.0f - s, 1.0f);
+  } else if constexpr (ACT == kActGelu) {
+    const float kInvSqrt2Pi = 0.39894228040143268f;
+    if constexpr (FAST) {
+      float er, ga;
+      erf_exp_fast(v, er, ga);
+      return fmaf(v * kInvSqrt2Pi, ga, fmaf(0.5f, er, 0.5f));
+    } else {
+      const float cdf = 0.5f * (1.0f + erff(v * 0.70710678118654752f));
+      const float pdf = expf(-0.5f * v * v) * kInvSqrt2Pi;
+      return fmaf(v, pdf, cdf);
+    }
+  } else {
+    const float kBeta = 0.79788456080286536f;
+    const float v2 = v * v;
+    const float inner = kBeta * fmaf(0.044715f * v2, v, v);
+    float t;
+    if constexpr (FAST)
+      t = tanh_fast(inner);
+    else
+      t = tanhf(inner);
+    const float dinner = kBeta * fmaf(3.0f * 0.044715f, v2, 1.0f);
+    // 0.5 (1 + t) + 0.5 v (1 - t^2) dinner
+    return fmaf(0.5f * v * dinner, fmaf(-t, t, 1.0f), fmaf(0.5f, t, 0.5f));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Thread-block cluster helpers (raw PTX so arrive and wait can be split)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned cluster_nctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  cluster_arrive();
+  cluster_wait();
+}
+// Read one float from the shared memory of CTA `rank` of this cluster (DSMEM).
+__device__ __forceinline__ float dsmem_ld_f32(const float* local_smem_ptr, unsigned rank) {
+  const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(local_smem_ptr));
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Geometry of one launch, filled in by the host planner
+// ---------------------------------------------------------------------------------------------
+struct Geom {
+  int N, R, C, G, D;
+  int CW;            // channels per column block (multiple of VE)
+  int CV;            // CW / VE: vectors per tile row == threads along C
+  int TY;            // row lanes; CV * TY threads do the streaming work
+  int ncb;           // column blocks per sample
+  int rows_per_cta;  // pixels per CTA tile
+  int chunks;        // CTA tiles per (sample, column block): ceil(R / rows_per_cta)
+  int slots;         // upper bound on the groups a column block touches
+  int k;             // cluster size of the fused kernels (== chunks there)
+};
+
+// Groups touched by column block starting at channel c0 (width CW, clipped to C):
+// first group and how many.
+__device__ __forceinline__ void cb_groups(const Geom& g, int c0, int& g_lo, int& n_slots) {
+  const int c_end = min(c0 + g.CW, g.C);
+  g_lo = c0 / g.D;
+  n_slots = (c_end - 1) / g.D - g_lo + 1;
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-level fold of per-thread running moments into one Moments per touched group.
+//   in : mean[e], m2[e] for the thread's VE channels, cnt = rows the thread consumed
+//   out: slot_out[s] for s < n_slots (shared memory), valid after the trailing __syncthreads()
+// red  : 2 * TY * CW + TY floats of shared scratch,  chan : 3 * CW floats of shared scratch.
+// Every reduction order is fixed by the geometry, so results are run-to-run identical.
+// ---------------------------------------------------------------------------------------------
+template <int VE>
+__device__ __forceinline__ void cta_fold_moments(const Geom& g, const float (&mean)[VE], const float (&m2)[VE],
+                                                 float cnt, int tx, int ty, bool streaming, int c0, float* red,
+                                                 float* chan, float* slot_out /* 3 floats per slot */) {
+  const int CW = g.CW, TY = g.TY;
+  float* red_mean = red;
+  float* red_m2 = red + TY * CW;
+  float* red_cnt = red + 2 * TY * CW;
+  if (streaming) {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      red_mean[ty * CW + tx * VE + e] = mean[e];
+      red_m2[ty * CW + tx * VE + e] = m2[e];
+    }
+    if (tx == 0) red_cnt[ty] = cnt;
+  }
+  __syncthreads();
+  const int c_valid = min(CW, g.C - c0);
+  for (int c = threadIdx.x; c < c_valid; c += blockDim.x) {
+    Moments acc = {0.f, 0.f, 0.f};
+    for (int j = 0; j < TY; ++j) {
+      Moments o = {red_mean[j * CW + c], red_m2[j * CW + c], red_cnt[j]};
+      acc = moments_merge(acc, o);
+    }
+    chan[c] = acc.mean;
+    chan[CW + c] = acc.m2;
+    chan[2 * CW + c] = acc.n;
+  }
+  __syncthreads();
+  int g_lo, n_slots;
+  cb_groups(g, c0, g_lo, n_slots);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+  for (int s = warp; s < n_slots; s += nwarps) {
+    const int lo = max((g_lo + s) * g.D, c0) - c0;
+    const int hi = min((g_lo + s + 1) * g.D, c0 + c_valid) - c0;
+    Moments acc = {0.f, 0.f, 0.f};
+    for (int c = lo + lane; c < hi; c += 32) {
+      Moments o = {chan[c], chan[CW + c], chan[2 * CW + c]};
+      acc = moments_merge(acc, o);
+    }
+    acc = moments_warp_reduce(acc);
+    if (lane == 0) {
+      slot_out[3 * s + 0] = acc.mean;
+      slot_out[3 * s + 1] = acc.m2;
+      slot_out[3 * s + 2] = acc.n;
+    }
+  }
+  __syncthreads();
+}
+
+// CTA-level fold of two per-channel running sums (backward): per-thread s1[e], s2[e] ->
+// chan[c] = sum over row lanes of s1, chan[CW + c] = same for s2.  red: 2 * TY * CW floats.
+template <int VE>
+__device__ __forceinline__ void cta_fold_sums(const Geom& g, const float (&s1)[VE], const float (&s2)[VE], int tx,
+                                              int ty, bool streaming, int c0, float* red, float* chan) {
+  const int CW = g.CW, TY = g.TY;
+  float* red1 = red;
+  float* red2 = red + TY * CW;
+  if (streaming) {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      red1[ty * CW + tx * VE + e] = s1[e];
+      red2[ty * CW + tx * VE + e] = s2[e];
+    }
+  }
+  __syncthreads();
+  const int c_valid = min(CW, g.C - c0);
+  for (int c = threadIdx.x; c < c_valid; c += blockDim.x) {
+    float a1 = 0.f, a2 = 0.f;
+    for (int j = 0; j < TY; ++j) {
+      a1 += red1[j * CW + c];
+      a2 += red2[j * CW + c];
+    }
+    chan[c] = a1;
+    chan[CW + c] = a2;
+  }
+  __syncthreads();
+}
+
+// Shared-memory floats needed by the folds above for a geometry.
+__host__ __device__ inline size_t fold_scratch_floats(int CW, int TY, int slots) {
+  return (size_t)2 * TY * CW + TY + (size_t)3 * CW + (size_t)5 * slots + 8;
+}
+
+}  // namespace gnb200

@@ -1,0 +1,345 @@
+// Forward GroupNorm (+activation) kernels for NHWC tensors, sm_100a.
+//
+// Two launch plans (chosen by the host planner in gn_plan.cpp):
+//
+//  fused   one launch.  A thread-block cluster of k CTAs owns one (sample, column block) slab;
+//          each CTA streams its rows from HBM once (16-byte loads along C), keeps them in shared
+//          memory while accumulating Welford moments, the k partial moments are combined through
+//          distributed shared memory, and the tile is normalised, scaled, shifted, activated and
+//          written from shared memory.  HBM traffic: one read + one write of the tensor.
+//
+//  two-pass  for slabs that do not fit a cluster's shared memory: stats kernel (partial moments
+//          per CTA to scratch) -> finalize kernel (fixed-order merge -> mean, rstd) -> apply
+//          kernel, which walks the tensor in the opposite order so the part of x read last is
+//          re-read from L2.
+//
+// The reference computes the same quantities with compute_stats_pt1 / compute_stats_pt2 /
+// scale_shift_kernel (src/gnnhwc/csrc/gn_kernel.cu:132-224, 226-292, 305-412).
+#include "gn_kernels.h"
+
+namespace gnb200 {
+
+// Per-thread running moments over the rows this thread owns.  `stash`, when not null, receives a
+// copy of every vector (the shared-memory tile of the fused kernel).
+template <typename T, int VE>
+__device__ __forceinline__ void stream_moments(const Pack<T, VE>* __restrict__ src, size_t row_stride_vec, int nrows,
+                                               int ty, int TY, Pack<T, VE>* stash, int stash_stride_vec,
+                                               float (&mean)[VE], float (&m2)[VE], float& cnt) {
+  constexpr int U = 4;
+  int r = ty;
+  for (; r + (U - 1) * TY < nrows; r += U * TY) {
+    Pack<T, VE> v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ld_stream(src + (size_t)(r + u * TY) * row_stride_vec);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (stash) stash[(size_t)(r + u * TY) * stash_stride_vec] = v[u];
+      float f[VE];
+      unpack<T, VE>(v[u], f);
+      cnt += 1.0f;
+      const float inv = __frcp_rn(cnt);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float d = f[e] - mean[e];
+        mean[e] = fmaf(d, inv, mean[e]);
+        m2[e] = fmaf(d, f[e] - mean[e], m2[e]);
+      }
+    }
+  }
+  for (; r < nrows; r += TY) {
+    const Pack<T, VE> v = ld_stream(src + (size_t)r * row_stride_vec);
+    if (stash) stash[(size_t)r * stash_stride_vec] = v;
+    float f[VE];
+    unpack<T, VE>(v, f);
+    cnt += 1.0f;
+    const float inv = __frcp_rn(cnt);
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const float d = f[e] - mean[e];
+      mean[e] = fmaf(d, inv, mean[e]);
+      m2[e] = fmaf(d, f[e] - mean[e], m2[e]);
+    }
+  }
+}
+
+// y = act(x * a + b) over the rows this thread owns; source may be shared or global memory.
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ void stream_apply(const Pack<T, VE>* src, size_t src_stride_vec, Pack<T, VE>* __restrict__ dst,
+                                             size_t dst_stride_vec, int nrows, int ty, int TY, const float (&a)[VE],
+                                             const float (&b)[VE]) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int U = 4;
+  int r = ty;
+  for (; r + (U - 1) * TY < nrows; r += U * TY) {
+    Pack<T, VE> v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = src[(size_t)(r + u * TY) * src_stride_vec];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float f[VE];
+      unpack<T, VE>(v[u], f);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
+      st_stream(dst + (size_t)(r + u * TY) * dst_stride_vec, pack<T, VE>(f));
+    }
+  }
+  for (; r < nrows; r += TY) {
+    float f[VE];
+    unpack<T, VE>(src[(size_t)r * src_stride_vec], f);
+#pragma unroll
+    for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
+    st_stream(dst + (size_t)r * dst_stride_vec, pack<T, VE>(f));
+  }
+}
+
+// Per-lane affine coefficients  a = rstd * gamma,  b = beta - mean * a  for the thread's channels.
+// `stat_mean` / `stat_rstd` are indexed by group relative to g_base.
+template <typename T, int VE>
+__device__ __forceinline__ void lane_affine(const T* gamma, const T* beta, const float* stat_mean,
+                                            const float* stat_rstd, int g_base, int c_first, int D, float (&a)[VE],
+                                            float (&b)[VE]) {
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    const int c = c_first + e;
+    const int s = c / D - g_base;
+    const float ga = load_param<T>(gamma, c), be = load_param<T>(beta, c);
+    a[e] = stat_rstd[s] * ga;
+    b[e] = fmaf(-stat_mean[s], a[e], be);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// fused one-pass kernel.  grid.x = N * ncb * k, cluster = (k,1,1).
+// dynamic smem: [tile rows_per_cta * CV packs][fold scratch]
+// ------------------------------------------------------------------------------------------------
+template <typename T, int VE, int ACT>
+__global__ void __launch_bounds__(kMaxThreads)
+    gn_fwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                        T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, float eps,
+                        const Geom g) {
+  extern __shared__ uint4 smem_raw[];
+  using P = Pack<T, VE>;
+  const unsigned k = cluster_nctarank(), rank = cluster_ctarank();
+  const int item = blockIdx.x / k;  // (n, cb)
+  const int n = item / g.ncb, cb = item - n * g.ncb;
+  const int c0 = cb * g.CW;
+  const int r0 = min((int)rank * g.rows_per_cta, g.R);
+  const int nrows = min(g.rows_per_cta, g.R - r0);
+
+  P* tile = reinterpret_cast<P*>(smem_raw);
+  const size_t tile_bytes = ((size_t)g.rows_per_cta * g.CV * sizeof(P) + 15) & ~(size_t)15;
+  float* fold = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
+  float* red = fold;
+  float* chan = red + 2 * g.TY * g.CW + g.TY;
+  float* part = chan + 3 * g.CW;          // 3 floats per slot: this CTA's partial moments
+  float* stat = part + 3 * g.slots;       // mean[slots], rstd[slots]
+
+  const int tid = threadIdx.x;
+  const int tx = tid % g.CV, ty = tid / g.CV;
+  const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
+  const size_t row_stride_vec = (size_t)g.C / VE;
+
+  float mean[VE], m2[VE], cnt = 0.f;
+#pragma unroll
+  for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
+  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
+  if (streaming)
+    stream_moments<T, VE>(reinterpret_cast<const P*>(x + base), row_stride_vec, nrows, ty, g.TY, tile + tx, g.CV, mean,
+                          m2, cnt);
+  cta_fold_moments<VE>(g, mean, m2, cnt, tx, ty, (ty < g.TY), c0, red, chan, part);
+
+  // combine the k partials (rank order -> every CTA of the cluster gets bit-identical statistics)
+  cluster_sync_all();
+  int g_lo, n_slots;
+  cb_groups(g, c0, g_lo, n_slots);
+  for (int s = tid; s < n_slots; s += blockDim.x) {
+    Moments acc = {0.f, 0.f, 0.f};
+    for (unsigned q = 0; q < k; ++q) {
+      Moments o = {dsmem_ld_f32(part + 3 * s + 0, q), dsmem_ld_f32(part + 3 * s + 1, q),
+                   dsmem_ld_f32(part + 3 * s + 2, q)};
+      acc = moments_merge(acc, o);
+    }
+    const float var = fmaxf(acc.m2 / acc.n, 0.f);
+    const float rs = rsqrtf(var + eps);
+    stat[s] = acc.mean;
+    stat[g.slots + s] = rs;
+    if (rank == 0) {
+      mean_out[(size_t)n * g.G + g_lo + s] = acc.mean;
+      rstd_out[(size_t)n * g.G + g_lo + s] = rs;
+    }
+  }
+  cluster_arrive();  // this CTA no longer reads its peers' shared memory
+  __syncthreads();
+
+  if (streaming) {
+    float a[VE], b[VE];
+    lane_affine<T, VE>(gamma, beta, stat, stat + g.slots, g_lo, c0 + tx * VE, g.D, a, b);
+    stream_apply<T, VE, ACT>(tile + tx, g.CV, reinterpret_cast<P*>(y + base), row_stride_vec, nrows, ty, g.TY, a, b);
+  }
+  cluster_wait();  // do not exit (and release shared memory) while a peer may still read `part`
+}
+
+// ------------------------------------------------------------------------------------------------
+// two-pass, kernel 1: partial moments per CTA tile.  grid.x = N * chunks * ncb.
+// scratch layout: wpart[((n * chunks + chunk) * ncb + cb) * slots + s] = {mean, m2, n}
+// ------------------------------------------------------------------------------------------------
+template <typename T, int VE>
+__global__ void __launch_bounds__(kMaxThreads)
+    gn_fwd_stats_kernel(const T* __restrict__ x, float* __restrict__ wpart, const Geom g) {
+  extern __shared__ uint4 smem_raw[];
+  using P = Pack<T, VE>;
+  float* red = reinterpret_cast<float*>(smem_raw);
+  float* chan = red + 2 * g.TY * g.CW + g.TY;
+  float* part = chan + 3 * g.CW;
+
+  const int tile_id = blockIdx.x;
+  const int cb = tile_id % g.ncb;
+  const int chunk = (tile_id / g.ncb) % g.chunks;
+  const int n = tile_id / (g.ncb * g.chunks);
+  const int c0 = cb * g.CW;
+  const int r0 = chunk * g.rows_per_cta;
+  const int nrows = min(g.rows_per_cta, g.R - r0);
+  const int tid = threadIdx.x;
+  const int tx = tid % g.CV, ty = tid / g.CV;
+  const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
+
+  float mean[VE], m2[VE], cnt = 0.f;
+#pragma unroll
+  for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
+  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
+  if (streaming)
+    stream_moments<T, VE>(reinterpret_cast<const P*>(x + base), (size_t)g.C / VE, nrows, ty, g.TY, (P*)nullptr, 0, mean,
+                          m2, cnt);
+  cta_fold_moments<VE>(g, mean, m2, cnt, tx, ty, (ty < g.TY), c0, red, chan, part);
+  int g_lo, n_slots;
+  cb_groups(g, c0, g_lo, n_slots);
+  float* out = wpart + (size_t)tile_id * g.slots * 3;
+  for (int i = tid; i < 3 * n_slots; i += blockDim.x) out[i] = part[i];
+}
+
+// two-pass, kernel 2: one warp per (n, group) merges all partials that cover the group.
+__global__ void gn_fwd_finalize_kernel(const float* __restrict__ wpart, float* __restrict__ mean_out,
+                                       float* __restrict__ rstd_out, float eps, const Geom g) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= g.N * g.G) return;
+  const int n = warp / g.G, grp = warp - n * g.G;
+  const int cb_lo = (grp * g.D) / g.CW, cb_hi = ((grp + 1) * g.D - 1) / g.CW;
+  const int ncov = cb_hi - cb_lo + 1;
+  Moments acc = {0.f, 0.f, 0.f};
+  for (int i = lane; i < ncov * g.chunks; i += 32) {
+    const int cb = cb_lo + i % ncov, chunk = i / ncov;
+    const int s = grp - (cb * g.CW) / g.D;
+    const float* p = wpart + ((((size_t)n * g.chunks + chunk) * g.ncb + cb) * g.slots + s) * 3;
+    Moments o = {p[0], p[1], p[2]};
+    acc = moments_merge(acc, o);
+  }
+  acc = moments_warp_reduce(acc);
+  if (lane == 0) {
+    const float var = fmaxf(acc.m2 / acc.n, 0.f);
+    mean_out[warp] = acc.mean;
+    rstd_out[warp] = rsqrtf(var + eps);
+  }
+}
+
+// two-pass, kernel 3: normalise + affine + activation.  Tiles are visited in the reverse order of
+// kernel 1 (tile_id = last - blockIdx.x), so the most recently read part of x is re-read first.
+template <typename T, int VE, int ACT>
+__global__ void __launch_bounds__(kMaxThreads)
+    gn_fwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                        const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ y,
+                        const Geom g) {
+  using P = Pack<T, VE>;
+  const int tile_id = gridDim.x - 1 - blockIdx.x;
+  const int cb = tile_id % g.ncb;
+  const int chunk = (tile_id / g.ncb) % g.chunks;
+  const int n = tile_id / (g.ncb * g.chunks);
+  const int c0 = cb * g.CW;
+  const int r0 = chunk * g.rows_per_cta;
+  const int nrows = min(g.rows_per_cta, g.R - r0);
+  const int tid = threadIdx.x;
+  const int tx = tid % g.CV, ty = tid / g.CV;
+  if (ty >= g.TY || c0 + tx * VE >= g.C) return;
+  float a[VE], b[VE];
+  lane_affine<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, 0, c0 + tx * VE, g.D, a, b);
+  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
+  const size_t rs = (size_t)g.C / VE;
+  stream_apply<T, VE, ACT>(reinterpret_cast<const P*>(x + base), rs, reinterpret_cast<P*>(y + base), rs, nrows, ty, g.TY,
+                           a, b);
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side launchers
+// ------------------------------------------------------------------------------------------------
+template <typename T, int VE, int ACT>
+static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t stream) {
+  auto kern = gn_fwd_fused_kernel<T, VE, ACT>;
+  cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem_bytes);
+  if (err != cudaSuccess) return err;
+  if (p.geom.k > 8) {
+    err = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (err != cudaSuccess) return err;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)p.grid, 1, 1);
+  cfg.blockDim = dim3((unsigned)p.threads, 1, 1);
+  cfg.dynamicSmemBytes = p.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)p.geom.k;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, (T*)c.y, c.mean, c.rstd,
+                            c.eps, p.geom);
+}
+
+template <typename T, int VE, int ACT>
+static cudaError_t launch_two_pass(const FwdCall& c, const Plan& p, cudaStream_t stream) {
+  float* wpart = reinterpret_cast<float*>(c.workspace);
+  gn_fwd_stats_kernel<T, VE><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>((const T*)c.x, wpart, p.geom);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  const int warps = p.geom.N * p.geom.G;
+  const int fin_threads = 128;
+  const unsigned fin_blocks = (unsigned)(((size_t)warps * 32 + fin_threads - 1) / fin_threads);
+  gn_fwd_finalize_kernel<<<fin_blocks, fin_threads, 0, stream>>>(wpart, c.mean, c.rstd, c.eps, p.geom);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  gn_fwd_apply_kernel<T, VE, ACT><<<(unsigned)p.grid, p.threads, 0, stream>>>(
+      (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, (T*)c.y, p.geom);
+  return cudaGetLastError();
+}
+
+template <typename T, int VE, int ACT>
+static cudaError_t launch_fwd_t(const FwdCall& c, const Plan& p, cudaStream_t stream) {
+  return p.fused ? launch_fused<T, VE, ACT>(c, p, stream) : launch_two_pass<T, VE, ACT>(c, p, stream);
+}
+
+template <typename T, int VE>
+static cudaError_t launch_fwd_act(const FwdCall& c, const Plan& p, cudaStream_t stream) {
+  switch (c.act) {
+    case kActIdentity: return launch_fwd_t<T, VE, kActIdentity>(c, p, stream);
+    case kActRelu: return launch_fwd_t<T, VE, kActRelu>(c, p, stream);
+    case kActSilu: return launch_fwd_t<T, VE, kActSilu>(c, p, stream);
+    case kActGelu: return launch_fwd_t<T, VE, kActGelu>(c, p, stream);
+    default: return launch_fwd_t<T, VE, kActGeluTanh>(c, p, stream);
+  }
+}
+
+template <typename T>
+static cudaError_t launch_fwd_ve(const FwdCall& c, const Plan& p, cudaStream_t stream) {
+  constexpr int VFULL = 16 / sizeof(T);
+  return p.ve == 1 ? launch_fwd_act<T, 1>(c, p, stream) : launch_fwd_act<T, VFULL>(c, p, stream);
+}
+
+cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream) {
+  switch (c.dtype) {
+    case 0: return launch_fwd_ve<float>(c, p, stream);
+    case 1: return launch_fwd_ve<__half>(c, p, stream);
+    default: return launch_fwd_ve<__nv_bfloat16>(c, p, stream);
+  }
+}
+
+}  // namespace gnb200

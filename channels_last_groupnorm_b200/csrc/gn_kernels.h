@@ -1,0 +1,61 @@
+// Host-side declarations shared by the planner, the launchers and the C ABI.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include "gn_common.cuh"
+
+namespace gnb200 {
+
+// A launch plan for one direction of one problem.
+struct Plan {
+  bool fused;         // true: one cluster kernel holds the slab on chip; false: multi-kernel path
+  int ve;             // elements per thread-vector (16 bytes worth, or 1)
+  int threads;        // CTA size
+  long long grid;     // CTAs of the streaming kernels
+  size_t smem_bytes;  // dynamic shared memory of the first streaming kernel
+  size_t ws_bytes;    // scratch bytes this plan needs
+  int launches;       // kernels enqueued per call
+  Geom geom;
+};
+
+struct FwdCall {
+  const void* x;
+  const void* gamma;
+  const void* beta;
+  void* y;
+  float* mean;
+  float* rstd;
+  void* workspace;
+  float eps;
+  int act;
+  int dtype;
+};
+
+struct BwdCall {
+  const void* dy;
+  const void* x;
+  const void* gamma;
+  const void* beta;
+  const float* mean;
+  const float* rstd;
+  void* dx;
+  float* dparam_f32;  // [dgamma | dbeta], 2*C floats
+  void* dgamma;       // optional, tensor dtype
+  void* dbeta;        // optional, tensor dtype
+  void* workspace;
+  int act;
+  int dtype;
+};
+
+// direction: 0 forward, 1 backward.  `aligned16`: every tensor pointer is 16-byte aligned.
+// Returns false (and leaves *plan untouched) if the shape cannot be indexed.
+bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction, bool aligned16, Plan* plan);
+
+// Largest scratch requirement over the plans the library may pick for this problem.
+size_t plan_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction);
+
+cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream);
+cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream);
+
+}  // namespace gnb200

@@ -1,0 +1,214 @@
+// Host-side launch planner: picks vector width, column-block width, CTA shape, cluster size and
+// the fused / multi-kernel path for one problem.  Plays the role of the reference's
+// calc_block_params / closest_factor heuristics (src/gnnhwc/csrc/gn_kernel.cu:37-60, 121-128),
+// but is organised around B200 resources: 148 SMs, <= 227 KB shared memory per CTA, clusters of
+// up to 8 (16 non-portable) CTAs.
+//
+// Environment overrides (for experiments and benchmarks only):
+//   GNB200_FORCE_PATH = fused | twopass     GNB200_CW = channels per column block
+//   GNB200_K = cluster size                 GNB200_THREADS = target CTA size
+//   GNB200_TILE_KB = shared-memory tile budget per CTA (fused path)
+//   GNB200_ROWS = rows per CTA tile (multi-kernel path)
+#include <stdlib.h>
+#include <string.h>
+
+#include "gn_kernels.h"
+
+namespace gnb200 {
+
+namespace {
+
+constexpr int kSmCount = 148;
+constexpr size_t kSmemMaxOptin = 227 * 1024;
+
+long long gcd_ll(long long a, long long b) {
+  while (b) {
+    long long t = a % b;
+    a = b;
+    b = t;
+  }
+  return a;
+}
+
+int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  if (!v || !*v) return fallback;
+  return atoi(v);
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+size_t fwd_fold_floats(int CW, int TY, int slots) { return (size_t)2 * TY * CW + TY + (size_t)3 * CW + (size_t)5 * slots + 8; }
+size_t bwd_fold_floats(int CW, int TY, int slots) { return (size_t)2 * TY * CW + (size_t)2 * CW + (size_t)4 * slots + 8; }
+
+struct Shape {
+  int N, R, C, G, D, s, ve;
+  int direction;
+};
+
+// thread layout for a column block of CV vectors: TY row lanes, CTA size rounded to a warp
+void thread_layout(int CV, int rows_per_cta, int target_threads, int* TY, int* threads) {
+  int ty = target_threads / CV;
+  if (ty < 1) ty = 1;
+  if (ty > rows_per_cta) ty = rows_per_cta;
+  if (ty < 1) ty = 1;
+  *TY = ty;
+  *threads = round_up(CV * ty, 32);
+}
+
+// One fused candidate: column block of `cw` channels split over a cluster of `k` CTAs.
+// Returns false if the tile does not fit; otherwise fills *out and a heuristic score
+// (higher is better): SMs kept busy x row-segment efficiency x co-residency.
+bool plan_fused_candidate(const Shape& sh, int cw, int k, Plan* out, double* score) {
+  const int ve = sh.ve, s = sh.s;
+  const int target_threads = env_int("GNB200_THREADS", 256);
+  const size_t tile_budget = (size_t)env_int("GNB200_TILE_KB", 100) * 1024;
+  const int ncb = sh.C / cw;
+  const int CV = cw / ve;
+  const int ntiles = sh.direction == 0 ? 1 : 2;
+  const int slots = cw / sh.D;
+  const int rows = (sh.R + k - 1) / k;
+  if (k > 1 && (long long)rows * (k - 1) >= sh.R) return false;  // a CTA of the cluster would be idle
+  int TY, threads;
+  thread_layout(CV, rows, target_threads, &TY, &threads);
+  const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15) * ntiles;
+  const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots) : bwd_fold_floats(cw, TY, slots)) * 4;
+  if (tile + fold > kSmemMaxOptin - 1024) return false;
+
+  Plan p = {};
+  p.fused = true;
+  p.ve = ve;
+  p.threads = threads;
+  p.grid = (long long)sh.N * ncb * k;
+  p.smem_bytes = tile + fold;
+  p.ws_bytes = sh.direction == 0 ? 0 : (size_t)sh.N * sh.C * 2 * sizeof(float);
+  p.launches = sh.direction == 0 ? 1 : 2;
+  p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, rows, k, slots, k};
+  if (p.grid > 0x7fffffffLL) return false;
+  *out = p;
+
+  const long long seg = (long long)cw * s;
+  const double seg_eff = seg >= 256 ? 1.0 : seg >= 128 ? 0.95 : seg >= 64 ? 0.8 : seg >= 32 ? 0.6 : 0.4;
+  const double sms = (double)(p.grid < kSmCount ? p.grid : kSmCount);
+  const double co_resident = (tile + fold <= tile_budget) ? 1.0 : 0.9;  // >= 2 CTAs per SM overlap their phases
+  const double tile_eff = (tile / ntiles >= 16 * 1024 || p.grid <= kSmCount) ? 1.0 : 0.9;  // tiny tiles: overhead
+  const double sync_eff = 1.0 - 0.004 * k;  // mild preference for smaller clusters
+  *score = sms * seg_eff * co_resident * tile_eff * sync_eff;
+  return true;
+}
+
+bool plan_fused(const Shape& sh, Plan* out) {
+  const int ve = sh.ve;
+  const long long U = (long long)sh.D / gcd_ll(sh.D, ve) * ve;  // lcm(D, ve): whole groups, whole vectors
+  if (U > sh.C || sh.C % U != 0) return false;
+  const int units = (int)(sh.C / U);
+  const int force_cw = env_int("GNB200_CW", 0);
+  const int force_k = env_int("GNB200_K", 0);
+  const int k_max = force_k == 16 ? 16 : 8;  // 16 needs the non-portable cluster size: opt-in only
+  bool found = false;
+  double best = -1.0;
+  for (int m = 1; m <= units; ++m) {
+    if (units % m) continue;
+    const long long w = U * m;
+    if (w / ve > kMaxThreads) break;
+    if (force_cw > 0 && w != force_cw) continue;
+    for (int k = 1; k <= k_max; k *= 2) {
+      if (force_k > 0 && k != force_k) continue;
+      Plan cand;
+      double score;
+      if (!plan_fused_candidate(sh, (int)w, k, &cand, &score)) continue;
+      if (score > best * 1.0001) {
+        best = score;
+        *out = cand;
+        found = true;
+      }
+    }
+  }
+  return found;
+}
+
+bool plan_two_pass(const Shape& sh, Plan* out) {
+  const int ve = sh.ve, s = sh.s;
+  const int target_threads = env_int("GNB200_THREADS", 256);
+  int cw = sh.C;
+  if (cw / ve > 256) cw = 256 * ve;  // last column block may be ragged
+  const int force_cw = env_int("GNB200_CW", 0);
+  if (force_cw > 0 && force_cw % ve == 0 && force_cw / ve <= kMaxThreads && force_cw <= sh.C) cw = force_cw;
+  const int ncb = (sh.C + cw - 1) / cw;
+  const int CV = cw / ve;
+  int slots = (cw - 1) / sh.D + 2;
+  if (slots > sh.G) slots = sh.G;
+
+  // rows per CTA tile: ~64 KB of x per tile, but at least ~4 tiles per SM when the problem allows
+  const long long row_bytes = (long long)cw * s;
+  long long rows = (64 * 1024 + row_bytes - 1) / row_bytes;
+  if (rows > sh.R) rows = sh.R;
+  const long long want_tiles = 4LL * kSmCount;
+  long long chunks = (sh.R + rows - 1) / rows;
+  if ((long long)sh.N * ncb * chunks < want_tiles) {
+    long long need = (want_tiles + (long long)sh.N * ncb - 1) / ((long long)sh.N * ncb);
+    long long min_rows = 2LL * (target_threads / CV > 0 ? target_threads / CV : 1);
+    long long r2 = (sh.R + need - 1) / need;
+    if (r2 < min_rows) r2 = min_rows;
+    if (r2 < rows) rows = r2;
+  }
+  const int force_rows = env_int("GNB200_ROWS", 0);
+  if (force_rows > 0) rows = force_rows;
+  if (rows > sh.R) rows = sh.R;
+  if (rows < 1) rows = 1;
+  chunks = (sh.R + rows - 1) / rows;
+  int TY, threads;
+  thread_layout(CV, (int)rows, target_threads, &TY, &threads);
+
+  Plan p = {};
+  p.fused = false;
+  p.ve = ve;
+  p.threads = threads;
+  p.grid = (long long)sh.N * chunks * ncb;
+  if (p.grid > 0x7fffffffLL) return false;
+  if (sh.direction == 0) {
+    p.smem_bytes = fwd_fold_floats(cw, TY, slots) * 4;
+    p.ws_bytes = (size_t)p.grid * slots * 3 * sizeof(float);
+    p.launches = 3;
+  } else {
+    p.smem_bytes = bwd_fold_floats(cw, TY, slots) * 4;
+    p.ws_bytes = ((size_t)sh.N * chunks * sh.C * 2 + (size_t)sh.N * sh.C * 2 + (size_t)sh.N * sh.G * 2) * sizeof(float);
+    p.launches = 4;
+  }
+  p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, (int)rows, (int)chunks, slots, 1};
+  *out = p;
+  return true;
+}
+
+}  // namespace
+
+bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction, bool aligned16, Plan* plan) {
+  if (N < 1 || R < 1 || C < 1 || G < 1 || C % G != 0) return false;
+  if (N > 0x7fffffffLL || R > 0x7fffffffLL || C > (1 << 24) || (long long)N * G > 0x7fffffffLL) return false;
+  if ((double)N * (double)R * (double)C > 9.0e15) return false;
+  Shape sh;
+  sh.N = (int)N;
+  sh.R = (int)R;
+  sh.C = (int)C;
+  sh.G = (int)G;
+  sh.D = (int)(C / G);
+  sh.s = dtype == 0 ? 4 : 2;
+  const int vfull = 16 / sh.s;
+  sh.ve = (aligned16 && C % vfull == 0) ? vfull : 1;
+  sh.direction = direction;
+  const char* force = getenv("GNB200_FORCE_PATH");
+  const bool want_fused = !(force && !strcmp(force, "twopass"));
+  if (want_fused && plan_fused(sh, plan)) return true;
+  return plan_two_pass(sh, plan);
+}
+
+size_t plan_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction) {
+  size_t best = 0;
+  for (int aligned = 0; aligned < 2; ++aligned) {
+    Plan p;
+    if (make_plan(N, R, C, G, dtype, direction, aligned != 0, &p) && p.ws_bytes > best) best = p.ws_bytes;
+  }
+  return best;
+}
+
+}  // namespace gnb200

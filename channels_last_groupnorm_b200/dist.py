@@ -1,0 +1,53 @@
+"""Batch-sharded data parallelism for GroupNorm.
+
+GroupNorm statistics are per (sample, group), so splitting the batch dimension N over ranks needs
+no communication in forward, and in backward only the parameter gradients sum over samples:
+one all-reduce of the packed fp32 `[dgamma | dbeta]` buffer (2 * C floats).  The reference has no
+multi-GPU code; this module is the host logic of that extension and is backend-agnostic
+(NCCL on GPUs, gloo in the CPU tests).
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n_total: int, rank: int, world_size: int):
+    """Half-open sample range [lo, hi) of `rank` when n_total samples are split evenly.
+
+    The split must be exact: a ragged split would give ranks different amounts of work and the
+    benchmark configuration (N = 64 over 1/2/4/8 ranks) never needs it.
+    """
+    if world_size < 1 or not (0 <= rank < world_size):
+        raise ValueError("shard_bounds: rank %d is not in [0, %d)" % (rank, world_size))
+    if n_total % world_size != 0:
+        raise ValueError("shard_bounds: batch of %d samples does not split evenly over %d ranks"
+                         % (n_total, world_size))
+    per = n_total // world_size
+    return rank * per, (rank + 1) * per
+
+
+def shard_batch(t: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
+    """This rank's samples of a global (N, ...) tensor (a view, no copy)."""
+    lo, hi = shard_bounds(t.shape[0], rank, world_size)
+    return t[lo:hi]
+
+
+def allreduce_param_grads(dparam_f32: torch.Tensor, group=None) -> torch.Tensor:
+    """Sums the packed fp32 [2, C] parameter-gradient buffer over the ranks of `group`, in place.
+
+    Checks on the host that every rank brings the same number of channels before the collective
+    is issued, so a mismatch raises on all ranks instead of hanging the reduction.
+    """
+    if dparam_f32.dtype != torch.float32 or dparam_f32.ndim != 2 or dparam_f32.shape[0] != 2:
+        raise ValueError("allreduce_param_grads: expected a float32 [2, C] tensor, got %s %s"
+                         % (dparam_f32.dtype, tuple(dparam_f32.shape)))
+    if not dist.is_available() or not dist.is_initialized():
+        return dparam_f32
+    world = dist.get_world_size(group)
+    if world == 1:
+        return dparam_f32
+    sizes = [None] * world
+    dist.all_gather_object(sizes, int(dparam_f32.shape[1]), group=group)
+    if len(set(sizes)) != 1:
+        raise RuntimeError("allreduce_param_grads: ranks disagree on num_channels: %s" % sizes)
+    dist.all_reduce(dparam_f32, op=dist.ReduceOp.SUM, group=group)
+    return dparam_f32

@@ -1,0 +1,122 @@
+"""Host-side mirror of the reference's operator interface.
+
+`GN_NHWC` and `GN_NHWC_Func` keep the names, argument meaning and call pattern of
+src/gnnhwc/custom_gn.py:29-90 of latentCall145/channels-last-groupnorm, so a model written
+against `gnnhwc` only has to change its import.  What differs, on purpose:
+
+* there is no NCHW branch: the reference silently falls back to `F.group_norm` for inputs whose
+  channel stride is not 1 (custom_gn.py:75-79); here such inputs raise `ValueError`, as do CPU
+  tensors.  Everything that runs goes through the sm_100a kernels.
+* backward accepts any rank >= 3 (the reference's `dy.contiguous(memory_format=channels_last)`
+  only works for rank 4, custom_gn.py:44).
+* `process_group`: for batch-sharded data-parallel training the packed fp32 `[dgamma | dbeta]`
+  buffer written by the backward kernels is summed across the ranks of that group with one
+  all-reduce; forward needs no communication.
+"""
+import torch
+import torch.nn as nn
+
+from . import _native  # noqa: F401  (loads the libraries; raises if they are missing)
+
+ACTIVATION_CODES = {
+    "identity": 0,
+    "relu": 1,
+    "swish": 2,
+    "silu": 2,
+    "gelu": 3,
+    "gelu_tanh": 4,
+}
+
+
+def _as_nhwc_flat(t: torch.Tensor) -> torch.Tensor:
+    """(N, C, *spatial) tensor with NHWC-contiguous storage -> (N, C, R) view with strides (R*C, 1, C).
+
+    Copies only when the storage is not already NHWC-contiguous.
+    """
+    n, c = t.shape[0], t.shape[1]
+    inner = tuple(range(2, t.ndim))
+    nhwc = t.permute(0, *inner, 1)
+    if not nhwc.is_contiguous():
+        nhwc = nhwc.contiguous()
+    return nhwc.reshape(n, -1, c).permute(0, 2, 1)
+
+
+class GN_NHWC_Func(torch.autograd.Function):
+    """apply(X, weight, bias, G, eps, activation_code[, process_group]) -> Y
+
+    Same positional signature as the reference Function (custom_gn.py:30-31); the optional
+    seventh argument is the process group whose ranks share the parameter gradients.
+    """
+
+    @staticmethod
+    def forward(ctx, X, weight, bias, G, eps, activation, process_group=None):
+        if not X.is_cuda:
+            raise ValueError("GN_NHWC_Func: X must be a CUDA tensor; this package has no CPU path")
+        if X.ndim < 3:
+            raise ValueError("GN_NHWC_Func: X must have shape (N, C, *spatial) with at least one spatial dim")
+        ctx.x_shape = X.shape
+        X_flat = _as_nhwc_flat(X)
+        Y, means, rstds = torch.ops.gnb200.fwd(X_flat, weight, bias, int(G), float(eps), int(activation))
+        ctx.save_for_backward(X_flat, weight, bias, means, rstds)
+        ctx.G = int(G)
+        ctx.activation = int(activation)
+        ctx.process_group = process_group
+        return _restore_shape(Y, ctx.x_shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        X_flat, weight, bias, means, rstds = ctx.saved_tensors
+        dy_flat = _as_nhwc_flat(dy)
+        if ctx.process_group is None:
+            dx, dgamma, dbeta = torch.ops.gnb200.bwd(dy_flat, X_flat, weight, bias, means, rstds, ctx.G, ctx.activation)
+        else:
+            dx, dparam = torch.ops.gnb200.bwd_f32(dy_flat, X_flat, weight, bias, means, rstds, ctx.G, ctx.activation)
+            torch.distributed.all_reduce(dparam, op=torch.distributed.ReduceOp.SUM, group=ctx.process_group)
+            dgamma, dbeta = dparam[0].to(weight.dtype), dparam[1].to(weight.dtype)
+        return _restore_shape(dx, ctx.x_shape), dgamma, dbeta, None, None, None, None
+
+
+def _restore_shape(flat: torch.Tensor, shape) -> torch.Tensor:
+    """(N, C, R) channels-last view -> (N, C, *spatial) view over the same NHWC storage."""
+    n, c = shape[0], shape[1]
+    spatial = tuple(shape[2:])
+    nhwc = flat.permute(0, 2, 1).reshape(n, *spatial, c)
+    return nhwc.permute(0, nhwc.ndim - 1, *range(1, nhwc.ndim - 1))
+
+
+class GN_NHWC(nn.GroupNorm):
+    """`nn.GroupNorm` with a fused activation for channels-last inputs.
+
+    GN_NHWC(num_groups, num_channels, activation='identity', eps=1e-5, affine=True, device=None,
+    dtype=None, process_group=None).  `activation` is one of identity, relu, silu (alias swish),
+    gelu, gelu_tanh; an unknown name raises KeyError like the reference (custom_gn.py:52-61).
+    state_dict keys are those of `nn.GroupNorm` (`weight`, `bias`).
+    """
+
+    def __init__(self, num_groups: int, num_channels: int, activation="identity", process_group=None, **kwargs):
+        super().__init__(num_groups, num_channels, **kwargs)
+        self.activation = activation
+        self.act_code = ACTIVATION_CODES[activation]
+        self.process_group = process_group
+
+    @torch._dynamo.disable
+    def forward(self, x):
+        if not x.is_cuda:
+            raise ValueError("GN_NHWC: input must be a CUDA tensor; this package has no CPU path")
+        if x.ndim < 3 or x.shape[1] != self.num_channels:
+            raise ValueError("GN_NHWC: expected input of shape (N, %d, *spatial), got %s"
+                             % (self.num_channels, tuple(x.shape)))
+        if x.stride(1) != 1 and x.shape[1] != 1:
+            raise ValueError(
+                "GN_NHWC: input is not channels-last (stride of dim 1 is %d, expected 1). Convert it with "
+                "x.to(memory_format=torch.channels_last); this package has no NCHW fallback." % x.stride(1))
+        if self.affine:
+            w, b = self.weight, self.bias
+        else:
+            w = torch.ones((self.num_channels,), device=x.device, dtype=x.dtype)
+            b = torch.zeros((self.num_channels,), device=x.device, dtype=x.dtype)
+        return GN_NHWC_Func.apply(x, w, b, self.num_groups, self.eps, self.act_code, self.process_group)
+
+    def extra_repr(self):
+        return "{num_groups}, {num_channels}, eps={eps}, affine={affine}, activation={activation}".format(
+            **self.__dict__)

@@ -1,0 +1,113 @@
+/*
+ * gnb200 — channels-last (NHWC) GroupNorm + fused activation for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libgnb200.so.  Plain pointers and sizes only: no torch / ATen types cross this
+ * boundary, so the library can be bound from C, C++, ctypes, cgo, JNI ...
+ *
+ * What each entry point stands in for in the reference project
+ * (latentCall145/channels-last-groupnorm, paths relative to that project):
+ *
+ *   gnb200_fwd              <- run_gn_fwd_kernels<T>   src/gnnhwc/csrc/gn_kernel.h:11-24
+ *                                                      (body: src/gnnhwc/csrc/gn_kernel.cu:439-531)
+ *   gnb200_bwd              <- run_gn_bwd_kernels<T>   src/gnnhwc/csrc/gn_kernel.h:26-41
+ *                                                      (body: src/gnnhwc/csrc/gn_kernel.cu:932-1055)
+ *   gnb200_*_workspace_bytes<- the CUDACachingAllocator::raw_alloc sizes computed inside the two
+ *                              launchers (gn_kernel.cu:461, 954, 973-974, 998-1001); here the caller
+ *                              owns the scratch buffer instead
+ *   gnb200_act_code         <- the activation_to_code table   src/gnnhwc/custom_gn.py:52-59
+ *
+ * Tensor layout (identical to the reference's (N, R, C) view, custom_gn.cpp:24,66-67):
+ *   x, y, dy, dx : N * R * C elements, NHWC-contiguous (channel is the fastest dimension,
+ *                  R = product of the spatial extents)
+ *   gamma, beta  : C elements, same dtype as x
+ *   mean, rstd   : N * G floats (always fp32; the reference stores them in the tensor dtype)
+ *
+ * Every pointer is a device pointer on the current CUDA device.  All work is enqueued on
+ * `stream` and nothing synchronises with the host.  No entry point below allocates device
+ * memory: scratch comes from the caller (`workspace`).
+ */
+#ifndef GNB200_H_
+#define GNB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of x / y / dy / dx / gamma / beta */
+enum { GNB200_F32 = 0, GNB200_F16 = 1, GNB200_BF16 = 2 };
+
+/* fused activation; same numbering as the reference (src/gnnhwc/custom_gn.py:52-59) */
+enum {
+  GNB200_ACT_IDENTITY = 0,
+  GNB200_ACT_RELU = 1,
+  GNB200_ACT_SILU = 2, /* alias "swish" */
+  GNB200_ACT_GELU = 3, /* erf form */
+  GNB200_ACT_GELU_TANH = 4
+};
+
+/* status codes: 0 = success, negative = failure (gnb200_last_error() has the text) */
+enum {
+  GNB200_OK = 0,
+  GNB200_ERR_INVALID_ARGUMENT = -1, /* null pointer, bad dtype/activation, C % G != 0, sizes <= 0 ... */
+  GNB200_ERR_WORKSPACE = -2,        /* workspace missing or smaller than gnb200_*_workspace_bytes() */
+  GNB200_ERR_CUDA = -3,             /* a CUDA runtime call or kernel launch failed */
+  GNB200_ERR_UNSUPPORTED = -4       /* shape outside the supported index range */
+};
+
+/* Library version, e.g. 100 = 0.1.0 */
+int gnb200_version(void);
+
+/* Text of the last failure on the calling thread ("" if none). Never NULL. */
+const char* gnb200_last_error(void);
+
+/* "identity" | "relu" | "silu" | "swish" | "gelu" | "gelu_tanh" -> code, or -1 if unknown. */
+int gnb200_act_code(const char* name);
+
+/* Scratch bytes that gnb200_fwd / gnb200_bwd need for this problem (0 is possible). */
+size_t gnb200_fwd_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype);
+size_t gnb200_bwd_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype);
+
+/*
+ * Forward:  y = act(gamma * (x - mean) * rstd + beta), statistics per (sample, group) over the
+ * R * (C/G) elements of the slab, biased variance, rstd = 1/sqrt(var + eps).
+ * Writes y (N*R*C), mean and rstd (N*G floats each).  `workspace` may be NULL when
+ * gnb200_fwd_workspace_bytes() is 0.  `stream` is a cudaStream_t (NULL = default stream).
+ */
+int gnb200_fwd(const void* x, const void* gamma, const void* beta,
+               int64_t N, int64_t R, int64_t C, int64_t G, double eps, int act, int dtype,
+               void* y, float* mean, float* rstd,
+               void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Backward.  Reads dy, x, gamma, beta and the mean/rstd written by gnb200_fwd.
+ * Writes dx (N*R*C) and the parameter gradients:
+ *   dgamma_dbeta_f32 : 2*C floats, [dgamma | dbeta] packed, summed over this call's N samples in
+ *                      a fixed order (no atomics).  Required.  This is the buffer a data-parallel
+ *                      caller all-reduces across ranks.
+ *   dgamma, dbeta    : C elements each in the tensor dtype (what the reference returns,
+ *                      custom_gn.cpp:70-71).  Either may be NULL to skip the cast.
+ */
+int gnb200_bwd(const void* dy, const void* x, const void* gamma, const void* beta,
+               const float* mean, const float* rstd,
+               int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype,
+               void* dx, float* dgamma_dbeta_f32, void* dgamma, void* dbeta,
+               void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Describes the launch plan chosen for a problem ("fwd fused k=4 cw=64 ..."), for logs, tests
+ * and benchmarks.  Writes at most buf_len bytes including the terminating NUL; returns the
+ * number of bytes the full text needs.  direction: 0 = forward, 1 = backward.
+ */
+int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction,
+                         char* buf, int buf_len);
+
+/* Number of kernel launches gnb200_fwd / gnb200_bwd enqueue for this problem. */
+int gnb200_launch_count(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GNB200_H_ */

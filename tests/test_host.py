@@ -1,0 +1,129 @@
+"""CPU tests of the host side: C ABI exports, argument validation, planner, module interface."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import channels_last_groupnorm_b200 as pkg
+from channels_last_groupnorm_b200 import _native as nt
+from channels_last_groupnorm_b200 import build as gnbuild
+
+
+def _declared_functions(header_text):
+    text = re.sub(r"/\*.*?\*/", "", header_text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gnb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(repo_root):
+    header = open(os.path.join(repo_root, "include", "gnb200.h")).read()
+    names = _declared_functions(header)
+    assert {"gnb200_fwd", "gnb200_bwd", "gnb200_fwd_workspace_bytes", "gnb200_bwd_workspace_bytes"} <= set(names)
+    lib = ctypes.CDLL(gnbuild.CORE_LIB)
+    for name in names:
+        assert hasattr(lib, name), "libgnb200.so does not export " + name
+
+
+def test_core_library_does_not_link_torch():
+    # the C ABI must be bindable without PyTorch: no libtorch / libc10 in the dynamic section
+    with open(gnbuild.CORE_LIB, "rb") as f:
+        blob = f.read()
+    assert b"libtorch" not in blob and b"libc10" not in blob
+
+
+def test_activation_codes_match_reference_table():
+    # src/gnnhwc/custom_gn.py:52-59 of the reference
+    want = {"identity": 0, "relu": 1, "swish": 2, "silu": 2, "gelu": 3, "gelu_tanh": 4}
+    assert pkg.ACTIVATION_CODES == want
+    for name, code in want.items():
+        assert nt.lib.gnb200_act_code(name.encode()) == code
+    assert nt.lib.gnb200_act_code(b"mish") == -1
+
+
+def test_invalid_arguments_are_rejected_before_any_cuda_call():
+    f = nt.lib.gnb200_fwd
+    one = ctypes.c_void_p(16)  # never dereferenced: validation fails first
+    assert f(one, one, one, 2, 4, 6, 4, 1e-5, 0, 0, one, one, one, None, 0, None) == -1  # C % G != 0
+    assert "divisible" in nt.lib.gnb200_last_error().decode()
+    assert f(one, one, one, 2, 4, 8, 4, 1e-5, 9, 0, one, one, one, None, 0, None) == -1  # bad activation
+    assert f(one, one, one, 2, 4, 8, 4, 1e-5, 0, 7, one, one, one, None, 0, None) == -1  # bad dtype
+    assert f(one, one, one, 0, 4, 8, 4, 1e-5, 0, 0, one, one, one, None, 0, None) == -1  # empty batch
+    assert f(None, one, one, 2, 4, 8, 4, 1e-5, 0, 0, one, one, one, None, 0, None) == -1  # null x
+    b = nt.lib.gnb200_bwd
+    assert b(one, one, one, one, one, one, 2, 4, 8, 4, 0, 0, one, None, None, None, None, 0, None) == -1
+    with pytest.raises(nt.Gnb200Error):
+        nt.check(-1)
+
+
+def test_workspace_is_required_when_the_plan_needs_one():
+    # a slab far too large for a cluster: multi-kernel path, scratch needed
+    N, R, C, G = 1, 1 << 20, 128, 32
+    need = nt.lib.gnb200_fwd_workspace_bytes(N, R, C, G, 1)
+    assert need > 0
+    one = ctypes.c_void_p(16)
+    rc = nt.lib.gnb200_fwd(one, one, one, N, R, C, G, 1e-5, 2, 1, one, one, one, None, 0, None)
+    assert rc == -2 and "workspace" in nt.lib.gnb200_last_error().decode()
+
+
+@pytest.mark.parametrize("shape,dtype,path", [
+    ((2, 1024, 128, 32), torch.float32, "fused"),
+    ((64, 4096, 256, 32), torch.bfloat16, "fused"),
+    ((1, 4096, 320, 32), torch.float16, "fused"),
+    ((1, 1 << 20, 128, 32), torch.float16, "twopass"),
+    ((1, 512 * 512, 256, 32), torch.float16, "twopass"),
+    ((2, 25, 3909, 3), torch.float32, "twopass"),
+])
+def test_planner_paths(shape, dtype, path):
+    for direction in (0, 1):
+        text = nt.describe_plan(*shape, dtype, direction)
+        assert (" " + path + " ") in text, text
+        fields = dict(kv.split("=") for kv in text.split()[2:])
+        assert int(fields["threads"]) % 32 == 0 and int(fields["threads"]) <= 512
+        assert int(fields["smem"]) <= 227 * 1024
+        assert int(fields["cw"]) % int(fields["ve"]) == 0
+        if path == "fused":
+            assert int(fields["k"]) in (1, 2, 4, 8)
+            D = shape[2] // shape[3]
+            assert int(fields["cw"]) % D == 0  # a cluster owns whole groups
+            assert nt.launch_count(*shape, dtype, direction) == (1 if direction == 0 else 2)
+
+
+def test_planner_env_override(monkeypatch):
+    monkeypatch.setenv("GNB200_FORCE_PATH", "twopass")
+    assert " twopass " in nt.describe_plan(2, 1024, 128, 32, torch.float32, 0)
+    monkeypatch.delenv("GNB200_FORCE_PATH")
+    assert " fused " in nt.describe_plan(2, 1024, 128, 32, torch.float32, 0)
+
+
+def test_module_interface_matches_reference():
+    m = pkg.GN_NHWC(32, 128, activation="silu", eps=1e-6)
+    assert isinstance(m, torch.nn.GroupNorm)
+    assert m.activation == "silu" and m.act_code == 2 and m.eps == 1e-6 and m.affine
+    assert set(m.state_dict().keys()) == {"weight", "bias"}
+    assert repr(m) == "GN_NHWC(32, 128, eps=1e-06, affine=True, activation=silu)"
+    assert pkg.GN_NHWC(4, 8, activation="swish").act_code == 2
+    with pytest.raises(KeyError):
+        pkg.GN_NHWC(4, 8, activation="mish")
+    plain = torch.nn.GroupNorm(32, 128)
+    m.load_state_dict(plain.state_dict())  # checkpoints of nn.GroupNorm load unchanged
+    assert pkg.GN_NHWC(4, 8, affine=False).weight is None
+
+
+def test_module_refuses_cpu_and_channels_first_inputs():
+    m = pkg.GN_NHWC(4, 8)
+    with pytest.raises(ValueError, match="CUDA"):
+        m(torch.randn(2, 8, 4, 4).to(memory_format=torch.channels_last))
+    with pytest.raises(ValueError, match="CUDA"):
+        pkg.GN_NHWC_Func.apply(torch.randn(2, 8, 4, 4), m.weight, m.bias, 4, 1e-5, 0)
+
+
+def test_torch_ops_are_registered_with_reference_schemas():
+    fwd = torch.ops.gnb200.fwd.default._schema
+    bwd = torch.ops.gnb200.bwd.default._schema
+    assert [a.type.kind() for a in fwd.arguments] == ["TensorType"] * 3 + ["IntType", "FloatType", "IntType"]
+    assert len(fwd.returns) == 3
+    assert [a.type.kind() for a in bwd.arguments] == ["TensorType"] * 6 + ["IntType", "IntType"]
+    assert len(bwd.returns) == 3
+    with pytest.raises(RuntimeError, match="CUDA"):
+        torch.ops.gnb200.fwd(torch.randn(1, 8, 4).permute(0, 2, 1), torch.ones(8), torch.zeros(8), 2, 1e-5, 0)

@@ -1,0 +1,390 @@
+"""GPU parity tests (B200): the CUDA path, called through the C ABI, against the CPU oracles.
+
+Tolerances (max-abs error relative to max(1, max|oracle|)): 1e-5 for fp32 tensors, 1e-2 for
+fp16 / bf16 tensors, on y, dx, dgamma and dbeta.
+"""
+import glob
+import os
+
+import pytest
+import torch
+
+from oracle import gn_oracle as O
+
+from .cases import CFG1, CFG2, CFG3, CFG4, CFG5, REFERENCE_CUSTOM, REFERENCE_TRAILING
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+REF_LIB = os.path.join(os.path.dirname(GOLDEN_DIR), "..", "oracle", "_ref", "gn_op.so")
+
+
+@pytest.fixture(scope="module")
+def nt():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from channels_last_groupnorm_b200 import _native
+
+    return _native
+
+
+def _flat(t):
+    """(N, C, *spatial) channels-last tensor -> contiguous (N, R, C) view of the same storage."""
+    n, c = t.shape[0], t.shape[1]
+    nhwc = t.permute(0, *range(2, t.ndim), 1)
+    assert nhwc.is_contiguous()
+    return nhwc.reshape(n, -1, c)
+
+
+def _unflat(a, shape):
+    n, c = shape[0], shape[1]
+    return a.reshape(n, *shape[2:], c).permute(0, len(shape) - 1, *range(1, len(shape) - 1))
+
+
+def run_cabi(nt, x, ga, be, dy, G, eps, act):
+    """Forward + backward through gnb200_fwd / gnb200_bwd; returns logical-shape tensors."""
+    code = O.ACT_CODES[act]
+    xd, gd, bd = x.cuda(), ga.cuda(), be.cuda()
+    y, mean, rstd = nt.fwd_raw(_flat(xd), gd, bd, G, eps, code)
+    out = {"y": _unflat(y, x.shape), "mean": mean, "rstd": rstd}
+    if dy is not None:
+        dx, dparam, dgamma, dbeta = nt.bwd_raw(_flat(dy.cuda()), _flat(xd), gd, bd, mean, rstd, G, code)
+        out.update(dx=_unflat(dx, x.shape), dgamma=dgamma, dbeta=dbeta, dparam=dparam)
+    torch.cuda.synchronize()
+    return out
+
+
+def check_against(out, want, dtype, keys=("y", "dx", "dgamma", "dbeta"), scale=1.0):
+    tol = O.TOLERANCE[dtype] * scale
+    errs = {k: O.rel_err(out[k], want[k]) for k in keys if k in want and k in out}
+    bad = {k: e for k, e in errs.items() if not e <= tol}
+    assert not bad, "error above %.1e: %s (all: %s)" % (tol, bad, errs)
+    return errs
+
+
+def _case_inputs(case, seed=0):
+    N, C, sp, G, eps, act, dt, dist, scale = case
+    x, ga, be, dy = O.make_inputs(N, C, sp, DT[dt], seed=seed, x_dist=dist, x_scale=scale)
+    return x, ga, be, dy, G, eps, act, DT[dt]
+
+
+def _id(case):
+    N, C, sp, G, eps, act, dt = case[:7]
+    return "%s-%s-%dx%dx%s-g%d" % (dt, act, N, C, "x".join(map(str, sp)), G)
+
+
+# ------------------------------------------------------------------------------------------------
+# benchmark configurations at sizes the CPU oracle finishes in seconds
+# ------------------------------------------------------------------------------------------------
+SMALL_CASES = [CFG1] + CFG2 + CFG3[:1] + CFG4[:1] + CFG5
+
+
+@pytest.mark.parametrize("path", ["auto", "twopass"])
+@pytest.mark.parametrize("case", SMALL_CASES, ids=_id)
+def test_baseline_configs_against_oracle(nt, case, path, monkeypatch):
+    if path == "twopass":
+        monkeypatch.setenv("GNB200_FORCE_PATH", "twopass")
+    x, ga, be, dy, G, eps, act, dtype = _case_inputs(case)
+    out = run_cabi(nt, x, ga, be, dy, G, eps, act)
+    big = x.numel() > 2_000_000
+    want = O.oracle_torch(x, ga, be, dy, G, eps, act) if big else O.oracle_c(x, ga, be, dy, G, eps, act, threads=4)
+    check_against(out, want, dtype)
+    if not big:  # saved statistics are part of the contract between fwd and bwd
+        assert O.rel_err(out["mean"], want["mean"]) < 1e-5
+        assert O.rel_err(out["rstd"] / want["rstd"].cuda().float(), torch.ones_like(want["rstd"])) < 1e-5
+    # packed fp32 gradient buffer == typed outputs before rounding
+    assert O.rel_err(out["dparam"][0], want["dgamma"]) <= O.TOLERANCE[dtype]
+    assert O.rel_err(out["dparam"][1], want["dbeta"]) <= O.TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("act", O.ACT_NAMES)
+@pytest.mark.parametrize("dt", ["float32", "float16", "bfloat16"])
+def test_every_activation_and_dtype(nt, act, dt):
+    x, ga, be, dy = O.make_inputs(3, 48, (9, 11), DT[dt], seed=2, x_dist="uniform3")
+    out = run_cabi(nt, x, ga, be, dy, 6, 1e-5, act)
+    check_against(out, O.oracle_c(x, ga, be, dy, 6, 1e-5, act), DT[dt])
+
+
+@pytest.mark.parametrize("shape", REFERENCE_CUSTOM, ids=lambda s: "%dx%dx%s-g%d" % (s[0], s[1], "x".join(map(str, s[2])), s[3]))
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+def test_reference_custom_shapes(nt, shape, dt):
+    N, C, sp, G = shape
+    x, ga, be, dy = O.make_inputs(N, C, sp, DT[dt], seed=1)
+    out = run_cabi(nt, x, ga, be, dy, G, 1e-5, "identity")
+    check_against(out, O.oracle_c(x, ga, be, dy, G, 1e-5, "identity", threads=4), DT[dt])
+
+
+# ------------------------------------------------------------------------------------------------
+# full-size configurations: checked on the device against torch's fp64 GroupNorm (CUDA), which is
+# itself checked against the CPU oracle at the small sizes above
+# ------------------------------------------------------------------------------------------------
+def _cuda_fp64_reference(x, ga, be, dy, G, eps, act):
+    xs = x.double().requires_grad_(True)
+    g = ga.double().requires_grad_(True)
+    b = be.double().requires_grad_(True)
+    y = O.torch_activation(act)(torch.nn.functional.group_norm(xs, G, g, b, eps))
+    dx, dg, db = torch.autograd.grad(y, (xs, g, b), dy.double())
+    return {"y": y.detach(), "dx": dx, "dgamma": dg, "dbeta": db}
+
+
+def test_cuda_fp64_reference_agrees_with_cpu_oracle(nt):
+    x, ga, be, dy, G, eps, act, dtype = _case_inputs(CFG5[0])
+    a = _cuda_fp64_reference(x.cuda(), ga.cuda(), be.cuda(), dy.cuda(), G, eps, act)
+    b = O.oracle_c(x, ga, be, dy, G, eps, act)
+    for k in ("y", "dx", "dgamma", "dbeta"):
+        assert O.rel_err(a[k], b[k]) < 1e-10
+
+
+@pytest.mark.parametrize("case", CFG3[1:3] + CFG4[3:], ids=_id)
+def test_full_size_configs_on_device(nt, case):
+    N, C, sp, G, eps, act, dt, dist, scale = case
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    shape = (N, *sp, C)
+    x = (torch.randn(shape, device="cuda", generator=gen) * scale).to(DT[dt]).permute(0, 3, 1, 2)
+    dy = torch.randn(shape, device="cuda", generator=gen).to(DT[dt]).permute(0, 3, 1, 2)
+    ga = (torch.rand(C, device="cuda", generator=gen) + 0.5).to(DT[dt])
+    be = (torch.randn(C, device="cuda", generator=gen) * 0.1).to(DT[dt])
+    out = run_cabi(nt, x, ga, be, dy, G, eps, act)
+    want = _cuda_fp64_reference(x, ga, be, dy, G, eps, act)
+    check_against(out, want, DT[dt])
+    # size-independent property: with identity activation and gamma=1, beta=0 every
+    # (sample, group) slab of y has mean 0 and variance 1
+    one, zero = torch.ones_like(ga), torch.zeros_like(be)
+    y = run_cabi(nt, x, one, zero, None, G, eps, "identity")["y"]
+    slabs = y.float().reshape(N, G, C // G, -1)
+    assert slabs.mean((2, 3)).abs().max() < 2e-3
+    assert (slabs.var((2, 3), correction=0) - 1).abs().max() < 5e-3
+
+
+# ------------------------------------------------------------------------------------------------
+# robustness of the statistics and of the plumbing
+# ------------------------------------------------------------------------------------------------
+def test_large_mean_small_variance_fp32(nt):
+    g = torch.Generator().manual_seed(3)
+    x = (300.0 + 0.05 * torch.randn(2, 16, 16, 32, generator=g)).permute(0, 3, 1, 2)
+    ga, be = torch.ones(32), torch.zeros(32)
+    dy = torch.randn(2, 16, 16, 32, generator=g).permute(0, 3, 1, 2)
+    for path in ("auto", "twopass"):
+        if path == "twopass":
+            os.environ["GNB200_FORCE_PATH"] = "twopass"
+        try:
+            out = run_cabi(nt, x, ga, be, dy, 4, 1e-5, "identity")
+        finally:
+            os.environ.pop("GNB200_FORCE_PATH", None)
+        want = O.oracle_c(x, ga, be, dy, 4, 1e-5, "identity")
+        # inputs near 300 carry an fp32 rounding of 3e-5 against a spread of 0.05: allow 1e-3
+        check_against(out, want, torch.float32, scale=100.0)
+
+
+def test_misaligned_pointers_use_the_scalar_path(nt):
+    N, C, sp, G = 2, 24, (5, 7), 3
+    x, ga, be, dy = O.make_inputs(N, C, sp, torch.float16, seed=4)
+    want = O.oracle_c(x, ga, be, dy, G, 1e-5, "silu")
+
+    def shifted(t):  # same values, storage starts 2 bytes past a 16-byte boundary
+        buf = torch.empty(t.numel() + 8, dtype=t.dtype, device="cuda")
+        v = buf[1:1 + t.numel()].view(N, *sp, C)
+        v.copy_(t.cuda().permute(0, 2, 3, 1))
+        assert v.data_ptr() % 16 != 0
+        return v.permute(0, 3, 1, 2)
+
+    out = run_cabi(nt, shifted(x), ga, be, shifted(dy), G, 1e-5, "silu")
+    check_against(out, want, torch.float16)
+
+
+def test_results_are_bitwise_reproducible(nt):
+    for case in (CFG4[0], CFG5[4], CFG3[0]):
+        x, ga, be, dy, G, eps, act, dtype = _case_inputs(case)
+        a = run_cabi(nt, x, ga, be, dy, G, eps, act)
+        b = run_cabi(nt, x, ga, be, dy, G, eps, act)
+        for k in ("y", "dx", "dparam", "mean", "rstd"):
+            assert torch.equal(a[k], b[k]), k
+
+
+def test_output_buffers_are_not_overrun(nt):
+    # canary-padded outputs: nothing outside [0, numel) may be written
+    N, C, sp, G = 3, 40, (17, 33), 8
+    x, ga, be, dy = O.make_inputs(N, C, sp, torch.bfloat16, seed=0, x_dist="uniform3")
+    xf, dyf = _flat(x.cuda()), _flat(dy.cuda())
+    pad = 64
+    for path in ("auto", "twopass"):
+        if path == "twopass":
+            os.environ["GNB200_FORCE_PATH"] = "twopass"
+        try:
+            ybuf = torch.full((xf.numel() + 2 * pad,), 7.0, dtype=x.dtype, device="cuda")
+            y = ybuf[pad:pad + xf.numel()].view(xf.shape)
+            _, mean, rstd = nt.fwd_raw(xf, ga.cuda(), be.cuda(), G, 1e-5, 4, y=y)
+            dbuf = torch.full((xf.numel() + 2 * pad,), 7.0, dtype=x.dtype, device="cuda")
+            dx = dbuf[pad:pad + xf.numel()].view(xf.shape)
+            nt.bwd_raw(dyf, xf, ga.cuda(), be.cuda(), mean, rstd, G, 4, dx=dx)
+            torch.cuda.synchronize()
+        finally:
+            os.environ.pop("GNB200_FORCE_PATH", None)
+        for buf in (ybuf, dbuf):
+            assert (buf[:pad] == 7).all() and (buf[-pad:] == 7).all()
+
+
+# ------------------------------------------------------------------------------------------------
+# the reference-facing Python interface (module + autograd Function + torch ops)
+# ------------------------------------------------------------------------------------------------
+def test_module_forward_backward_matches_oracle(nt):
+    import channels_last_groupnorm_b200 as pkg
+
+    for dt, act in (("float32", "gelu_tanh"), ("float16", "silu"), ("bfloat16", "gelu")):
+        N, C, sp, G = 2, 64, (12, 10), 8
+        x, ga, be, dy = O.make_inputs(N, C, sp, DT[dt], seed=7)
+        m = pkg.GN_NHWC(G, C, activation=act).cuda().to(DT[dt])
+        with torch.no_grad():
+            m.weight.copy_(ga)
+            m.bias.copy_(be)
+        xd = x.cuda().requires_grad_(True)
+        y = m(xd)
+        assert y.shape == x.shape and y.stride() == xd.stride()
+        y.backward(dy.cuda())
+        want = O.oracle_c(x, ga, be, dy, G, 1e-5, act)
+        got = {"y": y.detach(), "dx": xd.grad, "dgamma": m.weight.grad, "dbeta": m.bias.grad}
+        check_against(got, want, DT[dt])
+        assert xd.grad.stride() == xd.stride()
+
+
+def test_module_affine_false_and_state_dict(nt):
+    import channels_last_groupnorm_b200 as pkg
+
+    x, _, _, _ = O.make_inputs(2, 32, (6, 6), torch.float32, seed=8)
+    m = pkg.GN_NHWC(4, 32, affine=False, activation="relu").cuda()
+    y = m(x.cuda())
+    want = O.oracle_c(x, torch.ones(32), torch.zeros(32), None, 4, 1e-5, "relu")
+    assert O.rel_err(y, want["y"]) < 1e-5
+    ref = torch.nn.GroupNorm(4, 32).cuda()
+    m2 = pkg.GN_NHWC(4, 32).cuda()
+    m2.load_state_dict(ref.state_dict())
+    xc = x.cuda()
+    assert O.rel_err(m2(xc), ref(xc.contiguous())) < 1e-5
+
+
+def test_module_rejects_channels_first(nt):
+    import channels_last_groupnorm_b200 as pkg
+
+    m = pkg.GN_NHWC(4, 32).cuda()
+    with pytest.raises(ValueError, match="channels-last"):
+        m(torch.randn(2, 32, 6, 6, device="cuda"))
+
+
+@pytest.mark.parametrize("N,C,R_list", REFERENCE_TRAILING)
+def test_trailing_dims_like_reference(nt, N, C, R_list):
+    """Rank 3..6 inputs with stride(1) == 1, then successive flattening (test/trailing_dims.py:7-33)."""
+    import channels_last_groupnorm_b200 as pkg
+
+    R_list = list(R_list)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn((N, *R_list, C), generator=g).cuda()
+    x = x.permute(0, -1, *range(1, len(R_list) + 1))
+    for dtype in (torch.half, torch.float):
+        m = pkg.GN_NHWC(32, C).cuda().to(dtype)
+        ref = torch.nn.GroupNorm(32, C).cuda().to(dtype)
+        y_ref = ref(x.to(dtype))
+        rl = list(R_list)
+        xx = x
+        while True:
+            y = m(xx.to(dtype))
+            assert torch.nn.functional.mse_loss(y.float(), y_ref.float().view(N, C, *rl)) < 1e-6
+            if len(rl) == 1:
+                break
+            last = rl.pop(-1)
+            rl[-1] *= last
+            xx = xx.reshape(N, C, *rl)
+
+
+def test_pseudo_channels_last_inputs(nt):
+    """x.stride(1) == 1 but inner dims permuted (test/trailing_dims.py:35-63): values must match."""
+    import channels_last_groupnorm_b200 as pkg
+
+    B, C, G = 2, 32, 8
+    for dtype in (torch.half, torch.float):
+        m = pkg.GN_NHWC(G, C).cuda().to(dtype)
+        ref = torch.nn.GroupNorm(G, C).cuda().to(dtype)
+        for inner in ((3, 5), (3, 5, 7), (3, 5, 7, 11)):
+            x = torch.randn((B, *inner, C), device="cuda")
+            x = x.permute(0, -1, *range(len(inner), 0, -1)).to(dtype)
+            assert x.stride(1) == 1
+            assert torch.nn.functional.mse_loss(m(x).float(), ref(x).float()) < 1e-6
+
+
+def test_backward_of_rank3_and_rank5_inputs(nt):
+    import channels_last_groupnorm_b200 as pkg
+
+    for sp in ((20,), (3, 4, 5)):
+        x, ga, be, dy = O.make_inputs(2, 16, sp, torch.float32, seed=9)
+        m = pkg.GN_NHWC(4, 16, activation="silu").cuda()
+        with torch.no_grad():
+            m.weight.copy_(ga)
+            m.bias.copy_(be)
+        xd = x.cuda().requires_grad_(True)
+        m(xd).backward(dy.cuda())
+        want = O.oracle_c(x, ga, be, dy, 4, 1e-5, "silu")
+        check_against({"dx": xd.grad, "dgamma": m.weight.grad, "dbeta": m.bias.grad}, want, torch.float32,
+                      keys=("dx", "dgamma", "dbeta"))
+
+
+def test_torch_op_validation_errors(nt):
+    x = torch.randn(2, 8, 16, device="cuda").permute(0, 2, 1)  # (N, C, R) view of NHWC storage
+    w, b = torch.ones(8, device="cuda"), torch.zeros(8, device="cuda")
+    with pytest.raises(RuntimeError, match="divisible"):
+        torch.ops.gnb200.fwd(x, w, b, 3, 1e-5, 0)
+    with pytest.raises(RuntimeError, match="dtype"):
+        torch.ops.gnb200.fwd(x, w.half(), b, 2, 1e-5, 0)
+    with pytest.raises(RuntimeError, match="channels-last"):
+        torch.ops.gnb200.fwd(torch.randn(2, 16, 8, device="cuda"), torch.ones(16, device="cuda"),
+                             torch.zeros(16, device="cuda"), 2, 1e-5, 0)
+    with pytest.raises(RuntimeError, match="float64|Double|dtype"):
+        torch.ops.gnb200.fwd(x.double(), w.double(), b.double(), 2, 1e-5, 0)
+
+
+# ------------------------------------------------------------------------------------------------
+# against the reference itself
+# ------------------------------------------------------------------------------------------------
+def _golden_files():
+    return sorted(glob.glob(os.path.join(GOLDEN_DIR, "*.pt")))
+
+
+@pytest.mark.parametrize("path", _golden_files(), ids=[os.path.basename(p) for p in _golden_files()])
+def test_against_recorded_reference_outputs(nt, path):
+    g = torch.load(path)
+    meta = g["meta"]
+    dtype = DT[meta["dtype"]]
+    if "x" in g:
+        x, ga, be, dy = g["x"], g["gamma"], g["beta"], g["dy"]
+    else:
+        x, ga, be, dy = O.make_inputs(meta["N"], meta["C"], tuple(meta["spatial"]), dtype, seed=meta["seed"],
+                                      x_dist=meta["x_dist"], x_scale=meta["x_scale"])
+    out = run_cabi(nt, x, ga, be, dy, meta["G"], meta["eps"], meta["act"])
+    idx = g.get("sample_index")
+    # the reference runs with -use_fast_math and 16-bit statistics: its own distance to fp64 is
+    # up to ~1e-4 (fp32) / ~1e-2 (16-bit); allow that on top of our tolerance
+    slack = {"float32": 1e-4, "float16": 2e-2, "bfloat16": 1e-1}[meta["dtype"]]
+    for k in ("y", "dx", "dgamma", "dbeta"):
+        got = out[k]
+        if idx is not None and k in ("y", "dx"):
+            got = got.cpu().flatten()[idx]
+        assert O.rel_err(got, g["ref_" + k]) < slack, k
+
+
+@pytest.mark.skipif(not os.path.exists(REF_LIB), reason="reference extension not built (oracle/build_ref.py)")
+def test_against_live_reference_extension(nt):
+    """Same inputs through the unmodified reference kernels and through ours, on this GPU."""
+    torch.ops.load_library(REF_LIB)
+    for case in (CFG1, CFG2[1], CFG4[0], CFG5[1]):
+        x, ga, be, dy, G, eps, act, dtype = _case_inputs(case)
+        xd, gd, bd, dd = x.cuda(), ga.cuda(), be.cuda(), dy.cuda()
+        x_flat = xd.view(xd.shape[0], xd.shape[1], -1)
+        code = O.ACT_CODES[act]
+        y_r, means, rstds = torch.ops.gnop.fwd(x_flat, gd, bd, G, eps, code)
+        dx_r, dg_r, db_r = torch.ops.gnop.bwd(dd.view(x_flat.shape), x_flat, gd, bd, means, rstds, G, code)
+        ref = {"y": y_r.view(x.shape), "dx": dx_r.view(x.shape), "dgamma": dg_r, "dbeta": db_r}
+        ours = run_cabi(nt, x, ga, be, dy, G, eps, act)
+        want = O.oracle_torch(x, ga, be, dy, G, eps, act)
+        ours_err = check_against(ours, want, dtype)
+        ref_err = {k: O.rel_err(ref[k], want[k]) for k in ours_err}
+        print("\n%s ours %s\n%s ref  %s" % (_id(case), ours_err, " " * len(_id(case)), ref_err))
+        loose = 1e-3 if dtype == torch.float32 else 1e-1
+        assert all(e < loose for e in ref_err.values()), ref_err
