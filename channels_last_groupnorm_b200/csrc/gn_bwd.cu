@@ -1,7 +1,7 @@
 // Backward GroupNorm (+activation) kernels for NHWC tensors, sm_100a.
 //
-// With  xh = (x - mean) * rstd,  yh = gamma * xh + beta,  dyh = dy * act'(yh)  (recomputed in
-// registers, never stored) the per-(sample, channel) sums are
+// With  xh = (x - mean) * rstd,  yh = gamma * xh + beta,  dyh = dy * act'(yh)  the
+// per-(sample, channel) sums are
 //     S1[n,c] = sum_r dyh          S2[n,c] = sum_r dyh * xh
 // and  dbeta_c = sum_n S1,  dgamma_c = sum_n S2,
 //      A[n,g] = sum_{c in g} gamma_c S1 / (D R),   B[n,g] = sum_{c in g} gamma_c S2 / (D R),
@@ -44,111 +44,192 @@ __device__ __forceinline__ void lane_setup(const T* gamma, const T* beta, const 
   }
 }
 
-// Phase 1: accumulate S1, S2 for the thread's channels over its rows; optionally stash x, dy.
+// One row of phase 1: dyh = dy * act'(yh) for the thread's VE channels, sums updated.
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ void bwd_row_sums(const float (&fx)[VE], float (&fd)[VE], const BwdLane<T, VE>& L,
+                                             float (&s1)[VE], float (&s2)[VE]) {
+  constexpr bool FAST = sizeof(T) == 2;
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+    const float yh = fmaf(xh, L.ga[e], L.be[e]);
+    fd[e] *= act_grad<ACT, FAST>(yh);
+    s1[e] += fd[e];
+    s2[e] = fmaf(fd[e], xh, s2[e]);
+  }
+}
+
+// Phase 1 of the multi-kernel path: S1, S2 over the thread's rows straight from global memory.
 template <typename T, int VE, int ACT>
 __device__ __forceinline__ void stream_bwd_sums(const Pack<T, VE>* __restrict__ xs, const Pack<T, VE>* __restrict__ dys,
-                                                size_t row_stride_vec, int nrows, int ty, int TY, Pack<T, VE>* stash_x,
-                                                Pack<T, VE>* stash_dy, int stash_stride_vec, const BwdLane<T, VE>& L,
-                                                float (&s1)[VE], float (&s2)[VE]) {
-  constexpr bool FAST = sizeof(T) == 2;
-  constexpr int U = 2;
-  int r = ty;
-  for (; r + (U - 1) * TY < nrows; r += U * TY) {
+                                                size_t row_stride_vec, int nrows, int ty, int TY,
+                                                const BwdLane<T, VE>& L, float (&s1)[VE], float (&s2)[VE]) {
+  constexpr int U = 4;
+  const size_t step = (size_t)TY * row_stride_vec;
+  const Pack<T, VE>* px = xs + (size_t)ty * row_stride_vec;
+  const Pack<T, VE>* pd = dys + (size_t)ty * row_stride_vec;
+  int left = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
+  for (; left >= U; left -= U) {
     Pack<T, VE> vx[U], vd[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      vx[u] = ld_stream(xs + (size_t)(r + u * TY) * row_stride_vec);
-      vd[u] = ld_stream(dys + (size_t)(r + u * TY) * row_stride_vec);
+      vx[u] = ld_stream(px);
+      vd[u] = ld_stream(pd);
+      px += step;
+      pd += step;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (stash_x) {
-        stash_x[(size_t)(r + u * TY) * stash_stride_vec] = vx[u];
-        stash_dy[(size_t)(r + u * TY) * stash_stride_vec] = vd[u];
-      }
       float fx[VE], fd[VE];
       unpack<T, VE>(vx[u], fx);
       unpack<T, VE>(vd[u], fd);
-#pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
-        const float yh = fmaf(xh, L.ga[e], L.be[e]);
-        const float dyh = fd[e] * act_grad<ACT, FAST>(yh);
-        s1[e] += dyh;
-        s2[e] = fmaf(dyh, xh, s2[e]);
-      }
+      bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
     }
   }
-  for (; r < nrows; r += TY) {
-    const Pack<T, VE> vx = ld_stream(xs + (size_t)r * row_stride_vec);
-    const Pack<T, VE> vd = ld_stream(dys + (size_t)r * row_stride_vec);
-    if (stash_x) {
-      stash_x[(size_t)r * stash_stride_vec] = vx;
-      stash_dy[(size_t)r * stash_stride_vec] = vd;
-    }
+  for (; left > 0; --left) {
     float fx[VE], fd[VE];
-    unpack<T, VE>(vx, fx);
-    unpack<T, VE>(vd, fd);
+    unpack<T, VE>(ld_stream(px), fx);
+    unpack<T, VE>(ld_stream(pd), fd);
+    px += step;
+    pd += step;
+    bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+  }
+}
+
+// Phase 1 of the fused path: x and dy rows are copied into the shared-memory tiles (cp.async, the
+// whole per-thread share in flight up front), consumed as they land, and the dy tile is
+// overwritten in place with dyh = dy * act'(yh) rounded to T, so that phase 2 does not evaluate
+// the activation derivative again.  (For 16-bit T this rounds dyh once more than a recompute
+// would: an error of half a unit in the last place of T on one term of dx.)
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ void stream_bwd_sums_to_tile(const Pack<T, VE>* __restrict__ xs,
+                                                        const Pack<T, VE>* __restrict__ dys, size_t row_stride_vec,
+                                                        int nrows, int ty, int TY, Pack<T, VE>* tile_x_col,
+                                                        Pack<T, VE>* tile_d_col, int tile_stride_vec,
+                                                        const BwdLane<T, VE>& L, float (&s1)[VE], float (&s2)[VE]) {
+  using P = Pack<T, VE>;
+  const int iters = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
+  const size_t gstep = (size_t)TY * row_stride_vec;
+  const int sstep = TY * tile_stride_vec;
+  const P* gx = xs + (size_t)ty * row_stride_vec;
+  const P* gd = dys + (size_t)ty * row_stride_vec;
+  P* wx = tile_x_col + ty * tile_stride_vec;
+  P* wd = tile_d_col + ty * tile_stride_vec;
+  if constexpr (sizeof(P) == 16) {
+    constexpr int kDepth = 8;  // rows (x and dy vector each) in flight per thread
+    const P* rx = wx;
+    P* rd = wd;
+    int issued = 0, done = 0;
 #pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
-      const float yh = fmaf(xh, L.ga[e], L.be[e]);
-      const float dyh = fd[e] * act_grad<ACT, FAST>(yh);
-      s1[e] += dyh;
-      s2[e] = fmaf(dyh, xh, s2[e]);
+    for (int d = 0; d < kDepth; ++d) {
+      if (issued < iters) {
+        cp_async16(wx, gx);
+        cp_async16(wd, gd);
+        wx += sstep;
+        wd += sstep;
+        gx += gstep;
+        gd += gstep;
+        ++issued;
+      }
+      cp_async_commit();
+    }
+    while (done < iters) {
+      cp_async_wait<kDepth - 1>();
+      float fx[VE], fd[VE];
+      unpack<T, VE>(*rx, fx);
+      unpack<T, VE>(*rd, fd);
+      bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+      *rd = pack<T, VE>(fd);
+      rx += sstep;
+      rd += sstep;
+      ++done;
+      if (issued < iters) {
+        cp_async16(wx, gx);
+        cp_async16(wd, gd);
+        wx += sstep;
+        wd += sstep;
+        gx += gstep;
+        gd += gstep;
+        ++issued;
+      }
+      cp_async_commit();
+    }
+    cp_async_wait<0>();
+  } else {
+    for (int i = 0; i < iters; ++i) {
+      const P vx = ld_stream(gx);
+      float fx[VE], fd[VE];
+      unpack<T, VE>(vx, fx);
+      unpack<T, VE>(ld_stream(gd), fd);
+      bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+      *wx = vx;
+      *wd = pack<T, VE>(fd);
+      gx += gstep;
+      gd += gstep;
+      wx += sstep;
+      wd += sstep;
     }
   }
 }
 
-// Phase 2: dx = rstd * (gamma * dyh - A - xh * B); sources may be shared or global memory.
-template <typename T, int VE, int ACT>
+// Phase 2: dx = rstd * (gamma * dyh - A - xh * B) = ag * dyh + (nb * xh + na) with per-lane
+// ag = rstd * gamma, nb = -rstd * B, na = -rstd * A.
+//   kStashed = true : `dys` holds dyh already (fused path);  false: dys holds dy, act' is recomputed.
+template <typename T, int VE, int ACT, bool kStashed>
 __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<T, VE>* dys, size_t src_stride_vec,
                                               Pack<T, VE>* __restrict__ dst, size_t dst_stride_vec, int nrows, int ty,
                                               int TY, const BwdLane<T, VE>& L, const float (&A)[VE],
                                               const float (&B)[VE]) {
   constexpr bool FAST = sizeof(T) == 2;
-  constexpr int U = 2;
-  int r = ty;
-  for (; r + (U - 1) * TY < nrows; r += U * TY) {
+  constexpr int U = 4;
+  float ag[VE], nb[VE], na[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    ag[e] = L.r[e] * L.ga[e];
+    nb[e] = -L.r[e] * B[e];
+    na[e] = -L.r[e] * A[e];
+  }
+  const size_t sstep = (size_t)TY * src_stride_vec, dstep = (size_t)TY * dst_stride_vec;
+  const Pack<T, VE>* px = xs + (size_t)ty * src_stride_vec;
+  const Pack<T, VE>* pd = dys + (size_t)ty * src_stride_vec;
+  Pack<T, VE>* po = dst + (size_t)ty * dst_stride_vec;
+  int left = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
+  while (left > 0) {
+    const int nb_rows = left < U ? left : U;
     Pack<T, VE> vx[U], vd[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      vx[u] = xs[(size_t)(r + u * TY) * src_stride_vec];
-      vd[u] = dys[(size_t)(r + u * TY) * src_stride_vec];
+      if (u < nb_rows) {
+        vx[u] = *px;
+        vd[u] = *pd;
+        px += sstep;
+        pd += sstep;
+      }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      float fx[VE], fd[VE];
-      unpack<T, VE>(vx[u], fx);
-      unpack<T, VE>(vd[u], fd);
+      if (u < nb_rows) {
+        float fx[VE], fd[VE];
+        unpack<T, VE>(vx[u], fx);
+        unpack<T, VE>(vd[u], fd);
 #pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
-        const float yh = fmaf(xh, L.ga[e], L.be[e]);
-        const float dyh = fd[e] * act_grad<ACT, FAST>(yh);
-        fx[e] = L.r[e] * fmaf(L.ga[e], dyh, fmaf(-B[e], xh, -A[e]));
+        for (int e = 0; e < VE; ++e) {
+          const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+          float dyh = fd[e];
+          if constexpr (!kStashed) dyh *= act_grad<ACT, FAST>(fmaf(xh, L.ga[e], L.be[e]));
+          fx[e] = fmaf(ag[e], dyh, fmaf(nb[e], xh, na[e]));
+        }
+        st_stream(po, pack<T, VE>(fx));
+        po += dstep;
       }
-      st_stream(dst + (size_t)(r + u * TY) * dst_stride_vec, pack<T, VE>(fx));
     }
-  }
-  for (; r < nrows; r += TY) {
-    float fx[VE], fd[VE];
-    unpack<T, VE>(xs[(size_t)r * src_stride_vec], fx);
-    unpack<T, VE>(dys[(size_t)r * src_stride_vec], fd);
-#pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
-      const float yh = fmaf(xh, L.ga[e], L.be[e]);
-      const float dyh = fd[e] * act_grad<ACT, FAST>(yh);
-      fx[e] = L.r[e] * fmaf(L.ga[e], dyh, fmaf(-B[e], xh, -A[e]));
-    }
-    st_stream(dst + (size_t)r * dst_stride_vec, pack<T, VE>(fx));
+    left -= nb_rows;
   }
 }
 
 // ------------------------------------------------------------------------------------------------
 // fused kernel.  grid.x = N * ncb * k, cluster (k,1,1).
-// dynamic smem: [x tile][dy tile][red 2*TY*CW][chan 2*CW][slot partial 2*slots][coef 2*slots]
+// dynamic smem: [x tile][dy tile][red 2*TY*CW][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
 // scratch out : sums[(n * C + c) * 2 + {0,1}] = S1, S2 of the whole sample
 // ------------------------------------------------------------------------------------------------
 template <typename T, int VE, int ACT>
@@ -169,7 +250,8 @@ __global__ void __launch_bounds__(kMaxThreads)
   P* tile_x = reinterpret_cast<P*>(smem_raw);
   P* tile_dy = reinterpret_cast<P*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + 2 * tile_bytes);
-  float* chan = red + 2 * g.TY * g.CW;
+  float* part = red + 2 * g.TY * g.CW;
+  float* chan = part + 2 * max((int)blockDim.x, g.CW);
   float* spart = chan + 2 * g.CW;  // [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 over this CTA's rows
   float* coef = spart + 2 * g.slots;  // A[s], B[slots + s]
 
@@ -185,10 +267,10 @@ __global__ void __launch_bounds__(kMaxThreads)
   for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
   if (streaming) {
     lane_setup<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.D, L);
-    stream_bwd_sums<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base),
-                                row_stride_vec, nrows, ty, g.TY, tile_x + tx, tile_dy + tx, g.CV, L, s1, s2);
+    stream_bwd_sums_to_tile<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base),
+                                        row_stride_vec, nrows, ty, g.TY, tile_x + tx, tile_dy + tx, g.CV, L, s1, s2);
   }
-  cta_fold_sums<VE>(g, s1, s2, tx, ty, (ty < g.TY), c0, red, chan);
+  cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
 
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
@@ -246,8 +328,8 @@ __global__ void __launch_bounds__(kMaxThreads)
       A[e] = coef[s];
       B[e] = coef[g.slots + s];
     }
-    stream_bwd_dx<T, VE, ACT>(tile_x + tx, tile_dy + tx, g.CV, reinterpret_cast<P*>(dx + base), row_stride_vec, nrows,
-                              ty, g.TY, L, A, B);
+    stream_bwd_dx<T, VE, ACT, true>(tile_x + tx, tile_dy + tx, g.CV, reinterpret_cast<P*>(dx + base), row_stride_vec,
+                                    nrows, ty, g.TY, L, A, B);
   }
   cluster_wait();
 }
@@ -298,7 +380,8 @@ __global__ void __launch_bounds__(kMaxThreads)
   extern __shared__ uint4 smem_raw[];
   using P = Pack<T, VE>;
   float* red = reinterpret_cast<float*>(smem_raw);
-  float* chan = red + 2 * g.TY * g.CW;
+  float* part = red + 2 * g.TY * g.CW;
+  float* chan = part + 2 * max((int)blockDim.x, g.CW);
   const int tile_id = blockIdx.x;
   const int cb = tile_id % g.ncb;
   const int chunk = (tile_id / g.ncb) % g.chunks;
@@ -318,9 +401,9 @@ __global__ void __launch_bounds__(kMaxThreads)
   if (streaming) {
     lane_setup<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.D, L);
     stream_bwd_sums<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base),
-                                (size_t)g.C / VE, nrows, ty, g.TY, (P*)nullptr, (P*)nullptr, 0, L, s1, s2);
+                                (size_t)g.C / VE, nrows, ty, g.TY, L, s1, s2);
   }
-  cta_fold_sums<VE>(g, s1, s2, tx, ty, (ty < g.TY), c0, red, chan);
+  cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
   const int c_valid = min(g.CW, g.C - c0);
   float2* out = reinterpret_cast<float2*>(tpart) + ((size_t)n * g.chunks + chunk) * g.C + c0;
   for (int c = tid; c < c_valid; c += blockDim.x) out[c] = make_float2(chan[c], chan[g.CW + c]);
@@ -411,8 +494,8 @@ __global__ void __launch_bounds__(kMaxThreads)
   }
   const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
   const size_t rs = (size_t)g.C / VE;
-  stream_bwd_dx<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base), rs,
-                            reinterpret_cast<P*>(dx + base), rs, nrows, ty, g.TY, L, A, B);
+  stream_bwd_dx<T, VE, ACT, false>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base), rs,
+                                   reinterpret_cast<P*>(dx + base), rs, nrows, ty, g.TY, L, A, B);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -432,12 +515,8 @@ static cudaError_t launch_bwd_t(const BwdCall& c, const Plan& p, cudaStream_t st
   if (p.fused) {
     float* sums = reinterpret_cast<float*>(c.workspace);
     auto kern = gn_bwd_fused_kernel<T, VE, ACT>;
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem_bytes);
+    cudaError_t err = ensure_kernel_attributes((const void*)kern, p.smem_bytes, g.k > 8);
     if (err != cudaSuccess) return err;
-    if (g.k > 8) {
-      err = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-      if (err != cudaSuccess) return err;
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid, 1, 1);
     cfg.blockDim = dim3((unsigned)p.threads, 1, 1);
@@ -459,9 +538,11 @@ static cudaError_t launch_bwd_t(const BwdCall& c, const Plan& p, cudaStream_t st
   float* tpart = reinterpret_cast<float*>(c.workspace);
   float* sums = tpart + (size_t)g.N * g.chunks * g.C * 2;
   float* coef = sums + (size_t)g.N * g.C * 2;
+  cudaError_t err = ensure_kernel_attributes((const void*)gn_bwd_reduce_kernel<T, VE, ACT>, p.smem_bytes, false);
+  if (err != cudaSuccess) return err;
   gn_bwd_reduce_kernel<T, VE, ACT><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>(
       (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, tpart, g);
-  cudaError_t err = cudaGetLastError();
+  err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   gn_bwd_finalize_kernel<T><<<(unsigned)(g.N * g.G), dim3(32, 8, 1), 0, stream>>>(tpart, (const T*)c.gamma, sums, coef,
                                                                                  g);

@@ -163,13 +163,24 @@ __device__ __forceinline__ void st_stream(V* p, const V& v) {
     *p = v;
 }
 
+// Asynchronous 16-byte global -> shared copies (no registers held while in flight)
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // Activations and their derivatives, evaluated in fp32.
 //   FAST = false (fp32 tensors): libdevice expf / tanhf / erff, IEEE division -> meets 1e-5.
 //   FAST = true  (16-bit tensors): hardware approximations (tanh.approx, ex2.approx, rcp.approx)
 //                whose error (<= ~5e-4) sits below the rounding of a 16-bit result.
 // Formulas: relu / silu / gelu(erf) / gelu(tanh) and derivatives as in gn_kernel.cu:62-106 of the
-// reference; the fast erf is Abramowitz & Stegun 7.1.26 (|err| <= 1.5e-7).
+// reference.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float tanh_fast(float v) {
   float r;
@@ -187,20 +198,11 @@ __device__ __forceinline__ float rcp_fast(float v) {
   return r;
 }
 
-// erf(v / sqrt(2)) and exp(-v*v/2) from one exponential (fast path)
-__device__ __forceinline__ void erf_exp_fast(float v, float& erf_out, float& gauss_out) {
-  const float z = fabsf(v) * 0.70710678118654752f;
-  const float t = rcp_fast(fmaf(0.3275911f, z, 1.0f));
-  const float e = ex2_fast(v * v * -0.72134752044448170f);  // exp(-v^2/2) = 2^(-v^2/2 * log2 e)
-  float p = fmaf(1.061405429f, t, -1.453152027f);
-  p = fmaf(p, t, 1.421413741f);
-  p = fmaf(p, t, -0.284496736f);
-  p = fmaf(p, t, 0.254829592f);
-  p = p * t;
-  const float r = fmaf(-p, e, 1.0f);
-  erf_out = copysignf(r, v);
-  gauss_out = e;
-}
+// Fast path of the erf-GELU: the normal CDF written as Phi(v) = 0.5 (1 + tanh(u(v))) with
+// u(v) = v (c1 + c3 v^2 + c5 v^4), coefficients from a least-squares fit of Phi and of its
+// derivative on [-8, 8] (max error 2.6e-5 in Phi, 1.1e-4 in Phi'); v^2 is clamped to 64 inside the
+// polynomial, beyond which tanh has saturated.  One MUFU op (tanh.approx) per value.
+constexpr float kPhiC1 = 7.97667873e-01f, kPhiC3 = 3.68576979e-02f, kPhiC5 = -3.17788673e-04f;
 
 template <int ACT, bool FAST>
 __device__ __forceinline__ float act_fwd(float v) {
@@ -217,10 +219,10 @@ __device__ __forceinline__ float act_fwd(float v) {
     }
   } else if constexpr (ACT == kActGelu) {
     if constexpr (FAST) {
-      float er, ga;
-      erf_exp_fast(v, er, ga);
+      const float v2 = fminf(v * v, 64.0f);
+      const float t = tanh_fast(v * fmaf(fmaf(kPhiC5, v2, kPhiC3), v2, kPhiC1));
       const float h = 0.5f * v;
-      return fmaf(h, er, h);
+      return fmaf(h, t, h);
     } else {
       return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
     }
@@ -250,12 +252,14 @@ __device__ __forceinline__ float act_grad(float v) {
       s = 1.0f / (1.0f + expf(-v));
     return s * fmaf(v, 1.0f - s, 1.0f);
   } else if constexpr (ACT == kActGelu) {
-    const float kInvSqrt2Pi = 0.39894228040143268f;
     if constexpr (FAST) {
-      float er, ga;
-      erf_exp_fast(v, er, ga);
-      return fmaf(v * kInvSqrt2Pi, ga, fmaf(0.5f, er, 0.5f));
+      const float v2 = fminf(v * v, 64.0f);
+      const float t = tanh_fast(v * fmaf(fmaf(kPhiC5, v2, kPhiC3), v2, kPhiC1));
+      const float du = fmaf(fmaf(5.0f * kPhiC5, v2, 3.0f * kPhiC3), v2, kPhiC1);
+      // Phi + v * Phi',  Phi' = 0.5 (1 - t^2) u'; beyond |v| = 8 tanh saturates and the second term is 0
+      return fmaf(0.5f * v * du, fmaf(-t, t, 1.0f), fmaf(0.5f, t, 0.5f));
     } else {
+      const float kInvSqrt2Pi = 0.39894228040143268f;
       const float cdf = 0.5f * (1.0f + erff(v * 0.70710678118654752f));
       const float pdf = expf(-0.5f * v * v) * kInvSqrt2Pi;
       return fmaf(v, pdf, cdf);
@@ -332,71 +336,48 @@ __device__ __forceinline__ void cb_groups(const Geom& g, int c0, int& g_lo, int&
 }
 
 // ---------------------------------------------------------------------------------------------
-// CTA-level fold of per-thread running moments into one Moments per touched group.
-//   in : mean[e], m2[e] for the thread's VE channels, cnt = rows the thread consumed
-//   out: slot_out[s] for s < n_slots (shared memory), valid after the trailing __syncthreads()
-// red  : 2 * TY * CW + TY floats of shared scratch,  chan : 3 * CW floats of shared scratch.
-// Every reduction order is fixed by the geometry, so results are run-to-run identical.
+// CTA-level reductions.  Every order of summation is fixed by the launch geometry (no atomics),
+// so results are bit-identical from run to run.
 // ---------------------------------------------------------------------------------------------
+
+// Sum of one value per (row lane, channel) over the CTA tile, per group slot of the column block.
+//   val[e]  : the thread's contribution for its VE channels (must be 0 for threads that did not stream)
+//   red     : TY * CW floats of shared scratch;  out[s], s < n_slots : shared, valid on return
 template <int VE>
-__device__ __forceinline__ void cta_fold_moments(const Geom& g, const float (&mean)[VE], const float (&m2)[VE],
-                                                 float cnt, int tx, int ty, bool streaming, int c0, float* red,
-                                                 float* chan, float* slot_out /* 3 floats per slot */) {
+__device__ __forceinline__ void cta_group_sum(const Geom& g, const float (&val)[VE], int tx, int ty, int c0, int g_lo,
+                                              int n_slots, float* red, float* out) {
   const int CW = g.CW, TY = g.TY;
-  float* red_mean = red;
-  float* red_m2 = red + TY * CW;
-  float* red_cnt = red + 2 * TY * CW;
-  if (streaming) {
+  if (ty < TY) {
 #pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      red_mean[ty * CW + tx * VE + e] = mean[e];
-      red_m2[ty * CW + tx * VE + e] = m2[e];
-    }
-    if (tx == 0) red_cnt[ty] = cnt;
+    for (int e = 0; e < VE; ++e) red[ty * CW + tx * VE + e] = val[e];
   }
   __syncthreads();
   const int c_valid = min(CW, g.C - c0);
-  for (int c = threadIdx.x; c < c_valid; c += blockDim.x) {
-    Moments acc = {0.f, 0.f, 0.f};
-    for (int j = 0; j < TY; ++j) {
-      Moments o = {red_mean[j * CW + c], red_m2[j * CW + c], red_cnt[j]};
-      acc = moments_merge(acc, o);
-    }
-    chan[c] = acc.mean;
-    chan[CW + c] = acc.m2;
-    chan[2 * CW + c] = acc.n;
-  }
-  __syncthreads();
-  int g_lo, n_slots;
-  cb_groups(g, c0, g_lo, n_slots);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
   for (int s = warp; s < n_slots; s += nwarps) {
     const int lo = max((g_lo + s) * g.D, c0) - c0;
     const int hi = min((g_lo + s + 1) * g.D, c0 + c_valid) - c0;
-    Moments acc = {0.f, 0.f, 0.f};
-    for (int c = lo + lane; c < hi; c += 32) {
-      Moments o = {chan[c], chan[CW + c], chan[2 * CW + c]};
-      acc = moments_merge(acc, o);
+    const int w = hi - lo;
+    float acc = 0.f;
+    for (int i = lane; i < TY * w; i += 32) {
+      const int j = i / w;
+      acc += red[j * CW + lo + (i - j * w)];
     }
-    acc = moments_warp_reduce(acc);
-    if (lane == 0) {
-      slot_out[3 * s + 0] = acc.mean;
-      slot_out[3 * s + 1] = acc.m2;
-      slot_out[3 * s + 2] = acc.n;
-    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[s] = acc;
   }
   __syncthreads();
 }
 
-// CTA-level fold of two per-channel running sums (backward): per-thread s1[e], s2[e] ->
-// chan[c] = sum over row lanes of s1, chan[CW + c] = same for s2.  red: 2 * TY * CW floats.
+// Per-channel sums over the row lanes of two values (backward): chan[c] = sum_ty s1, chan[CW + c]
+// = sum_ty s2.  red: 2 * TY * CW floats, part: 2 * J * CW floats with J = max(1, blockDim / CW).
 template <int VE>
-__device__ __forceinline__ void cta_fold_sums(const Geom& g, const float (&s1)[VE], const float (&s2)[VE], int tx,
-                                              int ty, bool streaming, int c0, float* red, float* chan) {
+__device__ __forceinline__ void cta_channel_sums(const Geom& g, const float (&s1)[VE], const float (&s2)[VE], int tx,
+                                                 int ty, int c0, float* red, float* part, float* chan) {
   const int CW = g.CW, TY = g.TY;
   float* red1 = red;
   float* red2 = red + TY * CW;
-  if (streaming) {
+  if (ty < TY) {
 #pragma unroll
     for (int e = 0; e < VE; ++e) {
       red1[ty * CW + tx * VE + e] = s1[e];
@@ -404,22 +385,32 @@ __device__ __forceinline__ void cta_fold_sums(const Geom& g, const float (&s1)[V
     }
   }
   __syncthreads();
-  const int c_valid = min(CW, g.C - c0);
-  for (int c = threadIdx.x; c < c_valid; c += blockDim.x) {
+  const int J = max(1, (int)blockDim.x / CW);  // row-lane slices summed in parallel
+  {
+    const int j = threadIdx.x / CW;
+    if (j < J) {
+      for (int c = threadIdx.x - j * CW; c < CW; c += blockDim.x) {  // one pass unless CW > blockDim
+        float a1 = 0.f, a2 = 0.f;
+        for (int r = j; r < TY; r += J) {
+          a1 += red1[r * CW + c];
+          a2 += red2[r * CW + c];
+        }
+        part[j * CW + c] = a1;
+        part[(J + j) * CW + c] = a2;
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < CW; c += blockDim.x) {
     float a1 = 0.f, a2 = 0.f;
-    for (int j = 0; j < TY; ++j) {
-      a1 += red1[j * CW + c];
-      a2 += red2[j * CW + c];
+    for (int j = 0; j < J; ++j) {
+      a1 += part[j * CW + c];
+      a2 += part[(J + j) * CW + c];
     }
     chan[c] = a1;
     chan[CW + c] = a2;
   }
   __syncthreads();
-}
-
-// Shared-memory floats needed by the folds above for a geometry.
-__host__ __device__ inline size_t fold_scratch_floats(int CW, int TY, int slots) {
-  return (size_t)2 * TY * CW + TY + (size_t)3 * CW + (size_t)5 * slots + 8;
 }
 
 }  // namespace gnb200

@@ -19,45 +19,114 @@
 
 namespace gnb200 {
 
-// Per-thread running moments over the rows this thread owns.  `stash`, when not null, receives a
-// copy of every vector (the shared-memory tile of the fused kernel).
+template <int VE>
+__device__ __forceinline__ void welford_step(const float (&f)[VE], float (&mean)[VE], float (&m2)[VE], float& cnt) {
+  cnt += 1.0f;
+  const float inv = __fdividef(1.0f, cnt);
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    const float d = f[e] - mean[e];
+    mean[e] = fmaf(d, inv, mean[e]);
+    m2[e] = fmaf(d, f[e] - mean[e], m2[e]);
+  }
+}
+
+// Per-thread running moments over the rows this thread owns (rows ty, ty + TY, ...), read straight
+// from global memory with U independent 16-byte loads in flight (multi-kernel path).
 template <typename T, int VE>
 __device__ __forceinline__ void stream_moments(const Pack<T, VE>* __restrict__ src, size_t row_stride_vec, int nrows,
-                                               int ty, int TY, Pack<T, VE>* stash, int stash_stride_vec,
-                                               float (&mean)[VE], float (&m2)[VE], float& cnt) {
-  constexpr int U = 4;
-  int r = ty;
-  for (; r + (U - 1) * TY < nrows; r += U * TY) {
+                                               int ty, int TY, float (&mean)[VE], float (&m2)[VE], float& cnt) {
+  constexpr int U = 8;
+  const size_t step = (size_t)TY * row_stride_vec;
+  const Pack<T, VE>* p = src + (size_t)ty * row_stride_vec;
+  int left = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
+  for (; left >= U; left -= U) {
     Pack<T, VE> v[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) v[u] = ld_stream(src + (size_t)(r + u * TY) * row_stride_vec);
+    for (int u = 0; u < U; ++u) {
+      v[u] = ld_stream(p);
+      p += step;
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (stash) stash[(size_t)(r + u * TY) * stash_stride_vec] = v[u];
       float f[VE];
       unpack<T, VE>(v[u], f);
-      cnt += 1.0f;
-      const float inv = __frcp_rn(cnt);
-#pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        const float d = f[e] - mean[e];
-        mean[e] = fmaf(d, inv, mean[e]);
-        m2[e] = fmaf(d, f[e] - mean[e], m2[e]);
-      }
+      welford_step<VE>(f, mean, m2, cnt);
     }
   }
-  for (; r < nrows; r += TY) {
-    const Pack<T, VE> v = ld_stream(src + (size_t)r * row_stride_vec);
-    if (stash) stash[(size_t)r * stash_stride_vec] = v;
+  for (; left > 0; --left) {
     float f[VE];
-    unpack<T, VE>(v, f);
-    cnt += 1.0f;
-    const float inv = __frcp_rn(cnt);
+    unpack<T, VE>(ld_stream(p), f);
+    p += step;
+    welford_step<VE>(f, mean, m2, cnt);
+  }
+}
+
+// Same, but the rows are first brought into the shared-memory tile (fused path) and consumed from
+// there.  16-byte vectors travel with cp.async: the whole per-thread share of the tile is put in
+// flight up front (kDepth groups of kGroup rows) and consumed group by group as it lands; every
+// thread reads back only what it copied itself, so no block barrier is needed.
+template <typename T, int VE>
+__device__ __forceinline__ void stream_moments_to_tile(const Pack<T, VE>* __restrict__ src, size_t row_stride_vec,
+                                                       int nrows, int ty, int TY, Pack<T, VE>* tile_col,
+                                                       int tile_stride_vec, float (&mean)[VE], float (&m2)[VE],
+                                                       float& cnt) {
+  using P = Pack<T, VE>;
+  const int iters = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
+  const size_t gstep = (size_t)TY * row_stride_vec;
+  const int sstep = TY * tile_stride_vec;
+  const P* gp = src + (size_t)ty * row_stride_vec;
+  P* sp_w = tile_col + ty * tile_stride_vec;
+  if constexpr (sizeof(P) == 16) {
+    constexpr int kGroup = 2, kDepth = 8;
+    const P* sp_r = sp_w;
+    int issued = 0, done = 0;
 #pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const float d = f[e] - mean[e];
-      mean[e] = fmaf(d, inv, mean[e]);
-      m2[e] = fmaf(d, f[e] - mean[e], m2[e]);
+    for (int d = 0; d < kDepth; ++d) {
+#pragma unroll
+      for (int j = 0; j < kGroup; ++j) {
+        if (issued < iters) {
+          cp_async16(sp_w, gp);
+          sp_w += sstep;
+          gp += gstep;
+          ++issued;
+        }
+      }
+      cp_async_commit();
+    }
+    while (done < iters) {
+      cp_async_wait<kDepth - 1>();
+#pragma unroll
+      for (int j = 0; j < kGroup; ++j) {
+        if (done < iters) {
+          float f[VE];
+          unpack<T, VE>(*sp_r, f);
+          sp_r += sstep;
+          welford_step<VE>(f, mean, m2, cnt);
+          ++done;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kGroup; ++j) {
+        if (issued < iters) {
+          cp_async16(sp_w, gp);
+          sp_w += sstep;
+          gp += gstep;
+          ++issued;
+        }
+      }
+      cp_async_commit();
+    }
+    cp_async_wait<0>();
+  } else {
+    for (int i = 0; i < iters; ++i) {
+      const P v = ld_stream(gp);
+      *sp_w = v;
+      gp += gstep;
+      sp_w += sstep;
+      float f[VE];
+      unpack<T, VE>(v, f);
+      welford_step<VE>(f, mean, m2, cnt);
     }
   }
 }
@@ -69,26 +138,35 @@ __device__ __forceinline__ void stream_apply(const Pack<T, VE>* src, size_t src_
                                              const float (&b)[VE]) {
   constexpr bool FAST = sizeof(T) == 2;
   constexpr int U = 4;
-  int r = ty;
-  for (; r + (U - 1) * TY < nrows; r += U * TY) {
+  const size_t sstep = (size_t)TY * src_stride_vec, dstep = (size_t)TY * dst_stride_vec;
+  const Pack<T, VE>* sp = src + (size_t)ty * src_stride_vec;
+  Pack<T, VE>* dp = dst + (size_t)ty * dst_stride_vec;
+  int left = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
+  for (; left >= U; left -= U) {
     Pack<T, VE> v[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) v[u] = src[(size_t)(r + u * TY) * src_stride_vec];
+    for (int u = 0; u < U; ++u) {
+      v[u] = *sp;
+      sp += sstep;
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       float f[VE];
       unpack<T, VE>(v[u], f);
 #pragma unroll
       for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
-      st_stream(dst + (size_t)(r + u * TY) * dst_stride_vec, pack<T, VE>(f));
+      st_stream(dp, pack<T, VE>(f));
+      dp += dstep;
     }
   }
-  for (; r < nrows; r += TY) {
+  for (; left > 0; --left) {
     float f[VE];
-    unpack<T, VE>(src[(size_t)r * src_stride_vec], f);
+    unpack<T, VE>(*sp, f);
+    sp += sstep;
 #pragma unroll
     for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
-    st_stream(dst + (size_t)r * dst_stride_vec, pack<T, VE>(f));
+    st_stream(dp, pack<T, VE>(f));
+    dp += dstep;
   }
 }
 
@@ -108,9 +186,38 @@ __device__ __forceinline__ void lane_affine(const T* gamma, const T* beta, const
   }
 }
 
+// CTA-local moments of every group slot of the column block from the per-thread Welford states:
+// first the slot means (sum of cnt * mean / n), then the squared deviations around them.
+//   slot[s]            = local mean      slot[slots + s] = local M2      slot[2 * slots + s] = local count
+// scratch: red (TY * CW floats), tmp (slots floats).
+template <int VE>
+__device__ __forceinline__ void cta_slot_moments(const Geom& g, const float (&mean)[VE], const float (&m2)[VE],
+                                                 float cnt, int tx, int ty, int c0, int nrows, int g_lo, int n_slots,
+                                                 float* red, float* tmp, float* slot) {
+  float val[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) val[e] = cnt * mean[e];
+  cta_group_sum<VE>(g, val, tx, ty, c0, g_lo, n_slots, red, tmp);
+  const int c_end = min(c0 + g.CW, g.C);
+  for (int s = threadIdx.x; s < n_slots; s += blockDim.x) {
+    const int w = min((g_lo + s + 1) * g.D, c_end) - max((g_lo + s) * g.D, c0);
+    const float n_loc = (float)nrows * (float)w;
+    slot[s] = n_loc > 0.f ? tmp[s] / n_loc : 0.f;
+    slot[2 * g.slots + s] = n_loc;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    const int c = min(c0 + tx * VE + e, g.C - 1);
+    const float d = mean[e] - slot[c / g.D - g_lo];
+    val[e] = fmaf(cnt * d, d, m2[e]);
+  }
+  cta_group_sum<VE>(g, val, tx, ty, c0, g_lo, n_slots, red, slot + g.slots);
+}
+
 // ------------------------------------------------------------------------------------------------
 // fused one-pass kernel.  grid.x = N * ncb * k, cluster = (k,1,1).
-// dynamic smem: [tile rows_per_cta * CV packs][fold scratch]
+// dynamic smem: [tile rows_per_cta * CV packs][red TY*CW][tmp slots][slot 3*slots][stat 2*slots]
 // ------------------------------------------------------------------------------------------------
 template <typename T, int VE, int ACT>
 __global__ void __launch_bounds__(kMaxThreads)
@@ -128,11 +235,10 @@ __global__ void __launch_bounds__(kMaxThreads)
 
   P* tile = reinterpret_cast<P*>(smem_raw);
   const size_t tile_bytes = ((size_t)g.rows_per_cta * g.CV * sizeof(P) + 15) & ~(size_t)15;
-  float* fold = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
-  float* red = fold;
-  float* chan = red + 2 * g.TY * g.CW + g.TY;
-  float* part = chan + 3 * g.CW;          // 3 floats per slot: this CTA's partial moments
-  float* stat = part + 3 * g.slots;       // mean[slots], rstd[slots]
+  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
+  float* tmp = red + g.TY * g.CW;
+  float* slot = tmp + g.slots;        // local mean | local M2 | local count
+  float* stat = slot + 3 * g.slots;   // mean[slots], rstd[slots]
 
   const int tid = threadIdx.x;
   const int tx = tid % g.CV, ty = tid / g.CV;
@@ -144,27 +250,33 @@ __global__ void __launch_bounds__(kMaxThreads)
   for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
   const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
   if (streaming)
-    stream_moments<T, VE>(reinterpret_cast<const P*>(x + base), row_stride_vec, nrows, ty, g.TY, tile + tx, g.CV, mean,
-                          m2, cnt);
-  cta_fold_moments<VE>(g, mean, m2, cnt, tx, ty, (ty < g.TY), c0, red, chan, part);
-
-  // combine the k partials (rank order -> every CTA of the cluster gets bit-identical statistics)
-  cluster_sync_all();
+    stream_moments_to_tile<T, VE>(reinterpret_cast<const P*>(x + base), row_stride_vec, nrows, ty, g.TY, tile + tx,
+                                  g.CV, mean, m2, cnt);
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
+  cta_slot_moments<VE>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
+
+  // combine the k CTA-local moments (rank order -> every CTA of the cluster gets bit-identical
+  // statistics):  mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2
+  cluster_sync_all();
   for (int s = tid; s < n_slots; s += blockDim.x) {
-    Moments acc = {0.f, 0.f, 0.f};
+    float wsum = 0.f, ntot = 0.f;
     for (unsigned q = 0; q < k; ++q) {
-      Moments o = {dsmem_ld_f32(part + 3 * s + 0, q), dsmem_ld_f32(part + 3 * s + 1, q),
-                   dsmem_ld_f32(part + 3 * s + 2, q)};
-      acc = moments_merge(acc, o);
+      const float nq = dsmem_ld_f32(slot + 2 * g.slots + s, q);
+      wsum = fmaf(nq, dsmem_ld_f32(slot + s, q), wsum);
+      ntot += nq;
     }
-    const float var = fmaxf(acc.m2 / acc.n, 0.f);
-    const float rs = rsqrtf(var + eps);
-    stat[s] = acc.mean;
+    const float mu = wsum / ntot;
+    float m2tot = 0.f;
+    for (unsigned q = 0; q < k; ++q) {
+      const float d = dsmem_ld_f32(slot + s, q) - mu;
+      m2tot += fmaf(dsmem_ld_f32(slot + 2 * g.slots + s, q) * d, d, dsmem_ld_f32(slot + g.slots + s, q));
+    }
+    const float rs = rsqrtf(fmaxf(m2tot / ntot, 0.f) + eps);
+    stat[s] = mu;
     stat[g.slots + s] = rs;
     if (rank == 0) {
-      mean_out[(size_t)n * g.G + g_lo + s] = acc.mean;
+      mean_out[(size_t)n * g.G + g_lo + s] = mu;
       rstd_out[(size_t)n * g.G + g_lo + s] = rs;
     }
   }
@@ -176,12 +288,12 @@ __global__ void __launch_bounds__(kMaxThreads)
     lane_affine<T, VE>(gamma, beta, stat, stat + g.slots, g_lo, c0 + tx * VE, g.D, a, b);
     stream_apply<T, VE, ACT>(tile + tx, g.CV, reinterpret_cast<P*>(y + base), row_stride_vec, nrows, ty, g.TY, a, b);
   }
-  cluster_wait();  // do not exit (and release shared memory) while a peer may still read `part`
+  cluster_wait();  // do not exit (and release shared memory) while a peer may still read `slot`
 }
 
 // ------------------------------------------------------------------------------------------------
-// two-pass, kernel 1: partial moments per CTA tile.  grid.x = N * chunks * ncb.
-// scratch layout: wpart[((n * chunks + chunk) * ncb + cb) * slots + s] = {mean, m2, n}
+// two-pass, kernel 1: CTA-local moments per tile.  grid.x = N * chunks * ncb.
+// scratch layout: wpart[(((n * chunks + chunk) * ncb + cb) * slots + s) * 3] = {mean, M2, count}
 // ------------------------------------------------------------------------------------------------
 template <typename T, int VE>
 __global__ void __launch_bounds__(kMaxThreads)
@@ -189,8 +301,8 @@ __global__ void __launch_bounds__(kMaxThreads)
   extern __shared__ uint4 smem_raw[];
   using P = Pack<T, VE>;
   float* red = reinterpret_cast<float*>(smem_raw);
-  float* chan = red + 2 * g.TY * g.CW + g.TY;
-  float* part = chan + 3 * g.CW;
+  float* tmp = red + g.TY * g.CW;
+  float* slot = tmp + g.slots;
 
   const int tile_id = blockIdx.x;
   const int cb = tile_id % g.ncb;
@@ -208,16 +320,20 @@ __global__ void __launch_bounds__(kMaxThreads)
   for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
   const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
   if (streaming)
-    stream_moments<T, VE>(reinterpret_cast<const P*>(x + base), (size_t)g.C / VE, nrows, ty, g.TY, (P*)nullptr, 0, mean,
-                          m2, cnt);
-  cta_fold_moments<VE>(g, mean, m2, cnt, tx, ty, (ty < g.TY), c0, red, chan, part);
+    stream_moments<T, VE>(reinterpret_cast<const P*>(x + base), (size_t)g.C / VE, nrows, ty, g.TY, mean, m2, cnt);
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
+  cta_slot_moments<VE>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
   float* out = wpart + (size_t)tile_id * g.slots * 3;
-  for (int i = tid; i < 3 * n_slots; i += blockDim.x) out[i] = part[i];
+  for (int s = tid; s < n_slots; s += blockDim.x) {
+    out[3 * s + 0] = slot[s];
+    out[3 * s + 1] = slot[g.slots + s];
+    out[3 * s + 2] = slot[2 * g.slots + s];
+  }
 }
 
-// two-pass, kernel 2: one warp per (n, group) merges all partials that cover the group.
+// two-pass, kernel 2: one warp per (n, group) merges all partials that cover the group, in two
+// sweeps (mean first, then squared deviations around it); lane order and tree are fixed.
 __global__ void gn_fwd_finalize_kernel(const float* __restrict__ wpart, float* __restrict__ mean_out,
                                        float* __restrict__ rstd_out, float eps, const Geom g) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -225,19 +341,29 @@ __global__ void gn_fwd_finalize_kernel(const float* __restrict__ wpart, float* _
   const int n = warp / g.G, grp = warp - n * g.G;
   const int cb_lo = (grp * g.D) / g.CW, cb_hi = ((grp + 1) * g.D - 1) / g.CW;
   const int ncov = cb_hi - cb_lo + 1;
-  Moments acc = {0.f, 0.f, 0.f};
+  float wsum = 0.f, ntot = 0.f;
   for (int i = lane; i < ncov * g.chunks; i += 32) {
     const int cb = cb_lo + i % ncov, chunk = i / ncov;
     const int s = grp - (cb * g.CW) / g.D;
     const float* p = wpart + ((((size_t)n * g.chunks + chunk) * g.ncb + cb) * g.slots + s) * 3;
-    Moments o = {p[0], p[1], p[2]};
-    acc = moments_merge(acc, o);
+    wsum = fmaf(p[2], p[0], wsum);
+    ntot += p[2];
   }
-  acc = moments_warp_reduce(acc);
+  wsum = __shfl_sync(0xffffffffu, warp_sum(wsum), 0);
+  ntot = __shfl_sync(0xffffffffu, warp_sum(ntot), 0);
+  const float mu = wsum / ntot;
+  float m2 = 0.f;
+  for (int i = lane; i < ncov * g.chunks; i += 32) {
+    const int cb = cb_lo + i % ncov, chunk = i / ncov;
+    const int s = grp - (cb * g.CW) / g.D;
+    const float* p = wpart + ((((size_t)n * g.chunks + chunk) * g.ncb + cb) * g.slots + s) * 3;
+    const float d = p[0] - mu;
+    m2 += fmaf(p[2] * d, d, p[1]);
+  }
+  m2 = warp_sum(m2);
   if (lane == 0) {
-    const float var = fmaxf(acc.m2 / acc.n, 0.f);
-    mean_out[warp] = acc.mean;
-    rstd_out[warp] = rsqrtf(var + eps);
+    mean_out[warp] = mu;
+    rstd_out[warp] = rsqrtf(fmaxf(m2 / ntot, 0.f) + eps);
   }
 }
 
@@ -273,12 +399,8 @@ __global__ void __launch_bounds__(kMaxThreads)
 template <typename T, int VE, int ACT>
 static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t stream) {
   auto kern = gn_fwd_fused_kernel<T, VE, ACT>;
-  cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem_bytes);
+  cudaError_t err = ensure_kernel_attributes((const void*)kern, p.smem_bytes, p.geom.k > 8);
   if (err != cudaSuccess) return err;
-  if (p.geom.k > 8) {
-    err = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    if (err != cudaSuccess) return err;
-  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)p.grid, 1, 1);
   cfg.blockDim = dim3((unsigned)p.threads, 1, 1);
@@ -298,8 +420,10 @@ static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t st
 template <typename T, int VE, int ACT>
 static cudaError_t launch_two_pass(const FwdCall& c, const Plan& p, cudaStream_t stream) {
   float* wpart = reinterpret_cast<float*>(c.workspace);
+  cudaError_t err = ensure_kernel_attributes((const void*)gn_fwd_stats_kernel<T, VE>, p.smem_bytes, false);
+  if (err != cudaSuccess) return err;
   gn_fwd_stats_kernel<T, VE><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>((const T*)c.x, wpart, p.geom);
-  cudaError_t err = cudaGetLastError();
+  err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   const int warps = p.geom.N * p.geom.G;
   const int fin_threads = 128;

@@ -55,6 +55,10 @@ bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direct
 // Largest scratch requirement over the plans the library may pick for this problem.
 size_t plan_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction);
 
+// Raises a kernel's dynamic shared-memory limit (and allows a non-portable cluster size) once per
+// device and kernel; later calls with a request that is already covered cost one map lookup.
+cudaError_t ensure_kernel_attributes(const void* func, size_t smem_bytes, bool nonportable_cluster);
+
 cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream);
 cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream);
 

@@ -12,6 +12,10 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "gn_kernels.h"
 
 namespace gnb200 {
@@ -38,8 +42,14 @@ int env_int(const char* name, int fallback) {
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-size_t fwd_fold_floats(int CW, int TY, int slots) { return (size_t)2 * TY * CW + TY + (size_t)3 * CW + (size_t)5 * slots + 8; }
-size_t bwd_fold_floats(int CW, int TY, int slots) { return (size_t)2 * TY * CW + (size_t)2 * CW + (size_t)4 * slots + 8; }
+// shared-memory floats of the CTA reductions (layouts in gn_fwd.cu / gn_bwd.cu)
+size_t fwd_fold_floats(int CW, int TY, int slots, int threads) {
+  (void)threads;
+  return (size_t)TY * CW + (size_t)6 * slots + 8;
+}
+size_t bwd_fold_floats(int CW, int TY, int slots, int threads) {
+  return (size_t)2 * TY * CW + (size_t)2 * (threads > CW ? threads : CW) + (size_t)2 * CW + (size_t)4 * slots + 8;
+}
 
 struct Shape {
   int N, R, C, G, D, s, ve;
@@ -72,7 +82,7 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, Plan* out, double* sco
   int TY, threads;
   thread_layout(CV, rows, target_threads, &TY, &threads);
   const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15) * ntiles;
-  const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots) : bwd_fold_floats(cw, TY, slots)) * 4;
+  const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots, threads) : bwd_fold_floats(cw, TY, slots, threads)) * 4;
   if (tile + fold > kSmemMaxOptin - 1024) return false;
 
   Plan p = {};
@@ -167,11 +177,11 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
   p.grid = (long long)sh.N * chunks * ncb;
   if (p.grid > 0x7fffffffLL) return false;
   if (sh.direction == 0) {
-    p.smem_bytes = fwd_fold_floats(cw, TY, slots) * 4;
+    p.smem_bytes = fwd_fold_floats(cw, TY, slots, threads) * 4;
     p.ws_bytes = (size_t)p.grid * slots * 3 * sizeof(float);
     p.launches = 3;
   } else {
-    p.smem_bytes = bwd_fold_floats(cw, TY, slots) * 4;
+    p.smem_bytes = bwd_fold_floats(cw, TY, slots, threads) * 4;
     p.ws_bytes = ((size_t)sh.N * chunks * sh.C * 2 + (size_t)sh.N * sh.C * 2 + (size_t)sh.N * sh.G * 2) * sizeof(float);
     p.launches = 4;
   }
@@ -200,6 +210,27 @@ bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direct
   const bool want_fused = !(force && !strcmp(force, "twopass"));
   if (want_fused && plan_fused(sh, plan)) return true;
   return plan_two_pass(sh, plan);
+}
+
+cudaError_t ensure_kernel_attributes(const void* func, size_t smem_bytes, bool nonportable_cluster) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, std::pair<size_t, bool>> done;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  std::lock_guard<std::mutex> lock(mu);
+  auto& st = done[std::make_pair(dev, func)];
+  if (smem_bytes > 48 * 1024 && smem_bytes > st.first) {
+    err = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMaxOptin);
+    if (err != cudaSuccess) return err;
+    st.first = kSmemMaxOptin;
+  }
+  if (nonportable_cluster && !st.second) {
+    err = cudaFuncSetAttribute(func, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (err != cudaSuccess) return err;
+    st.second = true;
+  }
+  return cudaSuccess;
 }
 
 size_t plan_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction) {

@@ -60,7 +60,7 @@ def main():
         rec = {
             "meta": {"N": N, "C": C, "spatial": list(sp), "G": G, "eps": eps, "act": act, "dtype": dt,
                      "seed": 0, "x_dist": dist, "x_scale": scale, "gpu": torch.cuda.get_device_name(0),
-                     "torch": torch.__version__},
+                     "torch": str(torch.__version__)},
             "x": x.clone(), "gamma": ga.clone(), "beta": be.clone(), "dy": dy.clone(),
             "ref_dgamma": dgamma.cpu(), "ref_dbeta": dbeta.cpu(),
         }

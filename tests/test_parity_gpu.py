@@ -327,15 +327,14 @@ def test_backward_of_rank3_and_rank5_inputs(nt):
 
 
 def test_torch_op_validation_errors(nt):
-    x = torch.randn(2, 8, 16, device="cuda").permute(0, 2, 1)  # (N, C, R) view of NHWC storage
+    x = torch.randn(2, 16, 8, device="cuda").permute(0, 2, 1)  # (N=2, C=8, R=16) view of NHWC storage
     w, b = torch.ones(8, device="cuda"), torch.zeros(8, device="cuda")
     with pytest.raises(RuntimeError, match="divisible"):
         torch.ops.gnb200.fwd(x, w, b, 3, 1e-5, 0)
     with pytest.raises(RuntimeError, match="dtype"):
         torch.ops.gnb200.fwd(x, w.half(), b, 2, 1e-5, 0)
     with pytest.raises(RuntimeError, match="channels-last"):
-        torch.ops.gnb200.fwd(torch.randn(2, 16, 8, device="cuda"), torch.ones(16, device="cuda"),
-                             torch.zeros(16, device="cuda"), 2, 1e-5, 0)
+        torch.ops.gnb200.fwd(torch.randn(2, 8, 16, device="cuda"), w, b, 2, 1e-5, 0)
     with pytest.raises(RuntimeError, match="float64|Double|dtype"):
         torch.ops.gnb200.fwd(x.double(), w.double(), b.double(), 2, 1e-5, 0)
 
