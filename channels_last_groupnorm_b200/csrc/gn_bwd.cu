@@ -29,18 +29,30 @@ struct BwdLane {
   float be[VE];   // beta
 };
 
-template <typename T, int VE>
+// UNI: all VE channels of the thread belong to one group (one statistics lookup; the compiler
+// then keeps a single register for each of r / nmr).
+template <typename T, int VE, bool UNI>
 __device__ __forceinline__ void lane_setup(const T* gamma, const T* beta, const float* mean_n, const float* rstd_n,
-                                           int c_first, int D, BwdLane<T, VE>& L) {
-#pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    const int c = c_first + e;
-    const int grp = c / D;
+                                           int c_first, const FastDiv div_D, BwdLane<T, VE>& L) {
+  load_params<T, VE>(gamma, c_first, L.ga);
+  load_params<T, VE>(beta, c_first, L.be);
+  if constexpr (UNI) {
+    const int grp = div_D.div(c_first);
     const float rs = rstd_n[grp];
-    L.r[e] = rs;
-    L.nmr[e] = -mean_n[grp] * rs;
-    L.ga[e] = load_param<T>(gamma, c);
-    L.be[e] = load_param<T>(beta, c);
+    const float nm = -mean_n[grp] * rs;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      L.r[e] = rs;
+      L.nmr[e] = nm;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const int grp = div_D.div(c_first + e);
+      const float rs = rstd_n[grp];
+      L.r[e] = rs;
+      L.nmr[e] = -mean_n[grp] * rs;
+    }
   }
 }
 
@@ -96,83 +108,125 @@ __device__ __forceinline__ void stream_bwd_sums(const Pack<T, VE>* __restrict__ 
   }
 }
 
-// Phase 1 of the fused path: x and dy rows are copied into the shared-memory tiles (cp.async, the
-// whole per-thread share in flight up front), consumed as they land, and the dy tile is
-// overwritten in place with dyh = dy * act'(yh) rounded to T, so that phase 2 does not evaluate
-// the activation derivative again.  (For 16-bit T this rounds dyh once more than a recompute
-// would: an error of half a unit in the last place of T on one term of dx.)
+// Phase 1 of the fused path: the thread's x and dy rows are copied into the shared-memory tiles
+// with cp.async (all put in flight up front, four commit groups), consumed as they land, and the
+// dy tile is overwritten in place with dyh = dy * act'(yh) rounded to T, so that phase 2 does not
+// evaluate the activation derivative again.  (For 16-bit T this rounds dyh once more than a
+// recompute would: half a unit in the last place of T on one term of dx.)
 template <typename T, int VE, int ACT>
-__device__ __forceinline__ void stream_bwd_sums_to_tile(const Pack<T, VE>* __restrict__ xs,
-                                                        const Pack<T, VE>* __restrict__ dys, size_t row_stride_vec,
-                                                        int nrows, int ty, int TY, Pack<T, VE>* tile_x_col,
-                                                        Pack<T, VE>* tile_d_col, int tile_stride_vec,
-                                                        const BwdLane<T, VE>& L, float (&s1)[VE], float (&s2)[VE]) {
-  using P = Pack<T, VE>;
-  const int iters = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
-  const size_t gstep = (size_t)TY * row_stride_vec;
-  const int sstep = TY * tile_stride_vec;
-  const P* gx = xs + (size_t)ty * row_stride_vec;
-  const P* gd = dys + (size_t)ty * row_stride_vec;
-  P* wx = tile_x_col + ty * tile_stride_vec;
-  P* wd = tile_d_col + ty * tile_stride_vec;
-  if constexpr (sizeof(P) == 16) {
-    constexpr int kDepth = 8;  // rows (x and dy vector each) in flight per thread
-    const P* rx = wx;
-    P* rd = wd;
-    int issued = 0, done = 0;
+__device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, const T* __restrict__ gd,
+                                                   size_t gstep_elems, uint32_t sx, uint32_t sd, uint32_t sstep_bytes,
+                                                   int iters, const BwdLane<T, VE>& L, float (&s1)[VE],
+                                                   float (&s2)[VE]) {
+  if constexpr (sizeof(T) * VE == 16) {
+    const int q = (iters + 3) >> 2;
+    {
+      const T* px = gx;
+      const T* pd = gd;
+      uint32_t wx = sx, wd = sd;
+      int i = 0;
 #pragma unroll
-    for (int d = 0; d < kDepth; ++d) {
-      if (issued < iters) {
-        cp_async16(wx, gx);
-        cp_async16(wd, gd);
-        wx += sstep;
-        wd += sstep;
-        gx += gstep;
-        gd += gstep;
-        ++issued;
+      for (int st = 0; st < 4; ++st) {
+        const int end = min(iters, (st + 1) * q);
+        for (; i < end; ++i) {
+          cp_async16(wx, px);
+          cp_async16(wd, pd);
+          wx += sstep_bytes;
+          wd += sstep_bytes;
+          px += gstep_elems;
+          pd += gstep_elems;
+        }
+        cp_async_commit();
       }
-      cp_async_commit();
     }
-    while (done < iters) {
-      cp_async_wait<kDepth - 1>();
-      float fx[VE], fd[VE];
-      unpack<T, VE>(*rx, fx);
-      unpack<T, VE>(*rd, fd);
-      bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
-      *rd = pack<T, VE>(fd);
-      rx += sstep;
-      rd += sstep;
-      ++done;
-      if (issued < iters) {
-        cp_async16(wx, gx);
-        cp_async16(wd, gd);
-        wx += sstep;
-        wd += sstep;
-        gx += gstep;
-        gd += gstep;
-        ++issued;
+    uint32_t rx = sx, rd = sd;
+    int i = 0;
+#pragma unroll
+    for (int st = 0; st < 4; ++st) {
+      cp_async_wait_dyn(3 - st);
+      const int end = min(iters, (st + 1) * q);
+      for (; i < end; ++i) {
+        float fx[VE], fd[VE];
+        unpack16<T, VE>(lds128(rx), fx);
+        unpack16<T, VE>(lds128(rd), fd);
+        bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+        sts128(rd, pack16<T, VE>(fd));
+        rx += sstep_bytes;
+        rd += sstep_bytes;
       }
-      cp_async_commit();
     }
-    cp_async_wait<0>();
   } else {
+    const T* px = gx;
+    const T* pd = gd;
+    T* wx = reinterpret_cast<T*>(__cvta_shared_to_generic(sx));
+    T* wd = reinterpret_cast<T*>(__cvta_shared_to_generic(sd));
     for (int i = 0; i < iters; ++i) {
-      const P vx = ld_stream(gx);
       float fx[VE], fd[VE];
-      unpack<T, VE>(vx, fx);
-      unpack<T, VE>(ld_stream(gd), fd);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        wx[e] = px[e];
+        fx[e] = load_param<T>(px, e);
+        fd[e] = load_param<T>(pd, e);
+      }
       bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
-      *wx = vx;
-      *wd = pack<T, VE>(fd);
-      gx += gstep;
-      gd += gstep;
-      wx += sstep;
-      wd += sstep;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) wd[e] = store_param<T>(fd[e]);
+      px += gstep_elems;
+      pd += gstep_elems;
+      wx += sstep_bytes / sizeof(T);
+      wd += sstep_bytes / sizeof(T);
     }
   }
 }
 
-// Phase 2: dx = rstd * (gamma * dyh - A - xh * B) = ag * dyh + (nb * xh + na) with per-lane
+// Phase 2 of the fused path: dx = ag * dyh + (nb * xh + na) from the two tiles to global memory
+// (ag = rstd * gamma, nb = -rstd * B, na = -rstd * A per lane; the dy tile holds dyh).
+template <typename T, int VE>
+__device__ __forceinline__ void tile_bwd_dx(uint32_t sx, uint32_t sd, uint32_t sstep_bytes, T* __restrict__ gdst,
+                                            size_t gstep_elems, int iters, const BwdLane<T, VE>& L,
+                                            const float (&A)[VE], const float (&B)[VE]) {
+  float ag[VE], nb[VE], na[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    ag[e] = L.r[e] * L.ga[e];
+    nb[e] = -L.r[e] * B[e];
+    na[e] = -L.r[e] * A[e];
+  }
+  if constexpr (sizeof(T) * VE == 16) {
+    T* gp = gdst;
+#pragma unroll 2
+    for (int i = 0; i < iters; ++i) {
+      float fx[VE], fd[VE];
+      unpack16<T, VE>(lds128(sx), fx);
+      unpack16<T, VE>(lds128(sd), fd);
+      sx += sstep_bytes;
+      sd += sstep_bytes;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+        fx[e] = fmaf(ag[e], fd[e], fmaf(nb[e], xh, na[e]));
+      }
+      stg128(gp, pack16<T, VE>(fx));
+      gp += gstep_elems;
+    }
+  } else {
+    const T* px = reinterpret_cast<const T*>(__cvta_shared_to_generic(sx));
+    const T* pd = reinterpret_cast<const T*>(__cvta_shared_to_generic(sd));
+    T* gp = gdst;
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float xh = fmaf(load_param<T>(px, e), L.r[e], L.nmr[e]);
+        gp[e] = store_param<T>(fmaf(ag[e], load_param<T>(pd, e), fmaf(nb[e], xh, na[e])));
+      }
+      px += sstep_bytes / sizeof(T);
+      pd += sstep_bytes / sizeof(T);
+      gp += gstep_elems;
+    }
+  }
+}
+
+// Phase 2, global to global (multi-kernel path): dx = ag * dyh + (nb * xh + na) with per-lane
 // ag = rstd * gamma, nb = -rstd * B, na = -rstd * A.
 //   kStashed = true : `dys` holds dyh already (fused path);  false: dys holds dy, act' is recomputed.
 template <typename T, int VE, int ACT, bool kStashed>
@@ -232,7 +286,7 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
 // dynamic smem: [x tile][dy tile][red 2*TY*CW][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
 // scratch out : sums[(n * C + c) * 2 + {0,1}] = S1, S2 of the whole sample
 // ------------------------------------------------------------------------------------------------
-template <typename T, int VE, int ACT>
+template <typename T, int VE, int ACT, bool UNI>
 __global__ void __launch_bounds__(kMaxThreads)
     gn_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                         const T* __restrict__ beta, const float* __restrict__ mean_in,
@@ -240,8 +294,8 @@ __global__ void __launch_bounds__(kMaxThreads)
   extern __shared__ uint4 smem_raw[];
   using P = Pack<T, VE>;
   const unsigned k = cluster_nctarank(), rank = cluster_ctarank();
-  const int item = blockIdx.x / k;
-  const int n = item / g.ncb, cb = item - n * g.ncb;
+  const int item = blockIdx.x / k;  // k is a power of two
+  const int n = g.div_ncb.div(item), cb = item - n * g.ncb;
   const int c0 = cb * g.CW;
   const int r0 = min((int)rank * g.rows_per_cta, g.R);
   const int nrows = min(g.rows_per_cta, g.R - r0);
@@ -256,19 +310,21 @@ __global__ void __launch_bounds__(kMaxThreads)
   float* coef = spart + 2 * g.slots;  // A[s], B[slots + s]
 
   const int tid = threadIdx.x;
-  const int tx = tid % g.CV, ty = tid / g.CV;
+  const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
   const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
-  const size_t row_stride_vec = (size_t)g.C / VE;
-  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
+  const size_t base = ((size_t)n * g.R + r0 + ty) * g.C + c0 + (size_t)tx * VE;
+  const int iters = (streaming && ty < nrows) ? (nrows - ty + g.TY - 1) / g.TY : 0;
+  const uint32_t sx = smem_addr(tile_x + ty * g.CV + tx), sd = smem_addr(tile_dy + ty * g.CV + tx);
+  const uint32_t sstep = (uint32_t)(g.TY * g.CV * sizeof(P));
+  const size_t gstep = (size_t)g.TY * g.C;
 
   BwdLane<T, VE> L;
   float s1[VE], s2[VE];
 #pragma unroll
   for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
   if (streaming) {
-    lane_setup<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.D, L);
-    stream_bwd_sums_to_tile<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base),
-                                        row_stride_vec, nrows, ty, g.TY, tile_x + tx, tile_dy + tx, g.CV, L, s1, s2);
+    lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
+    tile_fill_bwd_sums<T, VE, ACT>(x + base, dy + base, gstep, sx, sd, sstep, iters, L, s1, s2);
   }
   cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
 
@@ -322,14 +378,20 @@ __global__ void __launch_bounds__(kMaxThreads)
 
   if (streaming) {
     float A[VE], B[VE];
+    if constexpr (UNI) {
+      const int s = g.div_D.div(c0 + tx * VE) - g_lo;
+      const float a0 = coef[s], b0 = coef[g.slots + s];
 #pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const int s = (c0 + tx * VE + e) / g.D - g_lo;
-      A[e] = coef[s];
-      B[e] = coef[g.slots + s];
+      for (int e = 0; e < VE; ++e) A[e] = a0, B[e] = b0;
+    } else {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const int s = g.div_D.div(c0 + tx * VE + e) - g_lo;
+        A[e] = coef[s];
+        B[e] = coef[g.slots + s];
+      }
     }
-    stream_bwd_dx<T, VE, ACT, true>(tile_x + tx, tile_dy + tx, g.CV, reinterpret_cast<P*>(dx + base), row_stride_vec,
-                                    nrows, ty, g.TY, L, A, B);
+    tile_bwd_dx<T, VE>(sx, sd, sstep, dx + base, gstep, iters, L, A, B);
   }
   cluster_wait();
 }
@@ -372,7 +434,7 @@ __global__ void gn_bwd_param_kernel(const float* __restrict__ sums, int N, int C
 // two-pass, kernel 1: per-tile channel sums.  grid.x = N * chunks * ncb.
 // scratch: tpart[((n * chunks + chunk) * C + c) * 2 + {0,1}]
 // ------------------------------------------------------------------------------------------------
-template <typename T, int VE, int ACT>
+template <typename T, int VE, int ACT, bool UNI>
 __global__ void __launch_bounds__(kMaxThreads)
     gn_bwd_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                          const T* __restrict__ beta, const float* __restrict__ mean_in,
@@ -383,14 +445,13 @@ __global__ void __launch_bounds__(kMaxThreads)
   float* part = red + 2 * g.TY * g.CW;
   float* chan = part + 2 * max((int)blockDim.x, g.CW);
   const int tile_id = blockIdx.x;
-  const int cb = tile_id % g.ncb;
-  const int chunk = (tile_id / g.ncb) % g.chunks;
-  const int n = tile_id / (g.ncb * g.chunks);
+  const int t1 = g.div_ncb.div(tile_id), cb = tile_id - t1 * g.ncb;
+  const int n = g.div_chunks.div(t1), chunk = t1 - n * g.chunks;
   const int c0 = cb * g.CW;
   const int r0 = chunk * g.rows_per_cta;
   const int nrows = min(g.rows_per_cta, g.R - r0);
   const int tid = threadIdx.x;
-  const int tx = tid % g.CV, ty = tid / g.CV;
+  const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
   const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
   const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
 
@@ -399,7 +460,7 @@ __global__ void __launch_bounds__(kMaxThreads)
 #pragma unroll
   for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
   if (streaming) {
-    lane_setup<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.D, L);
+    lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
     stream_bwd_sums<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base),
                                 (size_t)g.C / VE, nrows, ty, g.TY, L, s1, s2);
   }
@@ -466,7 +527,7 @@ __global__ void gn_bwd_finalize_kernel(const float* __restrict__ tpart, const T*
 }
 
 // two-pass, kernel 4: dx.  Reverse tile order relative to the reduce kernel.
-template <typename T, int VE, int ACT>
+template <typename T, int VE, int ACT, bool UNI>
 __global__ void __launch_bounds__(kMaxThreads)
     gn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                         const T* __restrict__ beta, const float* __restrict__ mean_in,
@@ -474,23 +535,29 @@ __global__ void __launch_bounds__(kMaxThreads)
                         const Geom g) {
   using P = Pack<T, VE>;
   const int tile_id = gridDim.x - 1 - blockIdx.x;
-  const int cb = tile_id % g.ncb;
-  const int chunk = (tile_id / g.ncb) % g.chunks;
-  const int n = tile_id / (g.ncb * g.chunks);
+  const int t1 = g.div_ncb.div(tile_id), cb = tile_id - t1 * g.ncb;
+  const int n = g.div_chunks.div(t1), chunk = t1 - n * g.chunks;
   const int c0 = cb * g.CW;
   const int r0 = chunk * g.rows_per_cta;
   const int nrows = min(g.rows_per_cta, g.R - r0);
   const int tid = threadIdx.x;
-  const int tx = tid % g.CV, ty = tid / g.CV;
+  const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
   if (ty >= g.TY || c0 + tx * VE >= g.C) return;
   BwdLane<T, VE> L;
-  lane_setup<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.D, L);
+  lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
   float A[VE], B[VE];
+  if constexpr (UNI) {
+    const int grp = g.div_D.div(c0 + tx * VE);
+    const float a0 = coef[((size_t)n * g.G + grp) * 2], b0 = coef[((size_t)n * g.G + grp) * 2 + 1];
 #pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    const int grp = (c0 + tx * VE + e) / g.D;
-    A[e] = coef[((size_t)n * g.G + grp) * 2];
-    B[e] = coef[((size_t)n * g.G + grp) * 2 + 1];
+    for (int e = 0; e < VE; ++e) A[e] = a0, B[e] = b0;
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const int grp = g.div_D.div(c0 + tx * VE + e);
+      A[e] = coef[((size_t)n * g.G + grp) * 2];
+      B[e] = coef[((size_t)n * g.G + grp) * 2 + 1];
+    }
   }
   const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
   const size_t rs = (size_t)g.C / VE;
@@ -509,12 +576,12 @@ static cudaError_t launch_param(const BwdCall& c, const float* sums, const Geom&
   return cudaGetLastError();
 }
 
-template <typename T, int VE, int ACT>
-static cudaError_t launch_bwd_t(const BwdCall& c, const Plan& p, cudaStream_t stream) {
+template <typename T, int VE, int ACT, bool UNI>
+static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t stream) {
   const Geom& g = p.geom;
   if (p.fused) {
     float* sums = reinterpret_cast<float*>(c.workspace);
-    auto kern = gn_bwd_fused_kernel<T, VE, ACT>;
+    auto kern = gn_bwd_fused_kernel<T, VE, ACT, UNI>;
     cudaError_t err = ensure_kernel_attributes((const void*)kern, p.smem_bytes, g.k > 8);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
@@ -538,9 +605,9 @@ static cudaError_t launch_bwd_t(const BwdCall& c, const Plan& p, cudaStream_t st
   float* tpart = reinterpret_cast<float*>(c.workspace);
   float* sums = tpart + (size_t)g.N * g.chunks * g.C * 2;
   float* coef = sums + (size_t)g.N * g.C * 2;
-  cudaError_t err = ensure_kernel_attributes((const void*)gn_bwd_reduce_kernel<T, VE, ACT>, p.smem_bytes, false);
+  cudaError_t err = ensure_kernel_attributes((const void*)gn_bwd_reduce_kernel<T, VE, ACT, UNI>, p.smem_bytes, false);
   if (err != cudaSuccess) return err;
-  gn_bwd_reduce_kernel<T, VE, ACT><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>(
+  gn_bwd_reduce_kernel<T, VE, ACT, UNI><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>(
       (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, tpart, g);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
@@ -550,9 +617,17 @@ static cudaError_t launch_bwd_t(const BwdCall& c, const Plan& p, cudaStream_t st
   if (err != cudaSuccess) return err;
   err = launch_param<T>(c, sums, g, stream);
   if (err != cudaSuccess) return err;
-  gn_bwd_apply_kernel<T, VE, ACT><<<(unsigned)p.grid, p.threads, 0, stream>>>(
+  gn_bwd_apply_kernel<T, VE, ACT, UNI><<<(unsigned)p.grid, p.threads, 0, stream>>>(
       (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, coef, (T*)c.dx, g);
   return cudaGetLastError();
+}
+
+template <typename T, int VE, int ACT>
+static cudaError_t launch_bwd_t(const BwdCall& c, const Plan& p, cudaStream_t stream) {
+  const bool uni = VE == 1 || p.geom.D % VE == 0;
+  if (uni) return launch_bwd_u<T, VE, ACT, true>(c, p, stream);
+  if constexpr (VE > 1) return launch_bwd_u<T, VE, ACT, false>(c, p, stream);
+  return cudaErrorInvalidValue;
 }
 
 template <typename T, int VE>

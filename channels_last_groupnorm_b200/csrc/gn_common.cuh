@@ -78,13 +78,15 @@ __device__ __forceinline__ void unpack(const Pack<T, VE>& p, float (&f)[VE]) {
   } else if constexpr (VE % 2 == 0) {
 #pragma unroll
     for (int e = 0; e < VE; e += 2) {
-      float2 t;
-      if constexpr (std::is_same<T, __half>::value)
-        t = __half22float2(*reinterpret_cast<const __half2*>(&p.v[e]));
-      else
-        t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&p.v[e]));
-      f[e] = t.x;
-      f[e + 1] = t.y;
+      if constexpr (std::is_same<T, __half>::value) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&p.v[e]));
+        f[e] = t.x;
+        f[e + 1] = t.y;
+      } else {  // bf16 is the upper half of an fp32: one shift / one mask per pair
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&p.v[e]);
+        f[e] = __uint_as_float(w << 16);
+        f[e + 1] = __uint_as_float(w & 0xffff0000u);
+      }
     }
   } else {
 #pragma unroll
@@ -133,6 +135,19 @@ __device__ __forceinline__ float load_param(const T* p, int i) {
     return __bfloat162float(p[i]);
 }
 
+// VE consecutive parameters starting at channel c (c is a multiple of VE on the vector path)
+template <typename T, int VE>
+__device__ __forceinline__ void load_params(const T* p, int c, float (&f)[VE]) {
+  if constexpr (sizeof(T) * VE == 16) {
+    Pack<T, VE> v;
+    *reinterpret_cast<uint4*>(&v) = *reinterpret_cast<const uint4*>(p + c);
+    unpack<T, VE>(v, f);
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) f[e] = load_param<T>(p, c + e);
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ T store_param(float v) {
   if constexpr (sizeof(T) == 4)
@@ -163,16 +178,86 @@ __device__ __forceinline__ void st_stream(V* p, const V& v) {
     *p = v;
 }
 
-// Asynchronous 16-byte global -> shared copies (no registers held while in flight)
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem_src) : "memory");
+// Shared memory by 32-bit shared-window address: explicit 128-bit accesses, asynchronous
+// 16-byte global -> shared copies (no registers held while in flight).
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+// wait until at most `pending` of the most recent commit groups are still in flight (pending <= 3)
+__device__ __forceinline__ void cp_async_wait_dyn(int pending) {
+  if (pending >= 3)
+    cp_async_wait<3>();
+  else if (pending == 2)
+    cp_async_wait<2>();
+  else if (pending == 1)
+    cp_async_wait<1>();
+  else
+    cp_async_wait<0>();
+}
+
+// 16 bytes of T viewed as a uint4 <-> fp32 lanes
+template <typename T, int VE>
+__device__ __forceinline__ void unpack16(const uint4& w, float (&f)[VE]) {
+  static_assert(sizeof(T) * VE == 16, "16-byte vectors only");
+  const uint32_t r[4] = {w.x, w.y, w.z, w.w};
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = __uint_as_float(r[e]);
+  } else if constexpr (std::is_same<T, __half>::value) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&r[e]));
+      f[2 * e] = t.x;
+      f[2 * e + 1] = t.y;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      f[2 * e] = __uint_as_float(r[e] << 16);
+      f[2 * e + 1] = __uint_as_float(r[e] & 0xffff0000u);
+    }
+  }
+}
+template <typename T, int VE>
+__device__ __forceinline__ uint4 pack16(const float (&f)[VE]) {
+  static_assert(sizeof(T) * VE == 16, "16-byte vectors only");
+  uint32_t r[4];
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r[e] = __float_as_uint(f[e]);
+  } else if constexpr (std::is_same<T, __half>::value) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __half2 h = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
+      r[e] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+      r[e] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  return make_uint4(r[0], r[1], r[2], r[3]);
+}
+__device__ __forceinline__ uint4 ldg128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void stg128(void* p, const uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 
 // ---------------------------------------------------------------------------------------------
 // Activations and their derivatives, evaluated in fp32.
@@ -315,6 +400,13 @@ __device__ __forceinline__ float dsmem_ld_f32(const float* local_smem_ptr, unsig
 // ---------------------------------------------------------------------------------------------
 // Geometry of one launch, filled in by the host planner
 // ---------------------------------------------------------------------------------------------
+// Division by a launch-time constant d (1 <= d < 2^31) for 0 <= n < 2^31:
+// n / d == (umulhi(n, mul) + n) >> shr.  Filled in by the host planner.
+struct FastDiv {
+  uint32_t mul, shr;
+  __device__ __forceinline__ int div(int n) const { return (int)((__umulhi((uint32_t)n, mul) + (uint32_t)n) >> shr); }
+};
+
 struct Geom {
   int N, R, C, G, D;
   int CW;            // channels per column block (multiple of VE)
@@ -325,14 +417,15 @@ struct Geom {
   int chunks;        // CTA tiles per (sample, column block): ceil(R / rows_per_cta)
   int slots;         // upper bound on the groups a column block touches
   int k;             // cluster size of the fused kernels (== chunks there)
+  FastDiv div_D, div_CV, div_CW, div_ncb, div_chunks;
 };
 
 // Groups touched by column block starting at channel c0 (width CW, clipped to C):
 // first group and how many.
 __device__ __forceinline__ void cb_groups(const Geom& g, int c0, int& g_lo, int& n_slots) {
   const int c_end = min(c0 + g.CW, g.C);
-  g_lo = c0 / g.D;
-  n_slots = (c_end - 1) / g.D - g_lo + 1;
+  g_lo = g.div_D.div(c0);
+  n_slots = g.div_D.div(c_end - 1) - g_lo + 1;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -340,29 +433,38 @@ __device__ __forceinline__ void cb_groups(const Geom& g, int c0, int& g_lo, int&
 // so results are bit-identical from run to run.
 // ---------------------------------------------------------------------------------------------
 
-// Sum of one value per (row lane, channel) over the CTA tile, per group slot of the column block.
-//   val[e]  : the thread's contribution for its VE channels (must be 0 for threads that did not stream)
-//   red     : TY * CW floats of shared scratch;  out[s], s < n_slots : shared, valid on return
-template <int VE>
-__device__ __forceinline__ void cta_group_sum(const Geom& g, const float (&val)[VE], int tx, int ty, int c0, int g_lo,
+// Sum of NV values per streaming thread over the CTA tile, per group slot of the column block.
+//   NV == VE : one value per channel (a vector may straddle groups)
+//   NV == 1  : one value per thread (every vector lies inside one group: D % VE == 0)
+//   val[i]   : must be 0 for threads that did not stream
+//   red      : TY * CV * NV floats of shared scratch;  out[s], s < n_slots : shared, valid on return
+template <int VE, int NV>
+__device__ __forceinline__ void cta_group_sum(const Geom& g, const float (&val)[NV], int tx, int ty, int c0, int g_lo,
                                               int n_slots, float* red, float* out) {
-  const int CW = g.CW, TY = g.TY;
+  const int TY = g.TY;
+  const int cols = g.CV * NV;  // values per row lane
   if (ty < TY) {
 #pragma unroll
-    for (int e = 0; e < VE; ++e) red[ty * CW + tx * VE + e] = val[e];
+    for (int e = 0; e < NV; ++e) red[ty * cols + tx * NV + e] = val[e];
   }
   __syncthreads();
-  const int c_valid = min(CW, g.C - c0);
+  const int c_valid = min(g.CW, g.C - c0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
   for (int s = warp; s < n_slots; s += nwarps) {
-    const int lo = max((g_lo + s) * g.D, c0) - c0;
-    const int hi = min((g_lo + s + 1) * g.D, c0 + c_valid) - c0;
-    const int w = hi - lo;
-    float acc = 0.f;
-    for (int i = lane; i < TY * w; i += 32) {
-      const int j = i / w;
-      acc += red[j * CW + lo + (i - j * w)];
+    int lo = max((g_lo + s) * g.D, c0) - c0;
+    int hi = min((g_lo + s + 1) * g.D, c0 + c_valid) - c0;
+    if (NV == 1) {  // channels -> vectors (group boundaries are multiples of VE here)
+      lo /= VE;
+      hi /= VE;
     }
+    const int w = hi - lo;
+    // lanes form a (32 / w2) x w2 grid over (row lane, column), w2 = power of two >= min(w, 32)
+    int sh = 0;
+    while ((1 << sh) < w && sh < 5) ++sh;
+    const int cl = lane & ((1 << sh) - 1), jl = lane >> sh, jstep = 32 >> sh;
+    float acc = 0.f;
+    for (int j = jl; j < TY; j += jstep)
+      for (int c = cl; c < w; c += (1 << sh)) acc += red[j * cols + lo + c];
     acc = warp_sum(acc);
     if (lane == 0) out[s] = acc;
   }
@@ -387,7 +489,7 @@ __device__ __forceinline__ void cta_channel_sums(const Geom& g, const float (&s1
   __syncthreads();
   const int J = max(1, (int)blockDim.x / CW);  // row-lane slices summed in parallel
   {
-    const int j = threadIdx.x / CW;
+    const int j = (int)blockDim.x >= CW ? g.div_CW.div((int)threadIdx.x) : 0;
     if (j < J) {
       for (int c = threadIdx.x - j * CW; c < CW; c += blockDim.x) {  // one pass unless CW > blockDim
         float a1 = 0.f, a2 = 0.f;

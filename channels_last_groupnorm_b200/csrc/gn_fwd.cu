@@ -62,80 +62,97 @@ __device__ __forceinline__ void stream_moments(const Pack<T, VE>* __restrict__ s
   }
 }
 
-// Same, but the rows are first brought into the shared-memory tile (fused path) and consumed from
-// there.  16-byte vectors travel with cp.async: the whole per-thread share of the tile is put in
-// flight up front (kDepth groups of kGroup rows) and consumed group by group as it lands; every
-// thread reads back only what it copied itself, so no block barrier is needed.
+// Fused path, phase 1: the thread's rows (ty, ty + TY, ...) of its column vector are copied into
+// the shared-memory tile with cp.async - all of them put in flight up front, in four commit
+// groups - and consumed (Welford) group by group as they land.  Every thread reads back only
+// what it copied itself, so no block barrier is needed.
 template <typename T, int VE>
-__device__ __forceinline__ void stream_moments_to_tile(const Pack<T, VE>* __restrict__ src, size_t row_stride_vec,
-                                                       int nrows, int ty, int TY, Pack<T, VE>* tile_col,
-                                                       int tile_stride_vec, float (&mean)[VE], float (&m2)[VE],
-                                                       float& cnt) {
-  using P = Pack<T, VE>;
-  const int iters = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
-  const size_t gstep = (size_t)TY * row_stride_vec;
-  const int sstep = TY * tile_stride_vec;
-  const P* gp = src + (size_t)ty * row_stride_vec;
-  P* sp_w = tile_col + ty * tile_stride_vec;
-  if constexpr (sizeof(P) == 16) {
-    constexpr int kGroup = 2, kDepth = 8;
-    const P* sp_r = sp_w;
-    int issued = 0, done = 0;
+__device__ __forceinline__ void tile_fill_moments(const T* __restrict__ gsrc, size_t gstep_elems, uint32_t stile,
+                                                  uint32_t sstep_bytes, int iters, float (&mean)[VE], float (&m2)[VE],
+                                                  float& cnt) {
+  if constexpr (sizeof(T) * VE == 16) {
+    const int q = (iters + 3) >> 2;
+    {
+      const T* gp = gsrc;
+      uint32_t sp = stile;
+      int i = 0;
 #pragma unroll
-    for (int d = 0; d < kDepth; ++d) {
-#pragma unroll
-      for (int j = 0; j < kGroup; ++j) {
-        if (issued < iters) {
-          cp_async16(sp_w, gp);
-          sp_w += sstep;
-          gp += gstep;
-          ++issued;
+      for (int st = 0; st < 4; ++st) {
+        const int end = min(iters, (st + 1) * q);
+        for (; i < end; ++i) {
+          cp_async16(sp, gp);
+          sp += sstep_bytes;
+          gp += gstep_elems;
         }
+        cp_async_commit();
       }
-      cp_async_commit();
     }
-    while (done < iters) {
-      cp_async_wait<kDepth - 1>();
+    uint32_t sp = stile;
+    int i = 0;
 #pragma unroll
-      for (int j = 0; j < kGroup; ++j) {
-        if (done < iters) {
-          float f[VE];
-          unpack<T, VE>(*sp_r, f);
-          sp_r += sstep;
-          welford_step<VE>(f, mean, m2, cnt);
-          ++done;
-        }
+    for (int st = 0; st < 4; ++st) {
+      cp_async_wait_dyn(3 - st);
+      const int end = min(iters, (st + 1) * q);
+#pragma unroll 2
+      for (; i < end; ++i) {
+        float f[VE];
+        unpack16<T, VE>(lds128(sp), f);
+        sp += sstep_bytes;
+        welford_step<VE>(f, mean, m2, cnt);
       }
-#pragma unroll
-      for (int j = 0; j < kGroup; ++j) {
-        if (issued < iters) {
-          cp_async16(sp_w, gp);
-          sp_w += sstep;
-          gp += gstep;
-          ++issued;
-        }
-      }
-      cp_async_commit();
     }
-    cp_async_wait<0>();
   } else {
+    const T* gp = gsrc;
+    T* sp = reinterpret_cast<T*>(__cvta_shared_to_generic(stile));
     for (int i = 0; i < iters; ++i) {
-      const P v = ld_stream(gp);
-      *sp_w = v;
-      gp += gstep;
-      sp_w += sstep;
       float f[VE];
-      unpack<T, VE>(v, f);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        sp[e] = gp[e];
+        f[e] = load_param<T>(gp, e);
+      }
+      gp += gstep_elems;
+      sp += sstep_bytes / sizeof(T);
       welford_step<VE>(f, mean, m2, cnt);
     }
   }
 }
 
-// y = act(x * a + b) over the rows this thread owns; source may be shared or global memory.
+// Fused path, phase 2: y = act(x * a + b) from the tile to global memory.
 template <typename T, int VE, int ACT>
-__device__ __forceinline__ void stream_apply(const Pack<T, VE>* src, size_t src_stride_vec, Pack<T, VE>* __restrict__ dst,
-                                             size_t dst_stride_vec, int nrows, int ty, int TY, const float (&a)[VE],
-                                             const float (&b)[VE]) {
+__device__ __forceinline__ void tile_apply(uint32_t stile, uint32_t sstep_bytes, T* __restrict__ gdst,
+                                           size_t gstep_elems, int iters, const float (&a)[VE], const float (&b)[VE]) {
+  constexpr bool FAST = sizeof(T) == 2;
+  if constexpr (sizeof(T) * VE == 16) {
+    uint32_t sp = stile;
+    T* gp = gdst;
+#pragma unroll 2
+    for (int i = 0; i < iters; ++i) {
+      float f[VE];
+      unpack16<T, VE>(lds128(sp), f);
+      sp += sstep_bytes;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
+      stg128(gp, pack16<T, VE>(f));
+      gp += gstep_elems;
+    }
+  } else {
+    const T* sp = reinterpret_cast<const T*>(__cvta_shared_to_generic(stile));
+    T* gp = gdst;
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) gp[e] = store_param<T>(act_fwd<ACT, FAST>(fmaf(load_param<T>(sp, e), a[e], b[e])));
+      sp += sstep_bytes / sizeof(T);
+      gp += gstep_elems;
+    }
+  }
+}
+
+// y = act(x * a + b) over the rows this thread owns, global to global (multi-kernel path).
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ void stream_apply(const Pack<T, VE>* __restrict__ src, size_t src_stride_vec,
+                                             Pack<T, VE>* __restrict__ dst, size_t dst_stride_vec, int nrows, int ty,
+                                             int TY, const float (&a)[VE], const float (&b)[VE]) {
   constexpr bool FAST = sizeof(T) == 2;
   constexpr int U = 4;
   const size_t sstep = (size_t)TY * src_stride_vec, dstep = (size_t)TY * dst_stride_vec;
@@ -146,7 +163,7 @@ __device__ __forceinline__ void stream_apply(const Pack<T, VE>* src, size_t src_
     Pack<T, VE> v[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      v[u] = *sp;
+      v[u] = ld_stream(sp);
       sp += sstep;
     }
 #pragma unroll
@@ -161,7 +178,7 @@ __device__ __forceinline__ void stream_apply(const Pack<T, VE>* src, size_t src_
   }
   for (; left > 0; --left) {
     float f[VE];
-    unpack<T, VE>(*sp, f);
+    unpack<T, VE>(ld_stream(sp), f);
     sp += sstep;
 #pragma unroll
     for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
@@ -171,18 +188,30 @@ __device__ __forceinline__ void stream_apply(const Pack<T, VE>* src, size_t src_
 }
 
 // Per-lane affine coefficients  a = rstd * gamma,  b = beta - mean * a  for the thread's channels.
-// `stat_mean` / `stat_rstd` are indexed by group relative to g_base.
-template <typename T, int VE>
+// `stat_mean` / `stat_rstd` are indexed by group relative to g_base.  UNI: all VE channels of the
+// thread belong to one group, so the statistics are looked up once.
+template <typename T, int VE, bool UNI>
 __device__ __forceinline__ void lane_affine(const T* gamma, const T* beta, const float* stat_mean,
-                                            const float* stat_rstd, int g_base, int c_first, int D, float (&a)[VE],
-                                            float (&b)[VE]) {
+                                            const float* stat_rstd, int g_base, int c_first, const FastDiv div_D,
+                                            float (&a)[VE], float (&b)[VE]) {
+  float ga[VE], be[VE];
+  load_params<T, VE>(gamma, c_first, ga);
+  load_params<T, VE>(beta, c_first, be);
+  if constexpr (UNI) {
+    const int s = div_D.div(c_first) - g_base;
+    const float mu = stat_mean[s], rs = stat_rstd[s];
 #pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    const int c = c_first + e;
-    const int s = c / D - g_base;
-    const float ga = load_param<T>(gamma, c), be = load_param<T>(beta, c);
-    a[e] = stat_rstd[s] * ga;
-    b[e] = fmaf(-stat_mean[s], a[e], be);
+    for (int e = 0; e < VE; ++e) {
+      a[e] = rs * ga[e];
+      b[e] = fmaf(-mu, a[e], be[e]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const int s = div_D.div(c_first + e) - g_base;
+      a[e] = stat_rstd[s] * ga[e];
+      b[e] = fmaf(-stat_mean[s], a[e], be[e]);
+    }
   }
 }
 
@@ -190,14 +219,22 @@ __device__ __forceinline__ void lane_affine(const T* gamma, const T* beta, const
 // first the slot means (sum of cnt * mean / n), then the squared deviations around them.
 //   slot[s]            = local mean      slot[slots + s] = local M2      slot[2 * slots + s] = local count
 // scratch: red (TY * CW floats), tmp (slots floats).
-template <int VE>
+template <int VE, bool UNI>
 __device__ __forceinline__ void cta_slot_moments(const Geom& g, const float (&mean)[VE], const float (&m2)[VE],
                                                  float cnt, int tx, int ty, int c0, int nrows, int g_lo, int n_slots,
                                                  float* red, float* tmp, float* slot) {
-  float val[VE];
+  constexpr int NV = UNI ? 1 : VE;
+  float val[NV];
+  if constexpr (UNI) {
+    float sm = 0.f;
 #pragma unroll
-  for (int e = 0; e < VE; ++e) val[e] = cnt * mean[e];
-  cta_group_sum<VE>(g, val, tx, ty, c0, g_lo, n_slots, red, tmp);
+    for (int e = 0; e < VE; ++e) sm += mean[e];
+    val[0] = cnt * sm;
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) val[e] = cnt * mean[e];
+  }
+  cta_group_sum<VE, NV>(g, val, tx, ty, c0, g_lo, n_slots, red, tmp);
   const int c_end = min(c0 + g.CW, g.C);
   for (int s = threadIdx.x; s < n_slots; s += blockDim.x) {
     const int w = min((g_lo + s + 1) * g.D, c_end) - max((g_lo + s) * g.D, c0);
@@ -206,20 +243,32 @@ __device__ __forceinline__ void cta_slot_moments(const Geom& g, const float (&me
     slot[2 * g.slots + s] = n_loc;
   }
   __syncthreads();
+  if constexpr (UNI) {
+    const float lm = slot[g.div_D.div(min(c0 + tx * VE, g.C - 1)) - g_lo];
+    float acc = 0.f, dev = 0.f;
 #pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    const int c = min(c0 + tx * VE + e, g.C - 1);
-    const float d = mean[e] - slot[c / g.D - g_lo];
-    val[e] = fmaf(cnt * d, d, m2[e]);
+    for (int e = 0; e < VE; ++e) {
+      const float d = mean[e] - lm;
+      dev = fmaf(d, d, dev);
+      acc += m2[e];
+    }
+    val[0] = fmaf(cnt, dev, acc);
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const int c = min(c0 + tx * VE + e, g.C - 1);
+      const float d = mean[e] - slot[g.div_D.div(c) - g_lo];
+      val[e] = fmaf(cnt * d, d, m2[e]);
+    }
   }
-  cta_group_sum<VE>(g, val, tx, ty, c0, g_lo, n_slots, red, slot + g.slots);
+  cta_group_sum<VE, NV>(g, val, tx, ty, c0, g_lo, n_slots, red, slot + g.slots);
 }
 
 // ------------------------------------------------------------------------------------------------
 // fused one-pass kernel.  grid.x = N * ncb * k, cluster = (k,1,1).
 // dynamic smem: [tile rows_per_cta * CV packs][red TY*CW][tmp slots][slot 3*slots][stat 2*slots]
 // ------------------------------------------------------------------------------------------------
-template <typename T, int VE, int ACT>
+template <typename T, int VE, int ACT, bool UNI>
 __global__ void __launch_bounds__(kMaxThreads)
     gn_fwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                         T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, float eps,
@@ -227,8 +276,8 @@ __global__ void __launch_bounds__(kMaxThreads)
   extern __shared__ uint4 smem_raw[];
   using P = Pack<T, VE>;
   const unsigned k = cluster_nctarank(), rank = cluster_ctarank();
-  const int item = blockIdx.x / k;  // (n, cb)
-  const int n = item / g.ncb, cb = item - n * g.ncb;
+  const int item = blockIdx.x / k;  // (n, cb); k is a power of two
+  const int n = g.div_ncb.div(item), cb = item - n * g.ncb;
   const int c0 = cb * g.CW;
   const int r0 = min((int)rank * g.rows_per_cta, g.R);
   const int nrows = min(g.rows_per_cta, g.R - r0);
@@ -241,20 +290,21 @@ __global__ void __launch_bounds__(kMaxThreads)
   float* stat = slot + 3 * g.slots;   // mean[slots], rstd[slots]
 
   const int tid = threadIdx.x;
-  const int tx = tid % g.CV, ty = tid / g.CV;
+  const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
   const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
-  const size_t row_stride_vec = (size_t)g.C / VE;
-
   float mean[VE], m2[VE], cnt = 0.f;
 #pragma unroll
   for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
-  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
-  if (streaming)
-    stream_moments_to_tile<T, VE>(reinterpret_cast<const P*>(x + base), row_stride_vec, nrows, ty, g.TY, tile + tx,
-                                  g.CV, mean, m2, cnt);
+  // this thread's rows: r0 + ty, r0 + ty + TY, ...; its tile slots are CV * TY vectors apart
+  const size_t base = ((size_t)n * g.R + r0 + ty) * g.C + c0 + (size_t)tx * VE;
+  const int iters = (streaming && ty < nrows) ? (nrows - ty + g.TY - 1) / g.TY : 0;
+  const uint32_t stile = smem_addr(tile + ty * g.CV + tx);
+  const uint32_t sstep = (uint32_t)(g.TY * g.CV * sizeof(P));
+  const size_t gstep = (size_t)g.TY * g.C;
+  tile_fill_moments<T, VE>(x + base, gstep, stile, sstep, iters, mean, m2, cnt);
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
-  cta_slot_moments<VE>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
+  cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
 
   // combine the k CTA-local moments (rank order -> every CTA of the cluster gets bit-identical
   // statistics):  mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2
@@ -285,8 +335,8 @@ __global__ void __launch_bounds__(kMaxThreads)
 
   if (streaming) {
     float a[VE], b[VE];
-    lane_affine<T, VE>(gamma, beta, stat, stat + g.slots, g_lo, c0 + tx * VE, g.D, a, b);
-    stream_apply<T, VE, ACT>(tile + tx, g.CV, reinterpret_cast<P*>(y + base), row_stride_vec, nrows, ty, g.TY, a, b);
+    lane_affine<T, VE, UNI>(gamma, beta, stat, stat + g.slots, g_lo, c0 + tx * VE, g.div_D, a, b);
+    tile_apply<T, VE, ACT>(stile, sstep, y + base, gstep, iters, a, b);
   }
   cluster_wait();  // do not exit (and release shared memory) while a peer may still read `slot`
 }
@@ -295,7 +345,7 @@ __global__ void __launch_bounds__(kMaxThreads)
 // two-pass, kernel 1: CTA-local moments per tile.  grid.x = N * chunks * ncb.
 // scratch layout: wpart[(((n * chunks + chunk) * ncb + cb) * slots + s) * 3] = {mean, M2, count}
 // ------------------------------------------------------------------------------------------------
-template <typename T, int VE>
+template <typename T, int VE, bool UNI>
 __global__ void __launch_bounds__(kMaxThreads)
     gn_fwd_stats_kernel(const T* __restrict__ x, float* __restrict__ wpart, const Geom g) {
   extern __shared__ uint4 smem_raw[];
@@ -305,14 +355,13 @@ __global__ void __launch_bounds__(kMaxThreads)
   float* slot = tmp + g.slots;
 
   const int tile_id = blockIdx.x;
-  const int cb = tile_id % g.ncb;
-  const int chunk = (tile_id / g.ncb) % g.chunks;
-  const int n = tile_id / (g.ncb * g.chunks);
+  const int t1 = g.div_ncb.div(tile_id), cb = tile_id - t1 * g.ncb;
+  const int n = g.div_chunks.div(t1), chunk = t1 - n * g.chunks;
   const int c0 = cb * g.CW;
   const int r0 = chunk * g.rows_per_cta;
   const int nrows = min(g.rows_per_cta, g.R - r0);
   const int tid = threadIdx.x;
-  const int tx = tid % g.CV, ty = tid / g.CV;
+  const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
   const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
 
   float mean[VE], m2[VE], cnt = 0.f;
@@ -323,7 +372,7 @@ __global__ void __launch_bounds__(kMaxThreads)
     stream_moments<T, VE>(reinterpret_cast<const P*>(x + base), (size_t)g.C / VE, nrows, ty, g.TY, mean, m2, cnt);
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
-  cta_slot_moments<VE>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
+  cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
   float* out = wpart + (size_t)tile_id * g.slots * 3;
   for (int s = tid; s < n_slots; s += blockDim.x) {
     out[3 * s + 0] = slot[s];
@@ -369,24 +418,23 @@ __global__ void gn_fwd_finalize_kernel(const float* __restrict__ wpart, float* _
 
 // two-pass, kernel 3: normalise + affine + activation.  Tiles are visited in the reverse order of
 // kernel 1 (tile_id = last - blockIdx.x), so the most recently read part of x is re-read first.
-template <typename T, int VE, int ACT>
+template <typename T, int VE, int ACT, bool UNI>
 __global__ void __launch_bounds__(kMaxThreads)
     gn_fwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                         const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ y,
                         const Geom g) {
   using P = Pack<T, VE>;
   const int tile_id = gridDim.x - 1 - blockIdx.x;
-  const int cb = tile_id % g.ncb;
-  const int chunk = (tile_id / g.ncb) % g.chunks;
-  const int n = tile_id / (g.ncb * g.chunks);
+  const int t1 = g.div_ncb.div(tile_id), cb = tile_id - t1 * g.ncb;
+  const int n = g.div_chunks.div(t1), chunk = t1 - n * g.chunks;
   const int c0 = cb * g.CW;
   const int r0 = chunk * g.rows_per_cta;
   const int nrows = min(g.rows_per_cta, g.R - r0);
   const int tid = threadIdx.x;
-  const int tx = tid % g.CV, ty = tid / g.CV;
+  const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
   if (ty >= g.TY || c0 + tx * VE >= g.C) return;
   float a[VE], b[VE];
-  lane_affine<T, VE>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, 0, c0 + tx * VE, g.D, a, b);
+  lane_affine<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, 0, c0 + tx * VE, g.div_D, a, b);
   const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
   const size_t rs = (size_t)g.C / VE;
   stream_apply<T, VE, ACT>(reinterpret_cast<const P*>(x + base), rs, reinterpret_cast<P*>(y + base), rs, nrows, ty, g.TY,
@@ -396,9 +444,9 @@ __global__ void __launch_bounds__(kMaxThreads)
 // ------------------------------------------------------------------------------------------------
 // host-side launchers
 // ------------------------------------------------------------------------------------------------
-template <typename T, int VE, int ACT>
+template <typename T, int VE, int ACT, bool UNI>
 static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t stream) {
-  auto kern = gn_fwd_fused_kernel<T, VE, ACT>;
+  auto kern = gn_fwd_fused_kernel<T, VE, ACT, UNI>;
   cudaError_t err = ensure_kernel_attributes((const void*)kern, p.smem_bytes, p.geom.k > 8);
   if (err != cudaSuccess) return err;
   cudaLaunchConfig_t cfg = {};
@@ -417,12 +465,12 @@ static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t st
                             c.eps, p.geom);
 }
 
-template <typename T, int VE, int ACT>
+template <typename T, int VE, int ACT, bool UNI>
 static cudaError_t launch_two_pass(const FwdCall& c, const Plan& p, cudaStream_t stream) {
   float* wpart = reinterpret_cast<float*>(c.workspace);
-  cudaError_t err = ensure_kernel_attributes((const void*)gn_fwd_stats_kernel<T, VE>, p.smem_bytes, false);
+  cudaError_t err = ensure_kernel_attributes((const void*)gn_fwd_stats_kernel<T, VE, UNI>, p.smem_bytes, false);
   if (err != cudaSuccess) return err;
-  gn_fwd_stats_kernel<T, VE><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>((const T*)c.x, wpart, p.geom);
+  gn_fwd_stats_kernel<T, VE, UNI><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>((const T*)c.x, wpart, p.geom);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   const int warps = p.geom.N * p.geom.G;
@@ -431,14 +479,19 @@ static cudaError_t launch_two_pass(const FwdCall& c, const Plan& p, cudaStream_t
   gn_fwd_finalize_kernel<<<fin_blocks, fin_threads, 0, stream>>>(wpart, c.mean, c.rstd, c.eps, p.geom);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  gn_fwd_apply_kernel<T, VE, ACT><<<(unsigned)p.grid, p.threads, 0, stream>>>(
+  gn_fwd_apply_kernel<T, VE, ACT, UNI><<<(unsigned)p.grid, p.threads, 0, stream>>>(
       (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, (T*)c.y, p.geom);
   return cudaGetLastError();
 }
 
 template <typename T, int VE, int ACT>
 static cudaError_t launch_fwd_t(const FwdCall& c, const Plan& p, cudaStream_t stream) {
-  return p.fused ? launch_fused<T, VE, ACT>(c, p, stream) : launch_two_pass<T, VE, ACT>(c, p, stream);
+  // uniform: every thread-vector lies inside one group (always true for single-element vectors)
+  const bool uni = VE == 1 || p.geom.D % VE == 0;
+  if (uni) return p.fused ? launch_fused<T, VE, ACT, true>(c, p, stream) : launch_two_pass<T, VE, ACT, true>(c, p, stream);
+  if constexpr (VE > 1)
+    return p.fused ? launch_fused<T, VE, ACT, false>(c, p, stream) : launch_two_pass<T, VE, ACT, false>(c, p, stream);
+  return cudaErrorInvalidValue;
 }
 
 template <typename T, int VE>

@@ -42,6 +42,26 @@ int env_int(const char* name, int fallback) {
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+// n / d == (umulhi(n, mul) + n) >> shr for 0 <= n < 2^31 (round-up method, 33-bit multiplier)
+FastDiv make_fast_div(int d) {
+  FastDiv f;
+  if (d < 1) d = 1;
+  uint32_t s = 0;
+  while ((1ull << s) < (unsigned long long)d) ++s;
+  const unsigned long long m = ((1ull << 32) * ((1ull << s) - (unsigned long long)d)) / (unsigned long long)d + 1;
+  f.mul = (uint32_t)m;
+  f.shr = s;
+  return f;
+}
+
+void fill_divisors(Geom* g) {
+  g->div_D = make_fast_div(g->D);
+  g->div_CV = make_fast_div(g->CV);
+  g->div_CW = make_fast_div(g->CW);
+  g->div_ncb = make_fast_div(g->ncb);
+  g->div_chunks = make_fast_div(g->chunks);
+}
+
 // shared-memory floats of the CTA reductions (layouts in gn_fwd.cu / gn_bwd.cu)
 size_t fwd_fold_floats(int CW, int TY, int slots, int threads) {
   (void)threads;
@@ -71,8 +91,7 @@ void thread_layout(int CV, int rows_per_cta, int target_threads, int* TY, int* t
 // (higher is better): SMs kept busy x row-segment efficiency x co-residency.
 bool plan_fused_candidate(const Shape& sh, int cw, int k, Plan* out, double* score) {
   const int ve = sh.ve, s = sh.s;
-  const int target_threads = env_int("GNB200_THREADS", 256);
-  const size_t tile_budget = (size_t)env_int("GNB200_TILE_KB", 100) * 1024;
+  const int target_threads = env_int("GNB200_THREADS", 128);
   const int ncb = sh.C / cw;
   const int CV = cw / ve;
   const int ntiles = sh.direction == 0 ? 1 : 2;
@@ -94,16 +113,27 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, Plan* out, double* sco
   p.ws_bytes = sh.direction == 0 ? 0 : (size_t)sh.N * sh.C * 2 * sizeof(float);
   p.launches = sh.direction == 0 ? 1 : 2;
   p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, rows, k, slots, k};
+  fill_divisors(&p.geom);
   if (p.grid > 0x7fffffffLL) return false;
   *out = p;
 
+  // Heuristic fitted to measurements on B200 (bf16 / fp16, N x 256 x 64 x 64 and similar):
+  // the kernels are bound by instruction issue and latency rather than DRAM, so co-resident CTAs
+  // per SM matter most, then rows per thread (per-thread set-up is amortised over them), then the
+  // contiguous row segment (64 B is nearly as good as 128 B; 32 B wastes DRAM sectors).
   const long long seg = (long long)cw * s;
-  const double seg_eff = seg >= 256 ? 1.0 : seg >= 128 ? 0.95 : seg >= 64 ? 0.8 : seg >= 32 ? 0.6 : 0.4;
+  const double seg_eff = seg >= 128 ? 1.0 : seg >= 64 ? 0.95 : seg >= 32 ? 0.7 : 0.4;
   const double sms = (double)(p.grid < kSmCount ? p.grid : kSmCount);
-  const double co_resident = (tile + fold <= tile_budget) ? 1.0 : 0.9;  // >= 2 CTAs per SM overlap their phases
-  const double tile_eff = (tile / ntiles >= 16 * 1024 || p.grid <= kSmCount) ? 1.0 : 0.9;  // tiny tiles: overhead
+  int per_sm = (int)(kSmemMaxOptin / (tile + fold + 1024));
+  const int by_threads = 2048 / threads;
+  if (per_sm > by_threads) per_sm = by_threads;
+  if (per_sm > 8) per_sm = 8;
+  static const double occ_tab[9] = {0.3, 0.55, 0.75, 0.86, 0.93, 0.97, 1.0, 1.0, 1.0};
+  const double occ = p.grid <= kSmCount ? 1.0 : occ_tab[per_sm];
+  const int rpt = rows / TY;
+  const double rpt_eff = rpt >= 16 ? 1.0 : rpt >= 8 ? 0.93 : rpt >= 4 ? 0.85 : 0.75;
   const double sync_eff = 1.0 - 0.004 * k;  // mild preference for smaller clusters
-  *score = sms * seg_eff * co_resident * tile_eff * sync_eff;
+  *score = sms * seg_eff * occ * rpt_eff * sync_eff;
   return true;
 }
 
@@ -149,9 +179,13 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
   int slots = (cw - 1) / sh.D + 2;
   if (slots > sh.G) slots = sh.G;
 
-  // rows per CTA tile: ~64 KB of x per tile, but at least ~4 tiles per SM when the problem allows
+  // rows per CTA tile: large tiles amortise the per-CTA reduction (up to 512 KB of x per tile),
+  // but at least ~4 tiles per SM when the problem allows
   const long long row_bytes = (long long)cw * s;
-  long long rows = (64 * 1024 + row_bytes - 1) / row_bytes;
+  long long tile_target = (long long)sh.N * sh.R * sh.C * s / (8LL * kSmCount);
+  if (tile_target < 64 * 1024) tile_target = 64 * 1024;
+  if (tile_target > 512 * 1024) tile_target = 512 * 1024;
+  long long rows = (tile_target + row_bytes - 1) / row_bytes;
   if (rows > sh.R) rows = sh.R;
   const long long want_tiles = 4LL * kSmCount;
   long long chunks = (sh.R + rows - 1) / rows;
@@ -186,6 +220,7 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
     p.launches = 4;
   }
   p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, (int)rows, (int)chunks, slots, 1};
+  fill_divisors(&p.geom);
   *out = p;
   return true;
 }
