@@ -604,6 +604,21 @@ def sweep(args):
             out_f.flush()
 
 
+def profile_target(args):
+    """A few plain calls of the hot path for ncu (`ncu ... python bench.py --workload W --profile 2`)."""
+    torch.cuda.set_device(0)
+    N, C, H, W, G, eps, act, dt, xs, bwd, dist_name = WORKLOADS[args.workload]
+    x, ga, be, dy = make_inputs(N, C, H, W, DT[dt], 0, xs, dist_name)
+    prob = DeviceProblem(args.workload, N, x, ga, be, dy, min_total_bytes=1)
+    stream = torch.cuda.current_stream().cuda_stream
+    for i in range(args.profile):
+        prob.fwd(i, stream)
+        if bwd:
+            prob.bwd_(i, stream, True)
+    torch.cuda.synchronize()
+    print("profiled", args.workload, args.profile, "calls")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -617,8 +632,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ref", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--profile", type=int, default=0, metavar="CALLS",
+                    help="profiling target: CALLS forward(+backward) calls of --workload through the C ABI, nothing else")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.profile > 0:
+        return profile_target(args)
     if args.sweep:
         return sweep(args)
     if args.impl == "reference":
