@@ -47,6 +47,11 @@ lib.gnb200_bwd.restype = ctypes.c_int
 lib.gnb200_bwd.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                            _c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
                            _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_size_t, _c_void_p]
+lib.gnb200_bwd_static_scratch.restype = ctypes.c_int
+lib.gnb200_bwd_static_scratch.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                          _c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
+                                          _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p]
+STATIC_SCRATCH_BYTES = 4 << 20
 lib.gnb200_describe_plan.restype = ctypes.c_int
 lib.gnb200_describe_plan.argtypes = [_c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
                                      ctypes.c_char_p, ctypes.c_int]
@@ -123,3 +128,12 @@ def bwd_raw(dy_nhwc, x_nhwc, gamma, beta, mean, rstd, G, act, dx=None, workspace
                          _ptr(workspace) if need else None,
                          workspace.numel() if (need and workspace is not None) else 0, s))
     return dx, dparam, dgamma, dbeta
+
+
+def bwd_static_scratch_raw(dy_nhwc, x_nhwc, gamma, beta, mean, rstd, G, act, dx, dparam, dgamma, dbeta, stream=None):
+    """Calls gnb200_bwd_static_scratch on preallocated outputs (the entry point itself allocates nothing)."""
+    N, R, C = x_nhwc.shape
+    s = torch.cuda.current_stream(x_nhwc.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_bwd_static_scratch(_ptr(dy_nhwc), _ptr(x_nhwc), _ptr(gamma), _ptr(beta), _ptr(mean), _ptr(rstd),
+                                        N, R, C, G, int(act), DTYPE_CODES[x_nhwc.dtype], _ptr(dx), _ptr(dparam),
+                                        _ptr(dgamma), _ptr(dbeta), s))

@@ -18,6 +18,21 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+}  // namespace
+
+namespace gnb200 {
+// Same thread-local text as fail(), for entry points that live in other translation units.
+int report_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+}  // namespace gnb200
+
+namespace {
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_common(int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype) {

@@ -24,7 +24,8 @@
  *
  * Every pointer is a device pointer on the current CUDA device.  All work is enqueued on
  * `stream` and nothing synchronises with the host.  No entry point below allocates device
- * memory: scratch comes from the caller (`workspace`).
+ * memory: scratch comes from the caller (`workspace`) or, for gnb200_bwd_static_scratch, from a
+ * fixed array inside the library.
  */
 #ifndef GNB200_H_
 #define GNB200_H_
@@ -95,6 +96,28 @@ int gnb200_bwd(const void* dy, const void* x, const void* gamma, const void* bet
                int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype,
                void* dx, float* dgamma_dbeta_f32, void* dgamma, void* dbeta,
                void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Backward for callers that must not allocate device memory and therefore cannot supply the
+ * `workspace` of gnb200_bwd: plugins of an inference runtime that owns all buffers, real-time
+ * loops that may not touch the allocator, code inside a stream capture, thin FFI bindings that
+ * only see the tensors they were handed.  Same arguments and results as gnb200_bwd without
+ * `workspace` / `workspace_bytes`; the scratch is a fixed GNB200_STATIC_SCRATCH_BYTES array inside
+ * the library (held on every GPU that loads the library until the process exits).
+ * This entry point has no counterpart in the reference, whose launcher always allocates
+ * (src/gnnhwc/csrc/gn_kernel.cu:954-1001).
+ *   - A problem whose plan needs more scratch than the array returns GNB200_ERR_WORKSPACE
+ *     (gnb200_last_error() states both sizes); nothing is launched.
+ *   - The first call on a device resolves the array's device address; make it before any stream
+ *     capture.  It never calls cudaMalloc / cudaFree or any allocating routine.
+ *   - All calls on a device share the array: calls whose kernels may overlap on the GPU race and
+ *     must be ordered by the caller.  Nothing needs clearing between calls.
+ */
+#define GNB200_STATIC_SCRATCH_BYTES (4u << 20)
+int gnb200_bwd_static_scratch(const void* dy, const void* x, const void* gamma, const void* beta,
+                              const float* mean, const float* rstd,
+                              int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype,
+                              void* dx, float* dgamma_dbeta_f32, void* dgamma, void* dbeta, void* stream);
 
 /*
  * Describes the launch plan chosen for a problem ("fwd fused k=4 cw=64 ..."), for logs, tests
