@@ -60,14 +60,18 @@ __device__ __forceinline__ void lane_setup(const T* gamma, const T* beta, const 
 template <typename T, int VE, int ACT>
 __device__ __forceinline__ void bwd_row_sums(const float (&fx)[VE], float (&fd)[VE], const BwdLane<T, VE>& L,
                                              float (&s1)[VE], float (&s2)[VE]) {
-  constexpr bool FAST = sizeof(T) == 2;
+  float xh[VE], yh[VE], gr[VE];
 #pragma unroll
   for (int e = 0; e < VE; ++e) {
-    const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
-    const float yh = fmaf(xh, L.ga[e], L.be[e]);
-    fd[e] *= act_grad<ACT, FAST>(yh);
+    xh[e] = fmaf(fx[e], L.r[e], L.nmr[e]);
+    yh[e] = fmaf(xh[e], L.ga[e], L.be[e]);
+  }
+  act_grad_vec<T, VE, ACT>(yh, gr);
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    fd[e] *= gr[e];
     s1[e] += fd[e];
-    s2[e] = fmaf(fd[e], xh, s2[e]);
+    s2[e] = fmaf(fd[e], xh[e], s2[e]);
   }
 }
 
@@ -145,6 +149,22 @@ __device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, con
     for (int st = 0; st < 4; ++st) {
       cp_async_wait_dyn(3 - st);
       const int end = min(iters, (st + 1) * q);
+      // two rows per trip: four independent shared loads and 2 * VE independent lanes in flight
+      for (; i + 2 <= end; i += 2) {
+        const uint4 wx0 = lds128(rx), wd0 = lds128(rd);
+        const uint4 wx1 = lds128(rx + sstep_bytes), wd1 = lds128(rd + sstep_bytes);
+        float fx0[VE], fd0[VE], fx1[VE], fd1[VE];
+        unpack16<T, VE>(wx0, fx0);
+        unpack16<T, VE>(wd0, fd0);
+        unpack16<T, VE>(wx1, fx1);
+        unpack16<T, VE>(wd1, fd1);
+        bwd_row_sums<T, VE, ACT>(fx0, fd0, L, s1, s2);
+        bwd_row_sums<T, VE, ACT>(fx1, fd1, L, s1, s2);
+        sts128(rd, pack16<T, VE>(fd0));
+        sts128(rd + sstep_bytes, pack16<T, VE>(fd1));
+        rx += 2 * sstep_bytes;
+        rd += 2 * sstep_bytes;
+      }
       for (; i < end; ++i) {
         float fx[VE], fd[VE];
         unpack16<T, VE>(lds128(rx), fx);
@@ -193,6 +213,15 @@ __device__ __forceinline__ void tile_bwd_dx(uint32_t sx, uint32_t sd, uint32_t s
     na[e] = -L.r[e] * A[e];
   }
   if constexpr (sizeof(T) * VE == 16) {
+    // 16-bit results: fold xh = r x + nmr into the coefficients (nb xh + na = c1 x + c2); the
+    // extra rounding is far below the 16-bit result.  fp32 keeps the xh form.
+    constexpr bool kFold = sizeof(T) == 2;
+    float c1[VE], c2[VE];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      c1[e] = nb[e] * L.r[e];
+      c2[e] = fmaf(nb[e], L.nmr[e], na[e]);
+    }
     T* gp = gdst;
 #pragma unroll 2
     for (int i = 0; i < iters; ++i) {
@@ -203,8 +232,12 @@ __device__ __forceinline__ void tile_bwd_dx(uint32_t sx, uint32_t sd, uint32_t s
       sd += sstep_bytes;
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
-        const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
-        fx[e] = fmaf(ag[e], fd[e], fmaf(nb[e], xh, na[e]));
+        if constexpr (kFold) {
+          fx[e] = fmaf(ag[e], fd[e], fmaf(c1[e], fx[e], c2[e]));
+        } else {
+          const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+          fx[e] = fmaf(ag[e], fd[e], fmaf(nb[e], xh, na[e]));
+        }
       }
       stg128(gp, pack16<T, VE>(fx));
       gp += gstep_elems;
@@ -234,7 +267,6 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
                                               Pack<T, VE>* __restrict__ dst, size_t dst_stride_vec, int nrows, int ty,
                                               int TY, const BwdLane<T, VE>& L, const float (&A)[VE],
                                               const float (&B)[VE]) {
-  constexpr bool FAST = sizeof(T) == 2;
   constexpr int U = 4;
   float ag[VE], nb[VE], na[VE];
 #pragma unroll
@@ -266,12 +298,17 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
         float fx[VE], fd[VE];
         unpack<T, VE>(vx[u], fx);
         unpack<T, VE>(vd[u], fd);
+        float xh[VE], yh[VE], gr[VE];
 #pragma unroll
         for (int e = 0; e < VE; ++e) {
-          const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
-          float dyh = fd[e];
-          if constexpr (!kStashed) dyh *= act_grad<ACT, FAST>(fmaf(xh, L.ga[e], L.be[e]));
-          fx[e] = fmaf(ag[e], dyh, fmaf(nb[e], xh, na[e]));
+          xh[e] = fmaf(fx[e], L.r[e], L.nmr[e]);
+          yh[e] = fmaf(xh[e], L.ga[e], L.be[e]);
+        }
+        if constexpr (!kStashed) act_grad_vec<T, VE, ACT>(yh, gr);
+#pragma unroll
+        for (int e = 0; e < VE; ++e) {
+          const float dyh = kStashed ? fd[e] : fd[e] * gr[e];
+          fx[e] = fmaf(ag[e], dyh, fmaf(nb[e], xh[e], na[e]));
         }
         st_stream(po, pack<T, VE>(fx));
         po += dstep;

@@ -365,6 +365,123 @@ __device__ __forceinline__ float act_grad(float v) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Packed f16x2 evaluation of the smooth activations for 16-bit tensors: two channels per
+// instruction and per MUFU op.  The pre-activation yh is formed in fp32 and converted with
+// saturation (|yh| > 65504 clamps instead of becoming inf); what is evaluated in half precision
+// (11 significant bits) is only the activation, whose result is rounded to a 16-bit tensor anyway
+// (forward) or multiplies a 16-bit dy (backward).  fp32 tensors never take this path.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ __half2 f32x2_to_h2_sat(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return *reinterpret_cast<__half2*>(&r);
+}
+__device__ __forceinline__ __half2 tanh_h2(__half2 v) {
+  uint32_t r;
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(r) : "r"(*reinterpret_cast<uint32_t*>(&v)));
+  return *reinterpret_cast<__half2*>(&r);
+}
+
+// which (activation, tensor type) pairs use the packed path: where it saves instructions
+template <typename T, int ACT>
+__host__ __device__ constexpr bool use_h2_fwd() {
+  return sizeof(T) == 2 && (ACT == kActGelu || ACT == kActGeluTanh || (ACT == kActSilu && std::is_same<T, __half>::value));
+}
+template <typename T, int ACT>
+__host__ __device__ constexpr bool use_h2_bwd() {
+  return sizeof(T) == 2 && (ACT == kActGelu || ACT == kActGeluTanh || ACT == kActSilu);
+}
+
+// tanh argument u(v) and its derivative du/dv for the two GELU forms, v^2 clamped to 64
+template <int ACT>
+__device__ __forceinline__ void gelu_poly_h2(__half2 v, __half2& u, __half2& du, bool want_du) {
+  const __half2 v2 = __hmin2(__hmul2(v, v), __float2half2_rn(64.0f));
+  if constexpr (ACT == kActGelu) {
+    const __half2 c1 = __float2half2_rn(kPhiC1), c3 = __float2half2_rn(kPhiC3), c5 = __float2half2_rn(kPhiC5);
+    u = __hmul2(v, __hfma2(__hfma2(c5, v2, c3), v2, c1));
+    if (want_du)
+      du = __hfma2(__hfma2(__float2half2_rn(5.0f * kPhiC5), v2, __float2half2_rn(3.0f * kPhiC3)), v2, c1);
+  } else {
+    const float kBeta = 0.79788456080286536f;
+    u = __hmul2(v, __hfma2(__float2half2_rn(kBeta * 0.044715f), v2, __float2half2_rn(kBeta)));
+    if (want_du) du = __hfma2(__float2half2_rn(3.0f * kBeta * 0.044715f), v2, __float2half2_rn(kBeta));
+  }
+}
+
+template <int ACT>
+__device__ __forceinline__ __half2 act_fwd_h2(__half2 v) {
+  const __half2 half_ = __float2half2_rn(0.5f);
+  if constexpr (ACT == kActSilu) {
+    const __half2 h = __hmul2(v, half_);
+    return __hfma2(h, tanh_h2(h), h);
+  } else {
+    __half2 u, du;
+    gelu_poly_h2<ACT>(v, u, du, false);
+    const __half2 h = __hmul2(v, half_);
+    return __hfma2(h, tanh_h2(u), h);
+  }
+}
+
+template <int ACT>
+__device__ __forceinline__ __half2 act_grad_h2(__half2 v) {
+  const __half2 half_ = __float2half2_rn(0.5f), one = __float2half2_rn(1.0f);
+  if constexpr (ACT == kActSilu) {
+    const __half2 t = tanh_h2(__hmul2(v, half_));
+    const __half2 s = __hfma2(half_, t, half_);
+    return __hmul2(s, __hfma2(v, __hsub2(one, s), one));
+  } else {
+    __half2 u, du;
+    gelu_poly_h2<ACT>(v, u, du, true);
+    const __half2 t = tanh_h2(u);
+    // Phi + v * Phi' with Phi' = 0.5 (1 - t^2) u'
+    return __hfma2(__hmul2(__hmul2(v, half_), du), __hfma2(__hneg2(t), t, one), __hfma2(half_, t, half_));
+  }
+}
+
+// Forward epilogue for one 16-byte vector: out = T(act(yh)) packed.
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ uint4 act_pack16(const float (&yh)[VE]) {
+  if constexpr (use_h2_fwd<T, ACT>()) {
+    uint32_t r[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __half2 y = act_fwd_h2<ACT>(f32x2_to_h2_sat(yh[2 * e], yh[2 * e + 1]));
+      if constexpr (std::is_same<T, __half>::value) {
+        r[e] = *reinterpret_cast<const uint32_t*>(&y);
+      } else {
+        const float2 f = __half22float2(y);
+        const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+        r[e] = *reinterpret_cast<const uint32_t*>(&b);
+      }
+    }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+  } else {
+    constexpr bool FAST = sizeof(T) == 2;
+    float o[VE];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) o[e] = act_fwd<ACT, FAST>(yh[e]);
+    return pack16<T, VE>(o);
+  }
+}
+
+// Backward: g[e] = act'(yh[e]) for one vector.
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ void act_grad_vec(const float (&yh)[VE], float (&g)[VE]) {
+  if constexpr (use_h2_bwd<T, ACT>() && VE % 2 == 0) {
+#pragma unroll
+    for (int e = 0; e < VE; e += 2) {
+      const float2 f = __half22float2(act_grad_h2<ACT>(f32x2_to_h2_sat(yh[e], yh[e + 1])));
+      g[e] = f.x;
+      g[e + 1] = f.y;
+    }
+  } else {
+    constexpr bool FAST = sizeof(T) == 2;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) g[e] = act_grad<ACT, FAST>(yh[e]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Thread-block cluster helpers (raw PTX so arrive and wait can be split)
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned cluster_ctarank() {

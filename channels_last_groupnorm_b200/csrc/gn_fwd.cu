@@ -132,8 +132,8 @@ __device__ __forceinline__ void tile_apply(uint32_t stile, uint32_t sstep_bytes,
       unpack16<T, VE>(lds128(sp), f);
       sp += sstep_bytes;
 #pragma unroll
-      for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
-      stg128(gp, pack16<T, VE>(f));
+      for (int e = 0; e < VE; ++e) f[e] = fmaf(f[e], a[e], b[e]);
+      stg128(gp, act_pack16<T, VE, ACT>(f));
       gp += gstep_elems;
     }
   } else {
@@ -170,9 +170,15 @@ __device__ __forceinline__ void stream_apply(const Pack<T, VE>* __restrict__ src
     for (int u = 0; u < U; ++u) {
       float f[VE];
       unpack<T, VE>(v[u], f);
+      if constexpr (sizeof(T) * VE == 16) {
 #pragma unroll
-      for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
-      st_stream(dp, pack<T, VE>(f));
+        for (int e = 0; e < VE; ++e) f[e] = fmaf(f[e], a[e], b[e]);
+        stg128(dp, act_pack16<T, VE, ACT>(f));
+      } else {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) f[e] = act_fwd<ACT, FAST>(fmaf(f[e], a[e], b[e]));
+        st_stream(dp, pack<T, VE>(f));
+      }
       dp += dstep;
     }
   }
