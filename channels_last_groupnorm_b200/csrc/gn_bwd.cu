@@ -75,40 +75,54 @@ __device__ __forceinline__ void bwd_row_sums(const float (&fx)[VE], float (&fd)[
   }
 }
 
-// Phase 1 of the multi-kernel path: S1, S2 over the thread's rows straight from global memory.
+constexpr int kRingDepth = 8;  // rows in flight per thread in the multi-kernel reduce kernel
+
+// Phase 1 of the multi-kernel path: S1, S2 over the thread's rows.  16-byte vectors of x and dy
+// travel through two shared-memory rings with cp.async (kRingDepth rows per thread in flight,
+// no registers held); slot s of the thread lives at ring + s * ring_stride.
 template <typename T, int VE, int ACT>
-__device__ __forceinline__ void stream_bwd_sums(const Pack<T, VE>* __restrict__ xs, const Pack<T, VE>* __restrict__ dys,
-                                                size_t row_stride_vec, int nrows, int ty, int TY,
-                                                const BwdLane<T, VE>& L, float (&s1)[VE], float (&s2)[VE]) {
-  constexpr int U = 4;
-  const size_t step = (size_t)TY * row_stride_vec;
-  const Pack<T, VE>* px = xs + (size_t)ty * row_stride_vec;
-  const Pack<T, VE>* pd = dys + (size_t)ty * row_stride_vec;
-  int left = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
-  for (; left >= U; left -= U) {
-    Pack<T, VE> vx[U], vd[U];
+__device__ __forceinline__ void stream_bwd_sums(const T* __restrict__ gx, const T* __restrict__ gd,
+                                                size_t gstep_elems, int iters, uint32_t ring_x, uint32_t ring_d,
+                                                uint32_t ring_stride, const BwdLane<T, VE>& L, float (&s1)[VE],
+                                                float (&s2)[VE]) {
+  if constexpr (sizeof(T) * VE == 16) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      vx[u] = ld_stream(px);
-      vd[u] = ld_stream(pd);
-      px += step;
-      pd += step;
+    for (int d = 0; d < kRingDepth; ++d) {
+      if (d < iters) {
+        cp_async16(ring_x + d * ring_stride, gx);
+        cp_async16(ring_d + d * ring_stride, gd);
+        gx += gstep_elems;
+        gd += gstep_elems;
+      }
+      cp_async_commit();
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int i = 0; i < iters; ++i) {
+      cp_async_wait<kRingDepth - 1>();
+      const uint32_t off = (i & (kRingDepth - 1)) * ring_stride;
       float fx[VE], fd[VE];
-      unpack<T, VE>(vx[u], fx);
-      unpack<T, VE>(vd[u], fd);
+      unpack16<T, VE>(lds128(ring_x + off), fx);
+      unpack16<T, VE>(lds128(ring_d + off), fd);
+      if (i + kRingDepth < iters) {
+        cp_async16(ring_x + off, gx);
+        cp_async16(ring_d + off, gd);
+        gx += gstep_elems;
+        gd += gstep_elems;
+      }
+      cp_async_commit();
       bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
     }
-  }
-  for (; left > 0; --left) {
-    float fx[VE], fd[VE];
-    unpack<T, VE>(ld_stream(px), fx);
-    unpack<T, VE>(ld_stream(pd), fd);
-    px += step;
-    pd += step;
-    bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+  } else {
+    for (int i = 0; i < iters; ++i) {
+      float fx[VE], fd[VE];
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        fx[e] = load_param<T>(gx, e);
+        fd[e] = load_param<T>(gd, e);
+      }
+      gx += gstep_elems;
+      gd += gstep_elems;
+      bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+    }
   }
 }
 
@@ -478,7 +492,9 @@ __global__ void __launch_bounds__(kMaxThreads)
                          const float* __restrict__ rstd_in, float* __restrict__ tpart, const Geom g) {
   extern __shared__ uint4 smem_raw[];
   using P = Pack<T, VE>;
-  float* red = reinterpret_cast<float*>(smem_raw);
+  // [ring x][ring dy] (kRingDepth * blockDim vectors each) [red][part][chan]
+  const size_t ring_bytes = sizeof(T) * VE == 16 ? (size_t)kRingDepth * blockDim.x * 16 : 0;
+  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + 2 * ring_bytes);
   float* part = red + 2 * g.TY * g.CW;
   float* chan = part + 2 * max((int)blockDim.x, g.CW);
   const int tile_id = blockIdx.x;
@@ -490,7 +506,8 @@ __global__ void __launch_bounds__(kMaxThreads)
   const int tid = threadIdx.x;
   const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
   const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
-  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
+  const size_t base = ((size_t)n * g.R + r0 + ty) * g.C + c0 + (size_t)tx * VE;
+  const int iters = (streaming && ty < nrows) ? (nrows - ty + g.TY - 1) / g.TY : 0;
 
   BwdLane<T, VE> L;
   float s1[VE], s2[VE];
@@ -498,8 +515,9 @@ __global__ void __launch_bounds__(kMaxThreads)
   for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
   if (streaming) {
     lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
-    stream_bwd_sums<T, VE, ACT>(reinterpret_cast<const P*>(x + base), reinterpret_cast<const P*>(dy + base),
-                                (size_t)g.C / VE, nrows, ty, g.TY, L, s1, s2);
+    const uint32_t ring = smem_addr(smem_raw) + tid * 16;
+    stream_bwd_sums<T, VE, ACT>(x + base, dy + base, (size_t)g.TY * g.C, iters, ring, ring + (uint32_t)ring_bytes,
+                                blockDim.x * 16, L, s1, s2);
   }
   cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
   const int c_valid = min(g.CW, g.C - c0);
@@ -507,37 +525,42 @@ __global__ void __launch_bounds__(kMaxThreads)
   for (int c = tid; c < c_valid; c += blockDim.x) out[c] = make_float2(chan[c], chan[g.CW + c]);
 }
 
-// two-pass, kernel 2: block per (n, group): sums over tiles (ascending) -> S1, S2 per channel, and
-// A, B of the group.  block (32, 8): x over the group's channels, y over tile lanes.
+// two-pass, kernel 2: one CTA of 256 threads per (n, group).  The group's channels are taken in
+// blocks of W (a power of two <= 32 covering D); thread t owns channel t % W of the block and the
+// tiles t / W, t / W + 256 / W, ... (fixed), the tile lanes are then summed in order.  Writes
+// S1, S2 per channel of the sample and the group's A, B.
 template <typename T>
-__global__ void gn_bwd_finalize_kernel(const float* __restrict__ tpart, const T* __restrict__ gamma,
-                                       float* __restrict__ sums, float* __restrict__ coef, const Geom g) {
-  __shared__ float sm1[8][33], sm2[8][33];
-  __shared__ float gs1[32], gs2[32];
+__global__ void __launch_bounds__(256)
+    gn_bwd_finalize_kernel(const float* __restrict__ tpart, const T* __restrict__ gamma, float* __restrict__ sums,
+                           float* __restrict__ coef, const Geom g) {
+  __shared__ float sm1[256], sm2[256];
+  __shared__ float scratch[8];
   const int n = blockIdx.x / g.G, grp = blockIdx.x - n * g.G;
-  const int lx = threadIdx.x, ly = threadIdx.y;
-  float w1 = 0.f, w2 = 0.f;  // gamma-weighted sums held by the (lx, ly == 0) threads
-  for (int cbase = 0; cbase < g.D; cbase += 32) {
+  int sh = 0;
+  while ((1 << sh) < g.D && sh < 5) ++sh;
+  const int W = 1 << sh, J = 256 >> sh;
+  const int lx = threadIdx.x & (W - 1), ly = threadIdx.x >> sh;
+  float w1 = 0.f, w2 = 0.f;  // gamma-weighted sums held by the ly == 0 threads
+  for (int cbase = 0; cbase < g.D; cbase += W) {
     const int cin = cbase + lx;
     const bool valid = cin < g.D;
     const int c = grp * g.D + cin;
     float a1 = 0.f, a2 = 0.f;
     if (valid) {
-      for (int chunk = ly; chunk < g.chunks; chunk += 8) {
+      for (int chunk = ly; chunk < g.chunks; chunk += J) {
         const float2 v = reinterpret_cast<const float2*>(tpart)[((size_t)n * g.chunks + chunk) * g.C + c];
         a1 += v.x;
         a2 += v.y;
       }
     }
-    sm1[ly][lx] = a1;
-    sm2[ly][lx] = a2;
+    sm1[threadIdx.x] = a1;
+    sm2[threadIdx.x] = a2;
     __syncthreads();
     if (ly == 0 && valid) {
       float t1 = 0.f, t2 = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        t1 += sm1[j][lx];
-        t2 += sm2[j][lx];
+      for (int j = 0; j < J; ++j) {
+        t1 += sm1[(j << sh) + lx];
+        t2 += sm2[(j << sh) + lx];
       }
       reinterpret_cast<float2*>(sums)[(size_t)n * g.C + c] = make_float2(t1, t2);
       const float ga = load_param<T>(gamma, c);
@@ -546,20 +569,12 @@ __global__ void gn_bwd_finalize_kernel(const float* __restrict__ tpart, const T*
     }
     __syncthreads();
   }
-  if (ly == 0) {
-    gs1[lx] = w1;
-    gs2[lx] = w2;
-  }
-  __syncthreads();
-  if (ly == 0 && lx == 0) {
-    float t1 = 0.f, t2 = 0.f;
-    for (int j = 0; j < 32; ++j) {
-      t1 += gs1[j];
-      t2 += gs2[j];
-    }
+  w1 = block_sum(w1, scratch);
+  w2 = block_sum(w2, scratch);
+  if (threadIdx.x == 0) {
     const float inv_m = 1.0f / ((float)g.D * (float)g.R);
-    coef[((size_t)n * g.G + grp) * 2] = t1 * inv_m;
-    coef[((size_t)n * g.G + grp) * 2 + 1] = t2 * inv_m;
+    coef[((size_t)n * g.G + grp) * 2] = w1 * inv_m;
+    coef[((size_t)n * g.G + grp) * 2 + 1] = w2 * inv_m;
   }
 }
 
@@ -648,7 +663,7 @@ static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t st
       (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, tpart, g);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  gn_bwd_finalize_kernel<T><<<(unsigned)(g.N * g.G), dim3(32, 8, 1), 0, stream>>>(tpart, (const T*)c.gamma, sums, coef,
+  gn_bwd_finalize_kernel<T><<<(unsigned)(g.N * g.G), 256, 0, stream>>>(tpart, (const T*)c.gamma, sums, coef,
                                                                                  g);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;

@@ -56,6 +56,20 @@ __device__ __forceinline__ Moments moments_warp_reduce(Moments v) {
   return v;
 }
 
+// Sum over a whole CTA in a fixed order (warp trees, then the warp results in warp order).
+// `scratch` holds one float per warp; the total is returned to every thread.
+__device__ __forceinline__ float warp_sum(float v);
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from a previous call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nwarps; ++w) t += scratch[w];
+  return t;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int delta = 16; delta >= 1; delta >>= 1) v += __shfl_down_sync(0xffffffffu, v, delta);

@@ -31,34 +31,47 @@ __device__ __forceinline__ void welford_step(const float (&f)[VE], float (&mean)
   }
 }
 
-// Per-thread running moments over the rows this thread owns (rows ty, ty + TY, ...), read straight
-// from global memory with U independent 16-byte loads in flight (multi-kernel path).
+constexpr int kRingDepth = 8;  // rows in flight per thread in the multi-kernel streaming kernels
+
+// Per-thread running moments over the rows this thread owns (rows ty, ty + TY, ...) in the
+// multi-kernel path.  16-byte vectors go through a shared-memory ring with cp.async: kRingDepth
+// rows per thread are in flight without holding registers; slot s of the thread lives at
+// ring + s * ring_stride.  Other vector widths use plain loads.
 template <typename T, int VE>
-__device__ __forceinline__ void stream_moments(const Pack<T, VE>* __restrict__ src, size_t row_stride_vec, int nrows,
-                                               int ty, int TY, float (&mean)[VE], float (&m2)[VE], float& cnt) {
-  constexpr int U = 8;
-  const size_t step = (size_t)TY * row_stride_vec;
-  const Pack<T, VE>* p = src + (size_t)ty * row_stride_vec;
-  int left = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
-  for (; left >= U; left -= U) {
-    Pack<T, VE> v[U];
+__device__ __forceinline__ void stream_moments(const T* __restrict__ gsrc, size_t gstep_elems, int iters,
+                                               uint32_t ring, uint32_t ring_stride, float (&mean)[VE],
+                                               float (&m2)[VE], float& cnt) {
+  if constexpr (sizeof(T) * VE == 16) {
+    const T* gp = gsrc;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      v[u] = ld_stream(p);
-      p += step;
+    for (int d = 0; d < kRingDepth; ++d) {
+      if (d < iters) {
+        cp_async16(ring + d * ring_stride, gp);
+        gp += gstep_elems;
+      }
+      cp_async_commit();
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int i = 0; i < iters; ++i) {
+      cp_async_wait<kRingDepth - 1>();
+      const uint32_t slot = ring + (i & (kRingDepth - 1)) * ring_stride;
       float f[VE];
-      unpack<T, VE>(v[u], f);
+      unpack16<T, VE>(lds128(slot), f);
+      if (i + kRingDepth < iters) {
+        cp_async16(slot, gp);
+        gp += gstep_elems;
+      }
+      cp_async_commit();
       welford_step<VE>(f, mean, m2, cnt);
     }
-  }
-  for (; left > 0; --left) {
-    float f[VE];
-    unpack<T, VE>(ld_stream(p), f);
-    p += step;
-    welford_step<VE>(f, mean, m2, cnt);
+  } else {
+    const T* gp = gsrc;
+    for (int i = 0; i < iters; ++i) {
+      float f[VE];
+#pragma unroll
+      for (int e = 0; e < VE; ++e) f[e] = load_param<T>(gp, e);
+      gp += gstep_elems;
+      welford_step<VE>(f, mean, m2, cnt);
+    }
   }
 }
 
@@ -356,7 +369,9 @@ __global__ void __launch_bounds__(kMaxThreads)
     gn_fwd_stats_kernel(const T* __restrict__ x, float* __restrict__ wpart, const Geom g) {
   extern __shared__ uint4 smem_raw[];
   using P = Pack<T, VE>;
-  float* red = reinterpret_cast<float*>(smem_raw);
+  // [ring: kRingDepth * blockDim vectors][red][tmp][slot]
+  const size_t ring_bytes = sizeof(T) * VE == 16 ? (size_t)kRingDepth * blockDim.x * 16 : 0;
+  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + ring_bytes);
   float* tmp = red + g.TY * g.CW;
   float* slot = tmp + g.slots;
 
@@ -373,9 +388,10 @@ __global__ void __launch_bounds__(kMaxThreads)
   float mean[VE], m2[VE], cnt = 0.f;
 #pragma unroll
   for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
-  const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
-  if (streaming)
-    stream_moments<T, VE>(reinterpret_cast<const P*>(x + base), (size_t)g.C / VE, nrows, ty, g.TY, mean, m2, cnt);
+  const size_t base = ((size_t)n * g.R + r0 + ty) * g.C + c0 + (size_t)tx * VE;
+  const int iters = (streaming && ty < nrows) ? (nrows - ty + g.TY - 1) / g.TY : 0;
+  stream_moments<T, VE>(x + base, (size_t)g.TY * g.C, iters, smem_addr(smem_raw) + tid * 16, blockDim.x * 16, mean, m2,
+                        cnt);
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
   cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
@@ -387,38 +403,40 @@ __global__ void __launch_bounds__(kMaxThreads)
   }
 }
 
-// two-pass, kernel 2: one warp per (n, group) merges all partials that cover the group, in two
-// sweeps (mean first, then squared deviations around it); lane order and tree are fixed.
-__global__ void gn_fwd_finalize_kernel(const float* __restrict__ wpart, float* __restrict__ mean_out,
-                                       float* __restrict__ rstd_out, float eps, const Geom g) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= g.N * g.G) return;
-  const int n = warp / g.G, grp = warp - n * g.G;
+// two-pass, kernel 2: one CTA per (n, group) merges all partials that cover the group, in two
+// sweeps (mean first, then squared deviations around it).  Every thread owns a fixed subset of
+// the partials and the CTA-wide sums use a fixed tree, so the result is reproducible.
+__global__ void __launch_bounds__(256)
+    gn_fwd_finalize_kernel(const float* __restrict__ wpart, float* __restrict__ mean_out,
+                           float* __restrict__ rstd_out, float eps, const Geom g) {
+  __shared__ float scratch[8];
+  const int n = blockIdx.x / g.G, grp = blockIdx.x - n * g.G;
   const int cb_lo = (grp * g.D) / g.CW, cb_hi = ((grp + 1) * g.D - 1) / g.CW;
   const int ncov = cb_hi - cb_lo + 1;
+  const int total = ncov * g.chunks;
   float wsum = 0.f, ntot = 0.f;
-  for (int i = lane; i < ncov * g.chunks; i += 32) {
-    const int cb = cb_lo + i % ncov, chunk = i / ncov;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int chunk = i / ncov, cb = cb_lo + (i - chunk * ncov);
     const int s = grp - (cb * g.CW) / g.D;
     const float* p = wpart + ((((size_t)n * g.chunks + chunk) * g.ncb + cb) * g.slots + s) * 3;
     wsum = fmaf(p[2], p[0], wsum);
     ntot += p[2];
   }
-  wsum = __shfl_sync(0xffffffffu, warp_sum(wsum), 0);
-  ntot = __shfl_sync(0xffffffffu, warp_sum(ntot), 0);
+  wsum = block_sum(wsum, scratch);
+  ntot = block_sum(ntot, scratch);
   const float mu = wsum / ntot;
   float m2 = 0.f;
-  for (int i = lane; i < ncov * g.chunks; i += 32) {
-    const int cb = cb_lo + i % ncov, chunk = i / ncov;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int chunk = i / ncov, cb = cb_lo + (i - chunk * ncov);
     const int s = grp - (cb * g.CW) / g.D;
     const float* p = wpart + ((((size_t)n * g.chunks + chunk) * g.ncb + cb) * g.slots + s) * 3;
     const float d = p[0] - mu;
     m2 += fmaf(p[2] * d, d, p[1]);
   }
-  m2 = warp_sum(m2);
-  if (lane == 0) {
-    mean_out[warp] = mu;
-    rstd_out[warp] = rsqrtf(fmaxf(m2 / ntot, 0.f) + eps);
+  m2 = block_sum(m2, scratch);
+  if (threadIdx.x == 0) {
+    mean_out[blockIdx.x] = mu;
+    rstd_out[blockIdx.x] = rsqrtf(fmaxf(m2 / ntot, 0.f) + eps);
   }
 }
 
@@ -479,10 +497,7 @@ static cudaError_t launch_two_pass(const FwdCall& c, const Plan& p, cudaStream_t
   gn_fwd_stats_kernel<T, VE, UNI><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>((const T*)c.x, wpart, p.geom);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  const int warps = p.geom.N * p.geom.G;
-  const int fin_threads = 128;
-  const unsigned fin_blocks = (unsigned)(((size_t)warps * 32 + fin_threads - 1) / fin_threads);
-  gn_fwd_finalize_kernel<<<fin_blocks, fin_threads, 0, stream>>>(wpart, c.mean, c.rstd, c.eps, p.geom);
+  gn_fwd_finalize_kernel<<<(unsigned)(p.geom.N * p.geom.G), 256, 0, stream>>>(wpart, c.mean, c.rstd, c.eps, p.geom);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   gn_fwd_apply_kernel<T, VE, ACT, UNI><<<(unsigned)p.grid, p.threads, 0, stream>>>(

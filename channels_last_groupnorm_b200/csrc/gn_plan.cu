@@ -89,9 +89,8 @@ void thread_layout(int CV, int rows_per_cta, int target_threads, int* TY, int* t
 // One fused candidate: column block of `cw` channels split over a cluster of `k` CTAs.
 // Returns false if the tile does not fit; otherwise fills *out and a heuristic score
 // (higher is better): SMs kept busy x row-segment efficiency x co-residency.
-bool plan_fused_candidate(const Shape& sh, int cw, int k, Plan* out, double* score) {
+bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Plan* out, double* score) {
   const int ve = sh.ve, s = sh.s;
-  const int target_threads = env_int("GNB200_THREADS", 128);
   const int ncb = sh.C / cw;
   const int CV = cw / ve;
   const int ntiles = sh.direction == 0 ? 1 : 2;
@@ -100,6 +99,8 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, Plan* out, double* sco
   if (k > 1 && (long long)rows * (k - 1) >= sh.R) return false;  // a CTA of the cluster would be idle
   int TY, threads;
   thread_layout(CV, rows, target_threads, &TY, &threads);
+  // larger CTAs only pay when every thread still owns >= 16 rows (per-thread set-up is amortised)
+  if (target_threads > 128 && env_int("GNB200_THREADS", 0) == 0 && rows / TY < 16) return false;
   const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15) * ntiles;
   const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots, threads) : bwd_fold_floats(cw, TY, slots, threads)) * 4;
   if (tile + fold > kSmemMaxOptin - 1024) return false;
@@ -122,14 +123,19 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, Plan* out, double* sco
   // per SM matter most, then rows per thread (per-thread set-up is amortised over them), then the
   // contiguous row segment (64 B is nearly as good as 128 B; 32 B wastes DRAM sectors).
   const long long seg = (long long)cw * s;
-  const double seg_eff = seg >= 128 ? 1.0 : seg >= 64 ? 0.95 : seg >= 32 ? 0.7 : 0.4;
+  const double seg_eff = seg >= 128 ? 1.0 : seg >= 64 ? 0.95 : seg >= 32 ? 0.5 : 0.3;
   const double sms = (double)(p.grid < kSmCount ? p.grid : kSmCount);
   int per_sm = (int)(kSmemMaxOptin / (tile + fold + 1024));
   const int by_threads = 2048 / threads;
   if (per_sm > by_threads) per_sm = by_threads;
-  if (per_sm > 8) per_sm = 8;
-  static const double occ_tab[9] = {0.3, 0.55, 0.75, 0.86, 0.93, 0.97, 1.0, 1.0, 1.0};
-  const double occ = p.grid <= kSmCount ? 1.0 : occ_tab[per_sm];
+  const long long per_sm_by_grid = (p.grid + kSmCount - 1) / kSmCount;  // a small grid leaves SMs half empty
+  if (per_sm > per_sm_by_grid) per_sm = (int)per_sm_by_grid;
+  // resident warps per SM hide latency: ~24 are enough, 4 are far too few
+  const int warps = per_sm * (threads / 32);
+  const double occ_w = warps >= 24 ? 1.0 : warps >= 16 ? 0.93 : warps >= 12 ? 0.86 : warps >= 8 ? 0.72 : warps >= 4 ? 0.5 : 0.3;
+  // ... and several CTAs per SM interleave their load / reduce / store phases
+  const double occ_c = per_sm >= 6 ? 1.0 : per_sm >= 4 ? 0.96 : per_sm == 3 ? 0.92 : per_sm == 2 ? 0.85 : 0.7;
+  const double occ = occ_w * occ_c;
   const int rpt = rows / TY;
   const double rpt_eff = rpt >= 16 ? 1.0 : rpt >= 8 ? 0.93 : rpt >= 4 ? 0.85 : 0.75;
   const double sync_eff = 1.0 - 0.004 * k;  // mild preference for smaller clusters
@@ -144,6 +150,7 @@ bool plan_fused(const Shape& sh, Plan* out) {
   const int units = (int)(sh.C / U);
   const int force_cw = env_int("GNB200_CW", 0);
   const int force_k = env_int("GNB200_K", 0);
+  const int force_threads = env_int("GNB200_THREADS", 0);
   const int k_max = force_k == 16 ? 16 : 8;  // 16 needs the non-portable cluster size: opt-in only
   bool found = false;
   double best = -1.0;
@@ -154,13 +161,16 @@ bool plan_fused(const Shape& sh, Plan* out) {
     if (force_cw > 0 && w != force_cw) continue;
     for (int k = 1; k <= k_max; k *= 2) {
       if (force_k > 0 && k != force_k) continue;
-      Plan cand;
-      double score;
-      if (!plan_fused_candidate(sh, (int)w, k, &cand, &score)) continue;
-      if (score > best * 1.0001) {
-        best = score;
-        *out = cand;
-        found = true;
+      for (int threads = 128; threads <= 512; threads *= 2) {
+        if (force_threads > 0 && threads != 128) continue;
+        Plan cand;
+        double score;
+        if (!plan_fused_candidate(sh, (int)w, k, force_threads > 0 ? force_threads : threads, &cand, &score)) continue;
+        if (score > best * 1.0001) {
+          best = score;
+          *out = cand;
+          found = true;
+        }
       }
     }
   }
@@ -210,12 +220,14 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
   p.threads = threads;
   p.grid = (long long)sh.N * chunks * ncb;
   if (p.grid > 0x7fffffffLL) return false;
+  // shared-memory rings of the streaming kernels: 8 rows x 16 bytes per thread (x; x and dy)
+  const size_t ring = ve > 1 ? (size_t)8 * threads * 16 : 0;
   if (sh.direction == 0) {
-    p.smem_bytes = fwd_fold_floats(cw, TY, slots, threads) * 4;
+    p.smem_bytes = ring + fwd_fold_floats(cw, TY, slots, threads) * 4;
     p.ws_bytes = (size_t)p.grid * slots * 3 * sizeof(float);
     p.launches = 3;
   } else {
-    p.smem_bytes = bwd_fold_floats(cw, TY, slots, threads) * 4;
+    p.smem_bytes = 2 * ring + bwd_fold_floats(cw, TY, slots, threads) * 4;
     p.ws_bytes = ((size_t)sh.N * chunks * sh.C * 2 + (size_t)sh.N * sh.C * 2 + (size_t)sh.N * sh.G * 2) * sizeof(float);
     p.launches = 4;
   }
