@@ -118,7 +118,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -139,7 +139,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         for ts, line in self.lines:
-            if t0 is not None and not (t0 - 0.05 <= ts <= t1 + 0.15):
+            if t0 is not None and not (t0 - 0.02 <= ts <= t1 + 0.04):
                 continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
@@ -311,22 +311,51 @@ class DeviceProblem:
                                      self.ws_b.data_ptr() if self.wb else None, self.wb, stream))
 
 
-def run_device_steps(prob, steps, warmup, world, barrier):
-    """Returns (seconds per step max over ranks, mean fwd seconds, mean bwd seconds)."""
+def _capture(fn, count):
+    """Captures `count` calls fn(i) into one CUDA graph (on a side stream). Returns the graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(count):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(side)
+    return graph
+
+
+def _time_graph(graph, barrier):
+    """Device time of one replay: barrier + synchronize on both sides, CUDA events around it."""
+    barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    a.record()
+    graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    barrier()
+    return a.elapsed_time(b) * 1e-3, (t0, t1)
+
+
+def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
+    """Times exactly `steps` steps (forward, backward, all-reduce of the parameter gradients).
+
+    Returns (seconds per step, max over ranks; mean forward seconds; mean backward seconds; wall
+    interval of the timed region; how the loop was issued).  The K steps are captured once into a
+    CUDA graph and replayed, so that host launch overhead does not enter the device time; the
+    forward-only and backward-only graphs give the per-kernel durations for the roofline.  If
+    capture is not possible the same loop runs eagerly with events around every call.
+    """
     import torch.distributed as dist
 
-    stream = torch.cuda.current_stream().cuda_stream
+    def cur():
+        return torch.cuda.current_stream().cuda_stream
 
-    def one(i, ev=None):
-        if ev:
-            ev[0].record()
-        prob.fwd(i, stream)
-        if ev:
-            ev[1].record()
+    def one(i):
+        prob.fwd(i, cur())
         if prob.bwd:
-            prob.bwd_(i, stream, typed=(world == 1))
-            if ev:
-                ev[2].record()
+            prob.bwd_(i, cur(), typed=(world == 1))
             if world > 1:
                 dist.all_reduce(prob.dparam)
                 prob.dgamma.copy_(prob.dparam[0])
@@ -334,6 +363,32 @@ def run_device_steps(prob, steps, warmup, world, barrier):
 
     for i in range(warmup):
         one(i)
+    torch.cuda.synchronize()
+
+    def reduce_max(v):
+        if world > 1:
+            t = torch.tensor([v], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return v
+
+    if use_graph:
+        try:
+            g_step = _capture(lambda i: one(warmup + i), steps)
+            g_fwd = _capture(lambda i: prob.fwd(i, cur()), steps)
+            g_bwd = _capture(lambda i: prob.bwd_(i, cur(), typed=True), steps) if prob.bwd else None
+            for g in (g_step, g_fwd, g_bwd):  # one untimed replay each
+                if g is not None:
+                    g.replay()
+            torch.cuda.synchronize()
+            total, wall = _time_graph(g_step, barrier)
+            fwd_t = _time_graph(g_fwd, barrier)[0] / steps
+            bwd_t = _time_graph(g_bwd, barrier)[0] / steps if g_bwd is not None else 0.0
+            return reduce_max(total / steps), fwd_t, bwd_t, wall, "cuda-graph"
+        except Exception as exc:  # pragma: no cover - depends on driver / NCCL capture support
+            sys.stderr.write("bench: CUDA-graph capture failed (%s); timing the eager loop\n" % str(exc)[:200])
+            torch.cuda.synchronize()
+
     barrier()
     torch.cuda.synchronize()
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
@@ -341,7 +396,16 @@ def run_device_steps(prob, steps, warmup, world, barrier):
     t_wall0 = time.time()
     start.record()
     for i in range(steps):
-        one(warmup + i, evs[i])
+        evs[i][0].record()
+        prob.fwd(warmup + i, cur())
+        evs[i][1].record()
+        if prob.bwd:
+            prob.bwd_(warmup + i, cur(), typed=(world == 1))
+            evs[i][2].record()
+            if world > 1:
+                dist.all_reduce(prob.dparam)
+                prob.dgamma.copy_(prob.dparam[0])
+                prob.dbeta.copy_(prob.dparam[1])
     stop.record()
     torch.cuda.synchronize()
     t_wall1 = time.time()
@@ -349,12 +413,7 @@ def run_device_steps(prob, steps, warmup, world, barrier):
     total = start.elapsed_time(stop) * 1e-3
     fwd_t = sum(e[0].elapsed_time(e[1]) for e in evs) * 1e-3 / steps
     bwd_t = sum(e[1].elapsed_time(e[2]) for e in evs) * 1e-3 / steps if prob.bwd else 0.0
-    per_step = total / steps
-    if world > 1:
-        t = torch.tensor([per_step], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        per_step = float(t.item())
-    return per_step, fwd_t, bwd_t, (t_wall0, t_wall1)
+    return reduce_max(total / steps), fwd_t, bwd_t, (t_wall0, t_wall1), "eager"
 
 
 def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
@@ -445,7 +504,8 @@ def device_arm(args):
     if rank == 0:
         sampler.start()
     prob = DeviceProblem(wl, n_local, x, ga, be, dy)
-    per_step, fwd_t, bwd_t, wall = run_device_steps(prob, args.steps, args.warmup, world, barrier)
+    per_step, fwd_t, bwd_t, wall, issue_mode = run_device_steps(prob, args.steps, args.warmup, world, barrier,
+                                                                use_graph=not args.no_graph)
     clocks = sampler.stop(*wall) if rank == 0 else None
     del prob
     torch.cuda.empty_cache()
@@ -482,7 +542,7 @@ def device_arm(args):
                     "api": "GN_NHWC module + autograd, pinned host buffers"},
             "gpu_launches": args.steps * (nt.launch_count(n_local, H * W, C, G, dtype, 0)
                                           + (nt.launch_count(n_local, H * W, C, G, dtype, 1) if bwd else 0)),
-            "clocks": clocks,
+            "clocks": clocks, "issue": issue_mode,
         }
         if world == 1 and not args.no_cpu:
             n_sample = min(N, 8)
@@ -506,17 +566,30 @@ NCU_TRAFFIC = {}
 # sweep over every benchmark shape (1 GPU): ours vs torch CUDA vs reference kernels vs CPU
 # ------------------------------------------------------------------------------------------------
 def time_cuda(fn, iters=20, reps=5, warmup=5):
+    """Median / min seconds per call of fn(i).  The `iters` calls are captured into one CUDA graph
+    and replayed (device time without host launch overhead); falls back to an eager loop."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
+    graph = None
+    try:
+        graph = _capture(lambda i: fn(warmup + i), iters)
+        graph.replay()
+        torch.cuda.synchronize()
+    except Exception:
+        graph = None
+        torch.cuda.synchronize()
     out = []
     k = warmup
     for _ in range(reps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(iters):
-            fn(k)
-            k += 1
+        if graph is not None:
+            graph.replay()
+        else:
+            for _ in range(iters):
+                fn(k)
+                k += 1
         b.record()
         torch.cuda.synchronize()
         out.append(a.elapsed_time(b) * 1e-3 / iters)
@@ -546,12 +619,13 @@ def sweep(args):
         rec = {"workload": wl, "config": workload_config(wl, 1)["workload"], "plan_fwd": nt.describe_plan(N, H * W, C, G, dtype, 0),
                "plan_bwd": nt.describe_plan(N, H * W, C, G, dtype, 1) if bwd else None, "nsets": prob.nsets,
                "peak_GBps": peak, "peak_kind": peak_kind}
-        t, tmin = time_cuda(lambda i: prob.fwd(i, stream))
+        cur = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731  (the capture stream inside a graph)
+        t, tmin = time_cuda(lambda i: prob.fwd(i, cur()))
         rec["ours_fwd_us"] = t * 1e6
         rec["ours_fwd_GBps"] = 2 * E * esize / t / 1e9
         rec["ours_fwd_frac"] = rec["ours_fwd_GBps"] / peak
         if bwd:
-            t, tmin = time_cuda(lambda i: prob.bwd_(i, stream, True))
+            t, tmin = time_cuda(lambda i: prob.bwd_(i, cur(), True))
             rec["ours_bwd_us"] = t * 1e6
             rec["ours_bwd_GBps"] = 3 * E * esize / t / 1e9
             rec["ours_bwd_frac"] = rec["ours_bwd_GBps"] / peak
@@ -631,6 +705,7 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ref", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time the eager loop instead of a CUDA-graph replay")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--profile", type=int, default=0, metavar="CALLS",
                     help="profiling target: CALLS forward(+backward) calls of --workload through the C ABI, nothing else")

@@ -547,6 +547,7 @@ __global__ void __launch_bounds__(256)
     const int c = grp * g.D + cin;
     float a1 = 0.f, a2 = 0.f;
     if (valid) {
+#pragma unroll 8
       for (int chunk = ly; chunk < g.chunks; chunk += J) {
         const float2 v = reinterpret_cast<const float2*>(tpart)[((size_t)n * g.chunks + chunk) * g.C + c];
         a1 += v.x;

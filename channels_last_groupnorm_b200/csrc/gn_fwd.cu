@@ -415,6 +415,7 @@ __global__ void __launch_bounds__(256)
   const int ncov = cb_hi - cb_lo + 1;
   const int total = ncov * g.chunks;
   float wsum = 0.f, ntot = 0.f;
+#pragma unroll 4
   for (int i = threadIdx.x; i < total; i += blockDim.x) {
     const int chunk = i / ncov, cb = cb_lo + (i - chunk * ncov);
     const int s = grp - (cb * g.CW) / g.D;
@@ -426,6 +427,7 @@ __global__ void __launch_bounds__(256)
   ntot = block_sum(ntot, scratch);
   const float mu = wsum / ntot;
   float m2 = 0.f;
+#pragma unroll 4
   for (int i = threadIdx.x; i < total; i += blockDim.x) {
     const int chunk = i / ncov, cb = cb_lo + (i - chunk * ncov);
     const int s = grp - (cb * g.CW) / g.D;

@@ -189,15 +189,15 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
   int slots = (cw - 1) / sh.D + 2;
   if (slots > sh.G) slots = sh.G;
 
-  // rows per CTA tile: large tiles amortise the per-CTA reduction (up to 512 KB of x per tile),
-  // but at least ~4 tiles per SM when the problem allows
+  // rows per CTA tile: large tiles amortise the per-thread set-up and the per-CTA reduction (about
+  // three tiles per SM, up to 512 KB of x per tile), but at least ~4 tiles per SM when the problem allows
   const long long row_bytes = (long long)cw * s;
-  long long tile_target = (long long)sh.N * sh.R * sh.C * s / (8LL * kSmCount);
+  long long tile_target = (long long)sh.N * sh.R * sh.C * s / (3LL * kSmCount);
   if (tile_target < 64 * 1024) tile_target = 64 * 1024;
   if (tile_target > 512 * 1024) tile_target = 512 * 1024;
   long long rows = (tile_target + row_bytes - 1) / row_bytes;
   if (rows > sh.R) rows = sh.R;
-  const long long want_tiles = 4LL * kSmCount;
+  const long long want_tiles = 2LL * kSmCount;
   long long chunks = (sh.R + rows - 1) / rows;
   if ((long long)sh.N * ncb * chunks < want_tiles) {
     long long need = (want_tiles + (long long)sh.N * ncb - 1) / ((long long)sh.N * ncb);
