@@ -417,7 +417,13 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
 
 
 def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
-    """Public API (module + autograd) with host buffers; copies inside the timed region."""
+    """Public API (module + autograd) with host buffers; every step copies its x and dy from pinned
+    host memory and its y, dx, dgamma, dbeta back, all inside the timed region.
+
+    The three legs of a step run on three streams (copy-in, compute, copy-out) over two sets of
+    device buffers, so the upload of step i+1 and the download of step i-1 overlap the kernels of
+    step i, as in an input pipeline; every byte still crosses PCIe once per step.
+    """
     import torch.distributed as dist
 
     import channels_last_groupnorm_b200 as pkg
@@ -431,35 +437,65 @@ def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
         m.weight.copy_(ga)
         m.bias.copy_(be)
     xh, dyh = x.pin_memory(), dy.pin_memory()
-    yh = torch.empty_like(xh).pin_memory()
-    dxh = torch.empty_like(xh).pin_memory()
-    dgh = torch.empty(C, dtype=dtype).pin_memory()
-    dbh = torch.empty(C, dtype=dtype).pin_memory()
-    xd = torch.empty(x.shape, dtype=dtype, device=dev)
-    dyd = torch.empty(x.shape, dtype=dtype, device=dev)
+    yh = [torch.empty_like(xh).pin_memory() for _ in range(2)]
+    dxh = [torch.empty_like(xh).pin_memory() for _ in range(2)]
+    dgh = [torch.empty(C, dtype=dtype).pin_memory() for _ in range(2)]
+    dbh = [torch.empty(C, dtype=dtype).pin_memory() for _ in range(2)]
+    xd = [torch.empty(x.shape, dtype=dtype, device=dev) for _ in range(2)]
+    dyd = [torch.empty(x.shape, dtype=dtype, device=dev) for _ in range(2)]
+    s_in, s_comp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    used = [False, False]
 
-    def one():
-        xd.copy_(xh, non_blocking=True)
-        xin = xd.permute(0, 3, 1, 2).detach().requires_grad_(bwd)
-        y = m(xin)
-        yh.copy_(y.detach().permute(0, 2, 3, 1), non_blocking=True)
-        if bwd:
-            dyd.copy_(dyh, non_blocking=True)
-            m.weight.grad = None
-            m.bias.grad = None
-            y.backward(dyd.permute(0, 3, 1, 2))
-            dxh.copy_(xin.grad.permute(0, 2, 3, 1), non_blocking=True)
-            dgh.copy_(m.weight.grad, non_blocking=True)
-            dbh.copy_(m.bias.grad, non_blocking=True)
+    def one(i):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            if used[b]:
+                s_in.wait_event(ev_comp[b])  # the device input buffers of this slot are free again
+            xd[b].copy_(xh, non_blocking=True)
+            if bwd:
+                dyd[b].copy_(dyh, non_blocking=True)
+            ev_in[b].record(s_in)
+        with torch.cuda.stream(s_comp):
+            s_comp.wait_event(ev_in[b])
+            xin = xd[b].permute(0, 3, 1, 2).detach().requires_grad_(bwd)
+            y = m(xin)
+            if bwd:
+                m.weight.grad = None
+                m.bias.grad = None
+                y.backward(dyd[b].permute(0, 3, 1, 2))
+            ev_comp[b].record(s_comp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[b])
+            if used[b]:
+                s_out.wait_event(ev_out[b])
+            results = [(yh[b], y.detach().permute(0, 2, 3, 1))]
+            if bwd:
+                results += [(dxh[b], xin.grad.permute(0, 2, 3, 1)), (dgh[b], m.weight.grad), (dbh[b], m.bias.grad)]
+            for host, devt in results:
+                devt.record_stream(s_out)
+                host.copy_(devt, non_blocking=True)
+            ev_out[b].record(s_out)
+        used[b] = True
 
-    for _ in range(warmup):
-        one()
+    def drain():
+        for st in (s_in, s_comp, s_out):
+            torch.cuda.current_stream().wait_stream(st)
+
+    for i in range(warmup):
+        one(i)
+    drain()
     barrier()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(steps):
-        one()
+    for st in (s_in, s_comp, s_out):
+        st.wait_event(start)
+    for i in range(steps):
+        one(warmup + i)
+    drain()
     stop.record()
     torch.cuda.synchronize()
     barrier()
@@ -539,7 +575,8 @@ def device_arm(args):
             "roofline": roof, "roofline_fwd": roof_fwd,
             "e2e": {"value": alg_global / e2e_t / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_t * 1e3, "steps": e2e_steps,
-                    "api": "GN_NHWC module + autograd, pinned host buffers"},
+                    "api": "GN_NHWC module + autograd, pinned host buffers; copy-in / compute / copy-out on three "
+                           "streams, two buffer sets"},
             "gpu_launches": args.steps * (nt.launch_count(n_local, H * W, C, G, dtype, 0)
                                           + (nt.launch_count(n_local, H * W, C, G, dtype, 1) if bwd else 0)),
             "clocks": clocks, "issue": issue_mode,

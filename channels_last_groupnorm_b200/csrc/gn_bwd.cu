@@ -335,7 +335,7 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
 // ------------------------------------------------------------------------------------------------
 // fused kernel.  grid.x = N * ncb * k, cluster (k,1,1).
 // dynamic smem: [x tile][dy tile][red 2*TY*CW][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
-// scratch out : sums[(n * C + c) * 2 + {0,1}] = S1, S2 of the whole sample
+// scratch out : sums[((n * k + rank) * C + c) * 2 + {0,1}] = S1, S2 over this CTA's rows
 // ------------------------------------------------------------------------------------------------
 template <typename T, int VE, int ACT, bool UNI>
 __global__ void __launch_bounds__(kMaxThreads)
@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   P* tile_x = reinterpret_cast<P*>(smem_raw);
   P* tile_dy = reinterpret_cast<P*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + 2 * tile_bytes);
-  float* part = red + 2 * g.TY * g.CW;
+  float* part = red + g.red_floats;
   float* chan = part + 2 * max((int)blockDim.x, g.CW);
   float* spart = chan + 2 * g.CW;  // [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 over this CTA's rows
   float* coef = spart + 2 * g.slots;  // A[s], B[slots + s]
@@ -377,12 +377,31 @@ __global__ void __launch_bounds__(kMaxThreads)
     lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
     tile_fill_bwd_sums<T, VE, ACT>(x + base, dy + base, gstep, sx, sd, sstep, iters, L, s1, s2);
   }
-  cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
 
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
   const int c_valid = min(g.CW, g.C - c0);
-  {  // gamma-weighted group sums of this CTA's rows: one warp per group, fixed lane order
+  const bool shuf = UNI && g.shuf;
+  if (shuf) {
+    // gamma-weighted group sums straight from registers: xor-butterflies + one pass over the warps
+    float a1 = 0.f, a2 = 0.f;
+    if (streaming) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        a1 = fmaf(L.ga[e], s1[e], a1);
+        a2 = fmaf(L.ga[e], s2[e], a2);
+      }
+    }
+    const float t1 = cta_slot_sum_shuf(g, a1, tx, red);
+    const float t2 = cta_slot_sum_shuf(g, a2, tx, red + 512);
+    if (tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
+      const int s = tid >> g.tps_shift;
+      spart[2 * s] = t1;
+      spart[2 * s + 1] = t2;
+    }
+  } else {
+    cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
+    // gamma-weighted group sums of this CTA's rows: one warp per group, fixed lane order
     const int warp = tid >> 5, lane = tid & 31, nwarps = (blockDim.x + 31) >> 5;
     for (int s = warp; s < n_slots; s += nwarps) {
       const int lo = max((g_lo + s) * g.D, c0) - c0;
@@ -401,30 +420,29 @@ __global__ void __launch_bounds__(kMaxThreads)
       }
     }
   }
-  cluster_sync_all();
+  cluster_arrive();  // publishes spart
+  // Channel sums of this CTA's rows go to scratch (summed over samples and cluster ranks by the
+  // parameter-gradient kernel).  On the shuffle path this work overlaps the wait for the peers.
+  if (shuf) cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
+  {
+    float2* out = reinterpret_cast<float2*>(sums) + (((size_t)n * k + rank) * g.C + c0);
+    for (int c = tid; c < c_valid; c += blockDim.x) out[c] = make_float2(chan[c], chan[g.CW + c]);
+  }
+  cluster_wait();
 
   const float inv_m = 1.0f / ((float)g.D * (float)g.R);
+  float* stage = red;  // k * 2 * slots floats: the peers' group sums, gathered in parallel
+  cluster_gather(spart, 2 * g.slots, k, stage);
   for (int s = tid; s < n_slots; s += blockDim.x) {
     float a1 = 0.f, a2 = 0.f;
     for (unsigned q = 0; q < k; ++q) {
-      a1 += dsmem_ld_f32(spart + 2 * s, q);
-      a2 += dsmem_ld_f32(spart + 2 * s + 1, q);
+      a1 += stage[q * 2 * g.slots + 2 * s];
+      a2 += stage[q * 2 * g.slots + 2 * s + 1];
     }
     coef[s] = a1 * inv_m;
     coef[g.slots + s] = a2 * inv_m;
   }
-  // whole-sample channel sums: channel c is summed (rank order) by CTA c % k
-  for (int c = tid; c < c_valid; c += blockDim.x) {
-    if ((unsigned)c % k != rank) continue;
-    float t1 = 0.f, t2 = 0.f;
-    for (unsigned q = 0; q < k; ++q) {
-      t1 += dsmem_ld_f32(chan + c, q);
-      t2 += dsmem_ld_f32(chan + g.CW + c, q);
-    }
-    float2* out = reinterpret_cast<float2*>(sums) + ((size_t)n * g.C + c0 + c);
-    *out = make_float2(t1, t2);
-  }
-  cluster_arrive();
+  cluster_arrive();  // this CTA no longer reads its peers' shared memory
   __syncthreads();
 
   if (streaming) {
@@ -448,7 +466,8 @@ __global__ void __launch_bounds__(kMaxThreads)
 }
 
 // ------------------------------------------------------------------------------------------------
-// parameter gradients:  dbeta_c = sum_n S1[n,c],  dgamma_c = sum_n S2[n,c]  (n ascending per lane,
+// parameter gradients:  dbeta_c = sum_n S1[n,c],  dgamma_c = sum_n S2[n,c]  over the N rows of `sums`
+// (one per sample, or per sample and cluster rank; ascending per lane,
 // then a fixed tree over the 8 row lanes).  block (32, 8), grid ceil(C / 32).
 // ------------------------------------------------------------------------------------------------
 template <typename T>
@@ -495,7 +514,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   // [ring x][ring dy] (kRingDepth * blockDim vectors each) [red][part][chan]
   const size_t ring_bytes = sizeof(T) * VE == 16 ? (size_t)kRingDepth * blockDim.x * 16 : 0;
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + 2 * ring_bytes);
-  float* part = red + 2 * g.TY * g.CW;
+  float* part = red + g.red_floats;
   float* chan = part + 2 * max((int)blockDim.x, g.CW);
   const int tile_id = blockIdx.x;
   const int t1 = g.div_ncb.div(tile_id), cb = tile_id - t1 * g.ncb;
@@ -622,10 +641,10 @@ __global__ void __launch_bounds__(kMaxThreads)
 // host-side launchers
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-static cudaError_t launch_param(const BwdCall& c, const float* sums, const Geom& g, cudaStream_t stream) {
+static cudaError_t launch_param(const BwdCall& c, const float* sums, int rows, const Geom& g, cudaStream_t stream) {
   const dim3 block(32, 8, 1);
   const unsigned blocks = (unsigned)((g.C + 31) / 32);
-  gn_bwd_param_kernel<T><<<blocks, block, 0, stream>>>(sums, g.N, g.C, c.dparam_f32, (T*)c.dgamma, (T*)c.dbeta);
+  gn_bwd_param_kernel<T><<<blocks, block, 0, stream>>>(sums, rows, g.C, c.dparam_f32, (T*)c.dgamma, (T*)c.dbeta);
   return cudaGetLastError();
 }
 
@@ -652,7 +671,7 @@ static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t st
     err = cudaLaunchKernelEx(&cfg, kern, (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean,
                              c.rstd, (T*)c.dx, sums, g);
     if (err != cudaSuccess) return err;
-    return launch_param<T>(c, sums, g, stream);
+    return launch_param<T>(c, sums, g.N * g.k, g, stream);
   }
   // two-pass scratch: [tile partials N*chunks*C*2][sums N*C*2][coef N*G*2]
   float* tpart = reinterpret_cast<float*>(c.workspace);
@@ -668,7 +687,7 @@ static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t st
                                                                                  g);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  err = launch_param<T>(c, sums, g, stream);
+  err = launch_param<T>(c, sums, g.N, g, stream);
   if (err != cudaSuccess) return err;
   gn_bwd_apply_kernel<T, VE, ACT, UNI><<<(unsigned)p.grid, p.threads, 0, stream>>>(
       (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, coef, (T*)c.dx, g);

@@ -549,6 +549,10 @@ struct Geom {
   int slots;         // upper bound on the groups a column block touches
   int k;             // cluster size of the fused kernels (== chunks there)
   FastDiv div_D, div_CV, div_CW, div_ncb, div_chunks;
+  // Shuffle reductions (fused kernels): usable when every vector lies in one group, CV and the
+  // threads per group row (D / VE) are powers of two and CV <= 32.  tps_shift = log2(D / VE).
+  int shuf, tps_shift;
+  int red_floats;  // size of the reduction scratch `red` (forward kernels), set by the planner
 };
 
 // Groups touched by column block starting at channel c0 (width CW, clipped to C):
@@ -598,6 +602,37 @@ __device__ __forceinline__ void cta_group_sum(const Geom& g, const float (&val)[
       for (int c = cl; c < w; c += (1 << sh)) acc += red[j * cols + lo + c];
     acc = warp_sum(acc);
     if (lane == 0) out[s] = acc;
+  }
+  __syncthreads();
+}
+
+// Sum of one value per thread over the CTA, per group slot, for the shuffle geometry (Geom::shuf):
+// lanes of a warp that share a slot are combined with xor-butterflies (identical result in every
+// lane), warp results go through `wsum` (nwarps * n_slots floats) and are added in warp order.
+// Returns the total of the calling thread's own slot; one __syncthreads inside.  Two consecutive
+// calls must use different `wsum` buffers.
+__device__ __forceinline__ float cta_slot_sum_shuf(const Geom& g, float v, int tx, float* wsum) {
+  const int tps = 1 << g.tps_shift;
+  for (int b = 1; b < tps; b <<= 1) v += __shfl_xor_sync(0xffffffffu, v, b);
+  for (int b = g.CV; b < 32; b <<= 1) v += __shfl_xor_sync(0xffffffffu, v, b);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  const int n_slots = g.CV >> g.tps_shift;
+  if (lane < g.CV && (lane & (tps - 1)) == 0) wsum[warp * n_slots + (lane >> g.tps_shift)] = v;
+  __syncthreads();
+  const int s = tx >> g.tps_shift;
+  float t = 0.f;
+  for (int w = 0; w < nwarps; ++w) t += wsum[w * n_slots + s];
+  return t;
+}
+
+// Copies `count` floats per CTA of the cluster from the peers' shared memory (same offset
+// `remote` in every CTA) into local shared memory: stage[q * count + i] = peer q's remote[i].
+// The loads of all (peer, element) pairs are spread over the threads so that they are in flight
+// together.  Call after the cluster barrier that publishes `remote`; ends with __syncthreads().
+__device__ __forceinline__ void cluster_gather(const float* remote, int count, unsigned k, float* stage) {
+  for (int i = threadIdx.x; i < (int)k * count; i += blockDim.x) {
+    const unsigned q = (unsigned)i / (unsigned)count;
+    stage[i] = dsmem_ld_f32(remote + (i - (int)q * count), q);
   }
   __syncthreads();
 }

@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   P* tile = reinterpret_cast<P*>(smem_raw);
   const size_t tile_bytes = ((size_t)g.rows_per_cta * g.CV * sizeof(P) + 15) & ~(size_t)15;
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
-  float* tmp = red + g.TY * g.CW;
+  float* tmp = red + g.red_floats;
   float* slot = tmp + g.slots;        // local mean | local M2 | local count
   float* stat = slot + 3 * g.slots;   // mean[slots], rstd[slots]
 
@@ -323,23 +323,50 @@ __global__ void __launch_bounds__(kMaxThreads)
   tile_fill_moments<T, VE>(x + base, gstep, stile, sstep, iters, mean, m2, cnt);
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
-  cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
+  if (UNI && g.shuf) {
+    // shuffle reductions: red doubles as the two warp-sum buffers
+    float sm = 0.f;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) sm += mean[e];
+    const float n_loc = (float)nrows * (float)g.D;
+    const float tot = cta_slot_sum_shuf(g, cnt * sm, tx, red);
+    const float lm = n_loc > 0.f ? tot / n_loc : 0.f;
+    float acc = 0.f, dev = 0.f;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const float d = mean[e] - lm;
+      dev = fmaf(d, d, dev);
+      acc += m2[e];
+    }
+    const float m2loc = cta_slot_sum_shuf(g, fmaf(cnt, dev, acc), tx, red + 512);
+    if (tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
+      const int s = tid >> g.tps_shift;
+      slot[s] = lm;
+      slot[g.slots + s] = m2loc;
+      slot[2 * g.slots + s] = n_loc;
+    }
+  } else {
+    cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
+  }
 
   // combine the k CTA-local moments (rank order -> every CTA of the cluster gets bit-identical
   // statistics):  mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2
   cluster_sync_all();
+  float* stage = red;  // k * 3 * slots floats: the peers' slot arrays, gathered in parallel
+  cluster_gather(slot, 3 * g.slots, k, stage);
   for (int s = tid; s < n_slots; s += blockDim.x) {
     float wsum = 0.f, ntot = 0.f;
     for (unsigned q = 0; q < k; ++q) {
-      const float nq = dsmem_ld_f32(slot + 2 * g.slots + s, q);
-      wsum = fmaf(nq, dsmem_ld_f32(slot + s, q), wsum);
-      ntot += nq;
+      const float* pq = stage + q * 3 * g.slots;
+      wsum = fmaf(pq[2 * g.slots + s], pq[s], wsum);
+      ntot += pq[2 * g.slots + s];
     }
     const float mu = wsum / ntot;
     float m2tot = 0.f;
     for (unsigned q = 0; q < k; ++q) {
-      const float d = dsmem_ld_f32(slot + s, q) - mu;
-      m2tot += fmaf(dsmem_ld_f32(slot + 2 * g.slots + s, q) * d, d, dsmem_ld_f32(slot + g.slots + s, q));
+      const float* pq = stage + q * 3 * g.slots;
+      const float d = pq[s] - mu;
+      m2tot += fmaf(pq[2 * g.slots + s] * d, d, pq[g.slots + s]);
     }
     const float rs = rsqrtf(fmaxf(m2tot / ntot, 0.f) + eps);
     stat[s] = mu;
@@ -372,7 +399,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   // [ring: kRingDepth * blockDim vectors][red][tmp][slot]
   const size_t ring_bytes = sizeof(T) * VE == 16 ? (size_t)kRingDepth * blockDim.x * 16 : 0;
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + ring_bytes);
-  float* tmp = red + g.TY * g.CW;
+  float* tmp = red + g.red_floats;
   float* slot = tmp + g.slots;
 
   const int tile_id = blockIdx.x;

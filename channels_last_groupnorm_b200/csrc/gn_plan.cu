@@ -54,21 +54,47 @@ FastDiv make_fast_div(int d) {
   return f;
 }
 
-void fill_divisors(Geom* g) {
+// shared-memory floats of the CTA reductions (layouts in gn_fwd.cu / gn_bwd.cu)
+// forward `red` scratch: the per-row-lane values of the generic reduction, or two warp-sum buffers
+// of the shuffle reduction, or the gathered slot arrays of up to 16 cluster peers
+size_t fwd_red_floats(int CW, int TY, int slots) {
+  size_t r = (size_t)TY * CW;
+  if (r < 1024) r = 1024;
+  if (r < (size_t)16 * 3 * slots) r = (size_t)16 * 3 * slots;
+  return r;
+}
+size_t fwd_fold_floats(int CW, int TY, int slots, int threads) {
+  (void)threads;
+  return fwd_red_floats(CW, TY, slots) + (size_t)6 * slots + 8;
+}
+size_t bwd_red_floats(int CW, int TY, int slots) {
+  size_t r = (size_t)2 * TY * CW;
+  if (r < 1024) r = 1024;
+  if (r < (size_t)16 * 2 * slots) r = (size_t)16 * 2 * slots;
+  return r;
+}
+size_t bwd_fold_floats(int CW, int TY, int slots, int threads) {
+  return bwd_red_floats(CW, TY, slots) + (size_t)2 * (threads > CW ? threads : CW) + (size_t)2 * CW + (size_t)4 * slots + 8;
+}
+
+bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+void fill_divisors(Geom* g, int ve, int direction) {
+  g->red_floats = (int)(direction == 0 ? fwd_red_floats(g->CW, g->TY, g->slots) : bwd_red_floats(g->CW, g->TY, g->slots));
+  g->shuf = 0;
+  g->tps_shift = 0;
+  if (ve > 0 && g->D % ve == 0) {
+    const int tps = g->D / ve;
+    if (is_pow2(g->CV) && g->CV <= 32 && is_pow2(tps) && tps <= g->CV && getenv("GNB200_NO_SHUF") == nullptr) {
+      g->shuf = 1;
+      while ((1 << g->tps_shift) < tps) ++g->tps_shift;
+    }
+  }
   g->div_D = make_fast_div(g->D);
   g->div_CV = make_fast_div(g->CV);
   g->div_CW = make_fast_div(g->CW);
   g->div_ncb = make_fast_div(g->ncb);
   g->div_chunks = make_fast_div(g->chunks);
-}
-
-// shared-memory floats of the CTA reductions (layouts in gn_fwd.cu / gn_bwd.cu)
-size_t fwd_fold_floats(int CW, int TY, int slots, int threads) {
-  (void)threads;
-  return (size_t)TY * CW + (size_t)6 * slots + 8;
-}
-size_t bwd_fold_floats(int CW, int TY, int slots, int threads) {
-  return (size_t)2 * TY * CW + (size_t)2 * (threads > CW ? threads : CW) + (size_t)2 * CW + (size_t)4 * slots + 8;
 }
 
 struct Shape {
@@ -111,10 +137,10 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   p.threads = threads;
   p.grid = (long long)sh.N * ncb * k;
   p.smem_bytes = tile + fold;
-  p.ws_bytes = sh.direction == 0 ? 0 : (size_t)sh.N * sh.C * 2 * sizeof(float);
+  p.ws_bytes = sh.direction == 0 ? 0 : (size_t)sh.N * k * sh.C * 2 * sizeof(float);  // channel sums per cluster rank
   p.launches = sh.direction == 0 ? 1 : 2;
   p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, rows, k, slots, k};
-  fill_divisors(&p.geom);
+  fill_divisors(&p.geom, ve, sh.direction);
   if (p.grid > 0x7fffffffLL) return false;
   *out = p;
 
@@ -232,7 +258,7 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
     p.launches = 4;
   }
   p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, (int)rows, (int)chunks, slots, 1};
-  fill_divisors(&p.geom);
+  fill_divisors(&p.geom, ve, sh.direction);
   *out = p;
   return true;
 }
