@@ -9,10 +9,12 @@
 // This is the reference's formula (src/gnnhwc/csrc/gn_kernel.cu:613-618, 723-727, 786-800,
 // 868-872) rewritten in terms of xh so that no large terms cancel when |mean| >> 1/rstd.
 //
-//  fused   one launch + a tiny parameter-gradient kernel.  A cluster of k CTAs keeps the x and dy
-//          rows of one (sample, column block) slab in shared memory, reduces S1/S2, exchanges the
-//          group sums through distributed shared memory and writes dx from shared memory:
-//          x and dy are read from HBM once, dx is written once.
+//  fused   one launch + a tiny parameter-gradient kernel.  A cluster of k CTAs owns one (sample,
+//          column block) slab: it reads x and dy once from HBM, reduces S1/S2, keeps dyh in shared
+//          memory, exchanges the group sums through distributed shared memory and writes dx from
+//          the dyh tile and x, which it reads a second time from L2 a few microseconds after the
+//          first read (the slab share of all resident CTAs is a few tens of MB, far below L2).
+//          HBM traffic: x and dy read once, dx written once.
 //  two-pass  reduce kernel (per-tile channel sums to scratch) -> finalize (fixed-order sums, A, B)
 //          -> parameter-gradient kernel -> apply kernel (reverse tile order for L2 reuse).
 //
@@ -126,97 +128,81 @@ __device__ __forceinline__ void stream_bwd_sums(const T* __restrict__ gx, const 
   }
 }
 
-// Phase 1 of the fused path: the thread's x and dy rows are copied into the shared-memory tiles
-// with cp.async (all put in flight up front, four commit groups), consumed as they land, and the
-// dy tile is overwritten in place with dyh = dy * act'(yh) rounded to T, so that phase 2 does not
-// evaluate the activation derivative again.  (For 16-bit T this rounds dyh once more than a
-// recompute would: half a unit in the last place of T on one term of dx.)
+constexpr int kXRing = 4;  // x rows in flight per thread in the fused backward kernel
+
+// One row of the fused path's copy pipeline: x into ring slot `slot`, dy into its tile row.
+template <typename T>
+__device__ __forceinline__ void bwd_issue_row(const T* gx, const T* gd, uint32_t ring_slot, uint32_t tile_row) {
+  cp_async16(ring_slot, gx);
+  cp_async16(tile_row, gd);
+}
+
+// Phase 1 of the fused path.  dy rows are copied straight into the shared-memory tile, x rows go
+// through a kXRing-deep shared-memory ring (cp.async, one commit group per row, kXRing rows in
+// flight per thread).  dyh = dy * act'(yh) is accumulated into the channel sums and written back
+// over the dy tile, rounded to T, so that phase 2 does not evaluate the activation derivative
+// again.  (For 16-bit T this rounds dyh once more than a recompute would: half a unit in the last
+// place of T on one term of dx.)  x is not kept on chip: phase 2 reads it again from L2.
 template <typename T, int VE, int ACT>
 __device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, const T* __restrict__ gd,
-                                                   size_t gstep_elems, uint32_t sx, uint32_t sd, uint32_t sstep_bytes,
-                                                   int iters, const BwdLane<T, VE>& L, float (&s1)[VE],
-                                                   float (&s2)[VE]) {
+                                                   size_t gstep_elems, uint32_t ring, uint32_t ring_stride,
+                                                   uint32_t sd, uint32_t sstep_bytes, int iters,
+                                                   const BwdLane<T, VE>& L, float (&s1)[VE], float (&s2)[VE]) {
   if constexpr (sizeof(T) * VE == 16) {
-    const int q = (iters + 3) >> 2;
-    {
-      const T* px = gx;
-      const T* pd = gd;
-      uint32_t wx = sx, wd = sd;
-      int i = 0;
+    uint32_t wd = sd;
 #pragma unroll
-      for (int st = 0; st < 4; ++st) {
-        const int end = min(iters, (st + 1) * q);
-        for (; i < end; ++i) {
-          cp_async16(wx, px);
-          cp_async16(wd, pd);
-          wx += sstep_bytes;
-          wd += sstep_bytes;
-          px += gstep_elems;
-          pd += gstep_elems;
-        }
-        cp_async_commit();
+    for (int d = 0; d < kXRing; ++d) {
+      if (d < iters) {
+        bwd_issue_row<T>(gx, gd, ring + d * ring_stride, wd);
+        gx += gstep_elems;
+        gd += gstep_elems;
+        wd += sstep_bytes;
       }
+      cp_async_commit();
     }
-    uint32_t rx = sx, rd = sd;
-    int i = 0;
-#pragma unroll
-    for (int st = 0; st < 4; ++st) {
-      cp_async_wait_dyn(3 - st);
-      const int end = min(iters, (st + 1) * q);
-      // two rows per trip: four independent shared loads and 2 * VE independent lanes in flight
-      for (; i + 2 <= end; i += 2) {
-        const uint4 wx0 = lds128(rx), wd0 = lds128(rd);
-        const uint4 wx1 = lds128(rx + sstep_bytes), wd1 = lds128(rd + sstep_bytes);
-        float fx0[VE], fd0[VE], fx1[VE], fd1[VE];
-        unpack16<T, VE>(wx0, fx0);
-        unpack16<T, VE>(wd0, fd0);
-        unpack16<T, VE>(wx1, fx1);
-        unpack16<T, VE>(wd1, fd1);
-        bwd_row_sums<T, VE, ACT>(fx0, fd0, L, s1, s2);
-        bwd_row_sums<T, VE, ACT>(fx1, fd1, L, s1, s2);
-        sts128(rd, pack16<T, VE>(fd0));
-        sts128(rd + sstep_bytes, pack16<T, VE>(fd1));
-        rx += 2 * sstep_bytes;
-        rd += 2 * sstep_bytes;
+    uint32_t rd = sd;
+    for (int i = 0; i < iters; ++i) {
+      cp_async_wait<kXRing - 1>();
+      const uint32_t slot = ring + (i & (kXRing - 1)) * ring_stride;
+      float fx[VE], fd[VE];
+      unpack16<T, VE>(lds128(slot), fx);
+      unpack16<T, VE>(lds128(rd), fd);
+      if (i + kXRing < iters) {
+        bwd_issue_row<T>(gx, gd, slot, wd);
+        gx += gstep_elems;
+        gd += gstep_elems;
+        wd += sstep_bytes;
       }
-      for (; i < end; ++i) {
-        float fx[VE], fd[VE];
-        unpack16<T, VE>(lds128(rx), fx);
-        unpack16<T, VE>(lds128(rd), fd);
-        bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
-        sts128(rd, pack16<T, VE>(fd));
-        rx += sstep_bytes;
-        rd += sstep_bytes;
-      }
+      cp_async_commit();
+      bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+      sts128(rd, pack16<T, VE>(fd));
+      rd += sstep_bytes;
     }
   } else {
-    const T* px = gx;
-    const T* pd = gd;
-    T* wx = reinterpret_cast<T*>(__cvta_shared_to_generic(sx));
     T* wd = reinterpret_cast<T*>(__cvta_shared_to_generic(sd));
     for (int i = 0; i < iters; ++i) {
       float fx[VE], fd[VE];
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
-        wx[e] = px[e];
-        fx[e] = load_param<T>(px, e);
-        fd[e] = load_param<T>(pd, e);
+        fx[e] = load_param<T>(gx, e);
+        fd[e] = load_param<T>(gd, e);
       }
       bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
 #pragma unroll
       for (int e = 0; e < VE; ++e) wd[e] = store_param<T>(fd[e]);
-      px += gstep_elems;
-      pd += gstep_elems;
-      wx += sstep_bytes / sizeof(T);
+      gx += gstep_elems;
+      gd += gstep_elems;
       wd += sstep_bytes / sizeof(T);
     }
   }
 }
 
-// Phase 2 of the fused path: dx = ag * dyh + (nb * xh + na) from the two tiles to global memory
-// (ag = rstd * gamma, nb = -rstd * B, na = -rstd * A per lane; the dy tile holds dyh).
+// Phase 2 of the fused path: dx = ag * dyh + (nb * xh + na); dyh from the shared-memory tile, x
+// a second time from global memory (an L2 hit: it was read microseconds earlier) through the same
+// ring.  ag = rstd * gamma, nb = -rstd * B, na = -rstd * A per lane.
 template <typename T, int VE>
-__device__ __forceinline__ void tile_bwd_dx(uint32_t sx, uint32_t sd, uint32_t sstep_bytes, T* __restrict__ gdst,
+__device__ __forceinline__ void tile_bwd_dx(const T* __restrict__ gx, uint32_t ring, uint32_t ring_stride,
+                                            uint32_t sd, uint32_t sstep_bytes, T* __restrict__ gdst,
                                             size_t gstep_elems, int iters, const BwdLane<T, VE>& L,
                                             const float (&A)[VE], const float (&B)[VE]) {
   float ag[VE], nb[VE], na[VE];
@@ -236,14 +222,27 @@ __device__ __forceinline__ void tile_bwd_dx(uint32_t sx, uint32_t sd, uint32_t s
       c1[e] = nb[e] * L.r[e];
       c2[e] = fmaf(nb[e], L.nmr[e], na[e]);
     }
+#pragma unroll
+    for (int d = 0; d < kXRing; ++d) {
+      if (d < iters) {
+        cp_async16(ring + d * ring_stride, gx);
+        gx += gstep_elems;
+      }
+      cp_async_commit();
+    }
     T* gp = gdst;
-#pragma unroll 2
     for (int i = 0; i < iters; ++i) {
+      cp_async_wait<kXRing - 1>();
+      const uint32_t slot = ring + (i & (kXRing - 1)) * ring_stride;
       float fx[VE], fd[VE];
-      unpack16<T, VE>(lds128(sx), fx);
+      unpack16<T, VE>(lds128(slot), fx);
       unpack16<T, VE>(lds128(sd), fd);
-      sx += sstep_bytes;
       sd += sstep_bytes;
+      if (i + kXRing < iters) {
+        cp_async16(slot, gx);
+        gx += gstep_elems;
+      }
+      cp_async_commit();
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
         if constexpr (kFold) {
@@ -257,16 +256,15 @@ __device__ __forceinline__ void tile_bwd_dx(uint32_t sx, uint32_t sd, uint32_t s
       gp += gstep_elems;
     }
   } else {
-    const T* px = reinterpret_cast<const T*>(__cvta_shared_to_generic(sx));
     const T* pd = reinterpret_cast<const T*>(__cvta_shared_to_generic(sd));
     T* gp = gdst;
     for (int i = 0; i < iters; ++i) {
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
-        const float xh = fmaf(load_param<T>(px, e), L.r[e], L.nmr[e]);
+        const float xh = fmaf(load_param<T>(gx, e), L.r[e], L.nmr[e]);
         gp[e] = store_param<T>(fmaf(ag[e], load_param<T>(pd, e), fmaf(nb[e], xh, na[e])));
       }
-      px += sstep_bytes / sizeof(T);
+      gx += gstep_elems;
       pd += sstep_bytes / sizeof(T);
       gp += gstep_elems;
     }
@@ -334,7 +332,7 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
 
 // ------------------------------------------------------------------------------------------------
 // fused kernel.  grid.x = N * ncb * k, cluster (k,1,1).
-// dynamic smem: [x tile][dy tile][red 2*TY*CW][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
+// dynamic smem: [dyh tile][x ring kXRing*threads*16 B][red][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
 // scratch out : sums[((n * k + rank) * C + c) * 2 + {0,1}] = S1, S2 over this CTA's rows
 // ------------------------------------------------------------------------------------------------
 template <typename T, int VE, int ACT, bool UNI>
@@ -352,9 +350,11 @@ __global__ void __launch_bounds__(kMaxThreads)
   const int nrows = min(g.rows_per_cta, g.R - r0);
 
   const size_t tile_bytes = ((size_t)g.rows_per_cta * g.CV * sizeof(P) + 15) & ~(size_t)15;
-  P* tile_x = reinterpret_cast<P*>(smem_raw);
-  P* tile_dy = reinterpret_cast<P*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
-  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + 2 * tile_bytes);
+  const size_t ring_bytes = sizeof(P) == 16 ? (size_t)kXRing * blockDim.x * 16 : 0;
+  P* tile_dy = reinterpret_cast<P*>(smem_raw);
+  const uint32_t ring = smem_addr(reinterpret_cast<char*>(smem_raw) + tile_bytes) + threadIdx.x * 16;
+  const uint32_t ring_stride = blockDim.x * 16;
+  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes + ring_bytes);
   float* part = red + g.red_floats;
   float* chan = part + 2 * max((int)blockDim.x, g.CW);
   float* spart = chan + 2 * g.CW;  // [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 over this CTA's rows
@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
   const size_t base = ((size_t)n * g.R + r0 + ty) * g.C + c0 + (size_t)tx * VE;
   const int iters = (streaming && ty < nrows) ? (nrows - ty + g.TY - 1) / g.TY : 0;
-  const uint32_t sx = smem_addr(tile_x + ty * g.CV + tx), sd = smem_addr(tile_dy + ty * g.CV + tx);
+  const uint32_t sd = smem_addr(tile_dy + ty * g.CV + tx);
   const uint32_t sstep = (uint32_t)(g.TY * g.CV * sizeof(P));
   const size_t gstep = (size_t)g.TY * g.C;
 
@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
   if (streaming) {
     lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
-    tile_fill_bwd_sums<T, VE, ACT>(x + base, dy + base, gstep, sx, sd, sstep, iters, L, s1, s2);
+    tile_fill_bwd_sums<T, VE, ACT>(x + base, dy + base, gstep, ring, ring_stride, sd, sstep, iters, L, s1, s2);
   }
 
   int g_lo, n_slots;
@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(kMaxThreads)
         B[e] = coef[g.slots + s];
       }
     }
-    tile_bwd_dx<T, VE>(sx, sd, sstep, dx + base, gstep, iters, L, A, B);
+    tile_bwd_dx<T, VE>(x + base, ring, ring_stride, sd, sstep, dx + base, gstep, iters, L, A, B);
   }
   cluster_wait();
 }

@@ -553,6 +553,7 @@ struct Geom {
   // threads per group row (D / VE) are powers of two and CV <= 32.  tps_shift = log2(D / VE).
   int shuf, tps_shift;
   int red_floats;  // size of the reduction scratch `red` (forward kernels), set by the planner
+  int dbg;         // experiments only: stop the fused forward kernel after stage `dbg` (0 = run normally)
 };
 
 // Groups touched by column block starting at channel c0 (width CW, clipped to C):

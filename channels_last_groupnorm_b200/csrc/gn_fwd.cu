@@ -314,6 +314,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   float mean[VE], m2[VE], cnt = 0.f;
 #pragma unroll
   for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
+  if (g.dbg == 1) return;
   // this thread's rows: r0 + ty, r0 + ty + TY, ...; its tile slots are CV * TY vectors apart
   const size_t base = ((size_t)n * g.R + r0 + ty) * g.C + c0 + (size_t)tx * VE;
   const int iters = (streaming && ty < nrows) ? (nrows - ty + g.TY - 1) / g.TY : 0;
@@ -321,6 +322,10 @@ __global__ void __launch_bounds__(kMaxThreads)
   const uint32_t sstep = (uint32_t)(g.TY * g.CV * sizeof(P));
   const size_t gstep = (size_t)g.TY * g.C;
   tile_fill_moments<T, VE>(x + base, gstep, stile, sstep, iters, mean, m2, cnt);
+  if (g.dbg == 2) {
+    if (mean[0] + m2[VE - 1] + cnt == -1.f) mean_out[0] = 0.f;
+    return;
+  }
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
   if (UNI && g.shuf) {
@@ -351,6 +356,7 @@ __global__ void __launch_bounds__(kMaxThreads)
 
   // combine the k CTA-local moments (rank order -> every CTA of the cluster gets bit-identical
   // statistics):  mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2
+  if (g.dbg == 3) return;
   cluster_sync_all();
   float* stage = red;  // k * 3 * slots floats: the peers' slot arrays, gathered in parallel
   cluster_gather(slot, 3 * g.slots, k, stage);
@@ -378,6 +384,10 @@ __global__ void __launch_bounds__(kMaxThreads)
   }
   cluster_arrive();  // this CTA no longer reads its peers' shared memory
   __syncthreads();
+  if (g.dbg == 4) {
+    cluster_wait();
+    return;
+  }
 
   if (streaming) {
     float a[VE], b[VE];

@@ -83,6 +83,7 @@ void fill_divisors(Geom* g, int ve, int direction) {
   g->red_floats = (int)(direction == 0 ? fwd_red_floats(g->CW, g->TY, g->slots) : bwd_red_floats(g->CW, g->TY, g->slots));
   g->shuf = 0;
   g->tps_shift = 0;
+  g->dbg = env_int("GNB200_DBG_STOP", 0);
   if (ve > 0 && g->D % ve == 0) {
     const int tps = g->D / ve;
     if (is_pow2(g->CV) && g->CV <= 32 && is_pow2(tps) && tps <= g->CV && getenv("GNB200_NO_SHUF") == nullptr) {
@@ -119,7 +120,6 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   const int ve = sh.ve, s = sh.s;
   const int ncb = sh.C / cw;
   const int CV = cw / ve;
-  const int ntiles = sh.direction == 0 ? 1 : 2;
   const int slots = cw / sh.D;
   const int rows = (sh.R + k - 1) / k;
   if (k > 1 && (long long)rows * (k - 1) >= sh.R) return false;  // a CTA of the cluster would be idle
@@ -127,7 +127,9 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   thread_layout(CV, rows, target_threads, &TY, &threads);
   // larger CTAs only pay when every thread still owns >= 16 rows (per-thread set-up is amortised)
   if (target_threads > 128 && env_int("GNB200_THREADS", 0) == 0 && rows / TY < 16) return false;
-  const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15) * ntiles;
+  // forward: the x tile.  backward: the dy * act' tile plus a 4-row cp.async ring for x
+  const size_t ring = (sh.direction == 1 && ve > 1) ? (size_t)4 * threads * 16 : 0;
+  const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15) + ring;
   const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots, threads) : bwd_fold_floats(cw, TY, slots, threads)) * 4;
   if (tile + fold > kSmemMaxOptin - 1024) return false;
 
