@@ -332,7 +332,7 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
 
 // ------------------------------------------------------------------------------------------------
 // fused kernel.  grid.x = N * ncb * k, cluster (k,1,1).
-// dynamic smem: [dyh tile][x ring kXRing*threads*16 B][red][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
+// dynamic smem: [dyh tile][x ring kXRing*threads*16 B, shared with red][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
 // scratch out : sums[((n * k + rank) * C + c) * 2 + {0,1}] = S1, S2 over this CTA's rows
 // ------------------------------------------------------------------------------------------------
 template <typename T, int VE, int ACT, bool UNI>
@@ -354,8 +354,11 @@ __global__ void __launch_bounds__(kMaxThreads)
   P* tile_dy = reinterpret_cast<P*>(smem_raw);
   const uint32_t ring = smem_addr(reinterpret_cast<char*>(smem_raw) + tile_bytes) + threadIdx.x * 16;
   const uint32_t ring_stride = blockDim.x * 16;
-  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes + ring_bytes);
-  float* part = red + g.red_floats;
+  // the reduction scratch `red` shares its bytes with the ring: the ring is idle between the two
+  // streaming phases, which is exactly when the reductions run
+  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
+  const size_t shared_bytes = max(ring_bytes, (size_t)g.red_floats * sizeof(float));
+  float* part = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes + shared_bytes);
   float* chan = part + 2 * max((int)blockDim.x, g.CW);
   float* spart = chan + 2 * g.CW;  // [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 over this CTA's rows
   float* coef = spart + 2 * g.slots;  // A[s], B[slots + s]
@@ -382,6 +385,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   cb_groups(g, c0, g_lo, n_slots);
   const int c_valid = min(g.CW, g.C - c0);
   const bool shuf = UNI && g.shuf;
+  __syncthreads();  // every thread is done with its ring slots: `red` may now be written
   if (shuf) {
     // gamma-weighted group sums straight from registers: xor-butterflies + one pass over the warps
     float a1 = 0.f, a2 = 0.f;

@@ -129,8 +129,12 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   if (target_threads > 128 && env_int("GNB200_THREADS", 0) == 0 && rows / TY < 16) return false;
   // forward: the x tile.  backward: the dy * act' tile plus a 4-row cp.async ring for x
   const size_t ring = (sh.direction == 1 && ve > 1) ? (size_t)4 * threads * 16 : 0;
-  const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15) + ring;
-  const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots, threads) : bwd_fold_floats(cw, TY, slots, threads)) * 4;
+  const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15);
+  size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots, threads) : bwd_fold_floats(cw, TY, slots, threads)) * 4;
+  if (sh.direction == 1) {  // the ring and the reduction scratch `red` share their bytes
+    const size_t red = bwd_red_floats(cw, TY, slots) * 4;
+    fold = fold - red + (ring > red ? ring : red);
+  }
   if (tile + fold > kSmemMaxOptin - 1024) return false;
 
   Plan p = {};
