@@ -280,7 +280,10 @@ class DeviceProblem:
         self.ga, self.be = ga.to(dev), be.to(dev)
         self.mean = torch.empty((n_local, G), dtype=torch.float32, device=dev)
         self.rstd = torch.empty((n_local, G), dtype=torch.float32, device=dev)
-        self.dparam = torch.empty((2, C), dtype=torch.float32, device=dev)
+        # two slots, so that the all-reduce of step i can overlap the kernels of step i+1
+        self.dparams = [torch.empty((2, C), dtype=torch.float32, device=dev) for _ in range(2)]
+        self.dparam = self.dparams[0]
+        self.dgdb = [torch.empty((2, C), dtype=self.dtype, device=dev) for _ in range(2)]
         self.dgamma = torch.empty(C, dtype=self.dtype, device=dev)
         self.dbeta = torch.empty(C, dtype=self.dtype, device=dev)
         wf = nt.lib.gnb200_fwd_workspace_bytes(n_local, self.R, C, G, self.code)
@@ -300,12 +303,13 @@ class DeviceProblem:
                                      self.G, self.eps, self.act, self.code, s["y"].data_ptr(), self.mean.data_ptr(),
                                      self.rstd.data_ptr(), self.ws_f.data_ptr() if self.wf else None, self.wf, stream))
 
-    def bwd_(self, i, stream, typed):
+    def bwd_(self, i, stream, typed, slot=0):
         s = self.sets[i % self.nsets]
         lib = self.nt.lib
+        dparam = self.dparams[slot]
         self.nt.check(lib.gnb200_bwd(s["dy"].data_ptr(), s["x"].data_ptr(), self.ga.data_ptr(), self.be.data_ptr(),
                                      self.mean.data_ptr(), self.rstd.data_ptr(), self.n, self.R, self.C, self.G,
-                                     self.act, self.code, s["dx"].data_ptr(), self.dparam.data_ptr(),
+                                     self.act, self.code, s["dx"].data_ptr(), dparam.data_ptr(),
                                      self.dgamma.data_ptr() if typed else None,
                                      self.dbeta.data_ptr() if typed else None,
                                      self.ws_b.data_ptr() if self.wb else None, self.wb, stream))
@@ -352,18 +356,41 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
     def cur():
         return torch.cuda.current_stream().cuda_stream
 
+    side = torch.cuda.Stream() if world > 1 else None
+    done = [None, None]  # per slot: event after which its all-reduced gradients are complete
+
     def one(i):
+        """Forward, backward and - on more than one rank - the all-reduce of the packed fp32
+        [dgamma | dbeta] buffer plus its cast to the tensor dtype.  The collective runs on a side
+        stream and alternates between two buffers, so it overlaps the next step's kernels, as a
+        gradient all-reduce overlaps the rest of a backward pass in training."""
+        b = i & 1
         prob.fwd(i, cur())
         if prob.bwd:
-            prob.bwd_(i, cur(), typed=(world == 1))
+            if world > 1 and done[b] is not None:
+                torch.cuda.current_stream().wait_event(done[b])  # slot b is free again
+            prob.bwd_(i, cur(), typed=(world == 1), slot=b)
             if world > 1:
-                dist.all_reduce(prob.dparam)
-                prob.dgamma.copy_(prob.dparam[0])
-                prob.dbeta.copy_(prob.dparam[1])
+                ready = torch.cuda.Event()
+                ready.record(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    side.wait_event(ready)
+                    dist.all_reduce(prob.dparams[b])
+                    prob.dgdb[b].copy_(prob.dparams[b])
+                    done[b] = torch.cuda.Event()
+                    done[b].record(side)
+
+    def join():
+        """Makes the current stream wait for the collectives still running on the side stream."""
+        for b in (0, 1):
+            if done[b] is not None:
+                torch.cuda.current_stream().wait_event(done[b])
 
     for i in range(warmup):
         one(i)
+    join()
     torch.cuda.synchronize()
+    done[0] = done[1] = None
 
     def reduce_max(v):
         if world > 1:
@@ -374,7 +401,13 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
 
     if use_graph:
         try:
-            g_step = _capture(lambda i: one(warmup + i), steps)
+            def step_and_join(i):
+                one(warmup + i)
+                if i == steps - 1:
+                    join()
+
+            g_step = _capture(step_and_join, steps)
+            done[0] = done[1] = None
             g_fwd = _capture(lambda i: prob.fwd(i, cur()), steps)
             g_bwd = _capture(lambda i: prob.bwd_(i, cur(), typed=True), steps) if prob.bwd else None
             for g in (g_step, g_fwd, g_bwd):  # one untimed replay each
@@ -396,16 +429,25 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
     t_wall0 = time.time()
     start.record()
     for i in range(steps):
+        b = i & 1
         evs[i][0].record()
         prob.fwd(warmup + i, cur())
         evs[i][1].record()
         if prob.bwd:
-            prob.bwd_(warmup + i, cur(), typed=(world == 1))
+            if world > 1 and done[b] is not None:
+                torch.cuda.current_stream().wait_event(done[b])
+            prob.bwd_(warmup + i, cur(), typed=(world == 1), slot=b)
             evs[i][2].record()
             if world > 1:
-                dist.all_reduce(prob.dparam)
-                prob.dgamma.copy_(prob.dparam[0])
-                prob.dbeta.copy_(prob.dparam[1])
+                ready = torch.cuda.Event()
+                ready.record(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    side.wait_event(ready)
+                    dist.all_reduce(prob.dparams[b])
+                    prob.dgdb[b].copy_(prob.dparams[b])
+                    done[b] = torch.cuda.Event()
+                    done[b].record(side)
+    join()
     stop.record()
     torch.cuda.synchronize()
     t_wall1 = time.time()
@@ -511,6 +553,13 @@ def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
 
 
 def device_arm(args):
+    with _StdoutToStderr():
+        line = _device_arm(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def _device_arm(args):
     import torch.distributed as dist
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -589,9 +638,11 @@ def device_arm(args):
                 "ms_per_sample_step": med * 1e3, "iters": iters,
                 "sample": "%d of %d samples, torch.nn.functional.group_norm + %s on CPU, channels_last %s, "
                           "autograd backward, median of %d runs" % (n_sample, N, act, dt, iters)}
-        print(json.dumps(line), flush=True)
+    else:
+        line = None
     if world > 1:
         dist.destroy_process_group()
+    return line
 
 
 # per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
@@ -728,6 +779,23 @@ def profile_target(args):
             prob.bwd_(i, stream, True)
     torch.cuda.synchronize()
     print("profiled", args.workload, args.profile, "calls")
+
+
+class _StdoutToStderr:
+    """While active, file descriptor 1 points at stderr, so that banners printed by libraries
+    (NCCL prints its version) cannot end up next to the one JSON line this program owes stdout."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+        return False
 
 
 def main():
