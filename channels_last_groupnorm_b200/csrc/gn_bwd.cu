@@ -335,8 +335,9 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
 // dynamic smem: [dyh tile][x ring kXRing*threads*16 B, shared with red][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
 // scratch out : sums[((n * k + rank) * C + c) * 2 + {0,1}] = S1, S2 over this CTA's rows
 // ------------------------------------------------------------------------------------------------
-template <typename T, int VE, int ACT, bool UNI>
-__global__ void __launch_bounds__(kMaxThreads)
+// MAXT: CTA size class.  128-thread launches are compiled for five CTAs per SM (<= 96 registers).
+template <typename T, int VE, int ACT, bool UNI, int MAXT>
+__global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
     gn_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                         const T* __restrict__ beta, const float* __restrict__ mean_in,
                         const float* __restrict__ rstd_in, T* __restrict__ dx, float* __restrict__ sums, const Geom g) {
@@ -472,16 +473,19 @@ __global__ void __launch_bounds__(kMaxThreads)
 // ------------------------------------------------------------------------------------------------
 // parameter gradients:  dbeta_c = sum_n S1[n,c],  dgamma_c = sum_n S2[n,c]  over the N rows of `sums`
 // (one per sample, or per sample and cluster rank; ascending per lane,
-// then a fixed tree over the 8 row lanes).  block (32, 8), grid ceil(C / 32).
+// then the 32 row lanes in order).  block (32, 32), grid ceil(C / 32).
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void gn_bwd_param_kernel(const float* __restrict__ sums, int N, int C, float* __restrict__ dparam_f32,
-                                    T* __restrict__ dgamma, T* __restrict__ dbeta) {
-  __shared__ float sm1[8][33], sm2[8][33];
+__global__ void __launch_bounds__(1024)
+    gn_bwd_param_kernel(const float* __restrict__ sums, int N, int C, float* __restrict__ dparam_f32,
+                        T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  constexpr int kLanes = 32;  // row lanes: block (32 channels, 32 row lanes)
+  __shared__ float sm1[kLanes][33], sm2[kLanes][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float a1 = 0.f, a2 = 0.f;
   if (c < C) {
-    for (int n = threadIdx.y; n < N; n += 8) {
+#pragma unroll 4
+    for (int n = threadIdx.y; n < N; n += kLanes) {
       const float2 v = reinterpret_cast<const float2*>(sums)[(size_t)n * C + c];
       a1 += v.x;
       a2 += v.y;
@@ -493,7 +497,7 @@ __global__ void gn_bwd_param_kernel(const float* __restrict__ sums, int N, int C
   if (threadIdx.y == 0 && c < C) {
     float t1 = 0.f, t2 = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < kLanes; ++j) {
       t1 += sm1[j][threadIdx.x];
       t2 += sm2[j][threadIdx.x];
     }
@@ -646,7 +650,7 @@ __global__ void __launch_bounds__(kMaxThreads)
 // ------------------------------------------------------------------------------------------------
 template <typename T>
 static cudaError_t launch_param(const BwdCall& c, const float* sums, int rows, const Geom& g, cudaStream_t stream) {
-  const dim3 block(32, 8, 1);
+  const dim3 block(32, 32, 1);
   const unsigned blocks = (unsigned)((g.C + 31) / 32);
   gn_bwd_param_kernel<T><<<blocks, block, 0, stream>>>(sums, rows, g.C, c.dparam_f32, (T*)c.dgamma, (T*)c.dbeta);
   return cudaGetLastError();
@@ -657,7 +661,7 @@ static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t st
   const Geom& g = p.geom;
   if (p.fused) {
     float* sums = reinterpret_cast<float*>(c.workspace);
-    auto kern = gn_bwd_fused_kernel<T, VE, ACT, UNI>;
+    auto kern = p.threads <= 128 ? gn_bwd_fused_kernel<T, VE, ACT, UNI, 128> : gn_bwd_fused_kernel<T, VE, ACT, UNI, kMaxThreads>;
     cudaError_t err = ensure_kernel_attributes((const void*)kern, p.smem_bytes, g.k > 8);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
