@@ -77,6 +77,25 @@ __device__ __forceinline__ void bwd_row_sums(const float (&fx)[VE], float (&fd)[
   }
 }
 
+// 16-bit tensors, fused path: yh straight from x (a = rstd * gamma, b = beta - mean * a) and
+// S2 accumulated against the raw x; the caller converts it with S2 = rstd * (S2raw - mean * S1).
+// One FMA per element less; the conversion's rounding (relative 1e-7 * |mean| * rstd) is far
+// below a 16-bit result.
+template <typename T, int VE, int ACT>
+__device__ __forceinline__ void bwd_row_sums_raw(const float (&fx)[VE], float (&fd)[VE], const float (&a)[VE],
+                                                 const float (&b)[VE], float (&s1)[VE], float (&s2)[VE]) {
+  float yh[VE], gr[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) yh[e] = fmaf(fx[e], a[e], b[e]);
+  act_grad_vec<T, VE, ACT>(yh, gr);
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    fd[e] *= gr[e];
+    s1[e] += fd[e];
+    s2[e] = fmaf(fd[e], fx[e], s2[e]);
+  }
+}
+
 constexpr int kRingDepth = 8;  // rows in flight per thread in the multi-kernel reduce kernel
 
 // Phase 1 of the multi-kernel path: S1, S2 over the thread's rows.  16-byte vectors of x and dy
@@ -149,6 +168,13 @@ __device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, con
                                                    uint32_t sd, uint32_t sstep_bytes, int iters,
                                                    const BwdLane<T, VE>& L, float (&s1)[VE], float (&s2)[VE]) {
   if constexpr (sizeof(T) * VE == 16) {
+    constexpr bool kRaw = sizeof(T) == 2;
+    float a[VE], b[VE];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      a[e] = L.r[e] * L.ga[e];
+      b[e] = fmaf(L.nmr[e], L.ga[e], L.be[e]);
+    }
     uint32_t wd = sd;
 #pragma unroll
     for (int d = 0; d < kXRing; ++d) {
@@ -174,9 +200,16 @@ __device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, con
         wd += sstep_bytes;
       }
       cp_async_commit();
-      bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+      if constexpr (kRaw)
+        bwd_row_sums_raw<T, VE, ACT>(fx, fd, a, b, s1, s2);
+      else
+        bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
       sts128(rd, pack16<T, VE>(fd));
       rd += sstep_bytes;
+    }
+    if constexpr (kRaw) {  // S2 = sum dyh * xh = rstd * (sum dyh * x - mean * sum dyh)
+#pragma unroll
+      for (int e = 0; e < VE; ++e) s2[e] = fmaf(L.r[e], s2[e], L.nmr[e] * s1[e]);
     }
   } else {
     T* wd = reinterpret_cast<T*>(__cvta_shared_to_generic(sd));

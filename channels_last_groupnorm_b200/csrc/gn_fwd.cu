@@ -76,43 +76,41 @@ __device__ __forceinline__ void stream_moments(const T* __restrict__ gsrc, size_
 }
 
 // Fused path, phase 1: the thread's rows (ty, ty + TY, ...) of its column vector are copied into
-// the shared-memory tile with cp.async - all of them put in flight up front, in four commit
-// groups - and consumed (Welford) group by group as they land.  Every thread reads back only
-// what it copied itself, so no block barrier is needed.
+// the shared-memory tile with cp.async - one commit group per row, eight rows in flight per
+// thread - and consumed (Welford) as they land.  Every thread reads back only what it copied
+// itself, so no block barrier is needed.
 template <typename T, int VE>
 __device__ __forceinline__ void tile_fill_moments(const T* __restrict__ gsrc, size_t gstep_elems, uint32_t stile,
                                                   uint32_t sstep_bytes, int iters, float (&mean)[VE], float (&m2)[VE],
                                                   float& cnt) {
   if constexpr (sizeof(T) * VE == 16) {
-    const int q = (iters + 3) >> 2;
-    {
-      const T* gp = gsrc;
-      uint32_t sp = stile;
-      int i = 0;
+    // one commit group per row, kTileDepth rows in flight per thread
+    constexpr int kTileDepth = 8;
+    const T* gp = gsrc;
+    uint32_t wp = stile;
 #pragma unroll
-      for (int st = 0; st < 4; ++st) {
-        const int end = min(iters, (st + 1) * q);
-        for (; i < end; ++i) {
-          cp_async16(sp, gp);
-          sp += sstep_bytes;
-          gp += gstep_elems;
-        }
-        cp_async_commit();
+    for (int d = 0; d < kTileDepth; ++d) {
+      if (d < iters) {
+        cp_async16(wp, gp);
+        wp += sstep_bytes;
+        gp += gstep_elems;
       }
+      cp_async_commit();
     }
-    uint32_t sp = stile;
-    int i = 0;
-#pragma unroll
-    for (int st = 0; st < 4; ++st) {
-      cp_async_wait_dyn(3 - st);
-      const int end = min(iters, (st + 1) * q);
+    uint32_t rp = stile;
 #pragma unroll 2
-      for (; i < end; ++i) {
-        float f[VE];
-        unpack16<T, VE>(lds128(sp), f);
-        sp += sstep_bytes;
-        welford_step<VE>(f, mean, m2, cnt);
+    for (int i = 0; i < iters; ++i) {
+      cp_async_wait<kTileDepth - 1>();
+      float f[VE];
+      unpack16<T, VE>(lds128(rp), f);
+      rp += sstep_bytes;
+      if (i + kTileDepth < iters) {
+        cp_async16(wp, gp);
+        wp += sstep_bytes;
+        gp += gstep_elems;
       }
+      cp_async_commit();
+      welford_step<VE>(f, mean, m2, cnt);
     }
   } else {
     const T* gp = gsrc;
