@@ -155,7 +155,10 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   // per SM matter most, then rows per thread (per-thread set-up is amortised over them), then the
   // contiguous row segment (64 B is nearly as good as 128 B; 32 B wastes DRAM sectors).
   const long long seg = (long long)cw * s;
-  const double seg_eff = seg >= 128 ? 1.0 : seg >= 64 ? 0.95 : seg >= 32 ? 0.5 : 0.3;
+  // 32-byte segments waste DRAM bursts on large tensors; a tensor that fits L2 shares the bursts
+  // between the CTAs of neighbouring column blocks
+  const bool small_tensor = (double)sh.N * sh.R * sh.C * s <= 32.0 * 1024 * 1024;
+  const double seg_eff = seg >= 128 ? 1.0 : seg >= 64 ? 0.95 : seg >= 32 ? (small_tensor ? 0.85 : 0.5) : 0.3;
   const double sms = (double)(p.grid < kSmCount ? p.grid : kSmCount);
   int per_sm = (int)(kSmemMaxOptin / (tile + fold + 1024));
   const int by_threads = 2048 / threads;
