@@ -645,9 +645,12 @@ def _device_arm(args):
     return line
 
 
-# per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; keyed by (workload, ranks, direction)
-NCU_TRAFFIC = {}
+# per-launch DRAM traffic in bytes (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture
+# summarised in profiles/fused_fwd_bwd_cfg4_bf16_gelu.md; keyed by (workload, ranks, direction)
+NCU_TRAFFIC = {
+    ("cfg4", 1, "forward"): 134313728 + 89355520,
+    ("cfg4", 1, "backward"): 268715776 + 108229632,
+}
 
 
 # ------------------------------------------------------------------------------------------------
