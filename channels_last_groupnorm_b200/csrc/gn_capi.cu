@@ -127,9 +127,9 @@ int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, 
   } else {
     const gnb200::Geom& g = p.geom;
     snprintf(text, sizeof(text),
-             "%s %s ve=%d cw=%d ncb=%d ty=%d threads=%d rows=%d chunks=%d k=%d grid=%lld smem=%zu ws=%zu launches=%d",
+             "%s %s ve=%d cw=%d ncb=%d ty=%d threads=%d rows=%d chunks=%d k=%d persist=%d grid=%lld smem=%zu ws=%zu launches=%d",
              direction == 0 ? "fwd" : "bwd", p.fused ? "fused" : "twopass", p.ve, g.CW, g.ncb, g.TY, p.threads,
-             g.rows_per_cta, g.chunks, g.k, p.grid, p.smem_bytes, p.ws_bytes, p.launches);
+             g.rows_per_cta, g.chunks, g.k, g.persist, p.grid, p.smem_bytes, p.ws_bytes, p.launches);
   }
   const int need = (int)strlen(text) + 1;
   if (buf && buf_len > 0) {

@@ -225,6 +225,21 @@ __device__ __forceinline__ void cp_async_wait_dyn(int pending) {
     cp_async_wait<0>();
 }
 
+// the same for pending <= 8
+__device__ __forceinline__ void cp_async_wait_dyn8(int pending) {
+  switch (pending) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 3: cp_async_wait<3>(); break;
+    case 4: cp_async_wait<4>(); break;
+    case 5: cp_async_wait<5>(); break;
+    case 6: cp_async_wait<6>(); break;
+    case 7: cp_async_wait<7>(); break;
+    default: cp_async_wait<8>(); break;
+  }
+}
+
 // 16 bytes of T viewed as a uint4 <-> fp32 lanes
 template <typename T, int VE>
 __device__ __forceinline__ void unpack16(const uint4& w, float (&f)[VE]) {
@@ -452,6 +467,48 @@ __device__ __forceinline__ __half2 act_grad_h2(__half2 v) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Mixed-precision arithmetic of sm_100: one instruction converts a 16-bit operand and combines it
+// with fp32 operands (PTX add / sub / fma with types .f32.f16 and .f32.bf16), so a 16-bit tensor
+// element enters an fp32 sum without a separate unpack instruction.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void split_halves(uint32_t w, uint16_t& lo, uint16_t& hi) {
+  asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(w));
+}
+// float(a) - c, exact conversion of a, one rounding
+template <typename T>
+__device__ __forceinline__ float mixed_sub(uint16_t a, float c) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  float d;
+  if constexpr (std::is_same<T, __half>::value)
+    asm("sub.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
+  else
+    asm("sub.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
+  return d;
+}
+// float(a) + c
+template <typename T>
+__device__ __forceinline__ float mixed_add(uint16_t a, float c) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  float d;
+  if constexpr (std::is_same<T, __half>::value)
+    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
+  else
+    asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
+  return d;
+}
+// float(a) * float(b) + c, product exact
+template <typename T>
+__device__ __forceinline__ float mixed_fma(uint16_t a, uint16_t b, float c) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  float d;
+  if constexpr (std::is_same<T, __half>::value)
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+  else
+    asm("fma.rn.f32.bf16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+  return d;
+}
+
 // Forward epilogue for one 16-byte vector: out = T(act(yh)) packed.
 template <typename T, int VE, int ACT>
 __device__ __forceinline__ uint4 act_pack16(const float (&yh)[VE]) {
@@ -553,6 +610,7 @@ struct Geom {
   // threads per group row (D / VE) are powers of two and CV <= 32.  tps_shift = log2(D / VE).
   int shuf, tps_shift;
   int red_floats;  // size of the reduction scratch `red` (forward kernels), set by the planner
+  int persist;     // fused forward: the grid holds the resident clusters only, each looping over items
   int dbg;         // experiments only: stop the fused forward kernel after stage `dbg` (0 = run normally)
 };
 

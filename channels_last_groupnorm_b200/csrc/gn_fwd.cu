@@ -31,13 +31,51 @@ __device__ __forceinline__ void welford_step(const float (&f)[VE], float (&mean)
   }
 }
 
+// 16-bit tensors accumulate shifted sums instead: with K a value of the thread's own data (its
+// first row),  s += x - K,  q += (x - K)^2;  the subtraction converts the 16-bit element on the fly
+// (mixed-precision sub), three instructions per element and no division in the loop.  Because K is
+// one of the samples, (K - mean)^2 <= M2, so q <= (n + 1) M2 and the cancellation in
+// M2 = q - s^2 / n costs at most (n + 1) ulp of the thread's M2 - n is the thread's row count, a
+// few hundred at most - where sums of raw squares would lose mean^2 / var.
+template <typename T, int VE, int KN>
+__device__ __forceinline__ void shifted_step(const uint4& w, const float (&K)[KN], float (&s)[VE], float (&q)[VE]) {
+  static_assert(sizeof(T) == 2 && VE == 8, "16-bit elements, 16-byte vectors");
+  const uint32_t r[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    uint16_t lo, hi;
+    split_halves(r[e], lo, hi);
+    const float d0 = mixed_sub<T>(lo, K[KN == 1 ? 0 : 2 * e]);
+    const float d1 = mixed_sub<T>(hi, K[KN == 1 ? 0 : 2 * e + 1]);
+    s[2 * e] += d0;
+    s[2 * e + 1] += d1;
+    q[2 * e] = fmaf(d0, d0, q[2 * e]);
+    q[2 * e + 1] = fmaf(d1, d1, q[2 * e + 1]);
+  }
+}
+
+// (s, q) about K over `rows` rows  ->  per-lane (mean, M2); s and q are overwritten.
+template <int VE, int KN>
+__device__ __forceinline__ void shifted_finish(const float (&K)[KN], int rows, float (&mean)[VE], float (&m2)[VE],
+                                               float& cnt) {
+  cnt = (float)rows;
+  const float inv = rows > 0 ? 1.0f / cnt : 0.f;
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    const float s = mean[e], q = m2[e];
+    const float ds = s * inv;
+    mean[e] = K[KN == 1 ? 0 : e] + ds;
+    m2[e] = fmaxf(fmaf(-s, ds, q), 0.f);
+  }
+}
+
 constexpr int kRingDepth = 8;  // rows in flight per thread in the multi-kernel streaming kernels
 
 // Per-thread running moments over the rows this thread owns (rows ty, ty + TY, ...) in the
 // multi-kernel path.  16-byte vectors go through a shared-memory ring with cp.async: kRingDepth
 // rows per thread are in flight without holding registers; slot s of the thread lives at
 // ring + s * ring_stride.  Other vector widths use plain loads.
-template <typename T, int VE>
+template <typename T, int VE, bool UNI>
 __device__ __forceinline__ void stream_moments(const T* __restrict__ gsrc, size_t gstep_elems, int iters,
                                                uint32_t ring, uint32_t ring_stride, float (&mean)[VE],
                                                float (&m2)[VE], float& cnt) {
@@ -51,18 +89,38 @@ __device__ __forceinline__ void stream_moments(const T* __restrict__ gsrc, size_
       }
       cp_async_commit();
     }
+    constexpr bool kShifted = sizeof(T) == 2;
+    constexpr int KN = UNI ? 1 : VE;
+    float K[KN];
+    if constexpr (kShifted) {
+      cp_async_wait<kRingDepth - 1>();  // row 0 has landed; its values are the shift
+#pragma unroll
+      for (int e = 0; e < KN; ++e) K[e] = 0.f;
+      if (iters > 0) {
+        float f0[VE];
+        unpack16<T, VE>(lds128(ring), f0);
+#pragma unroll
+        for (int e = 0; e < KN; ++e) K[e] = f0[e];
+      }
+    }
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kRingDepth - 1>();
       const uint32_t slot = ring + (i & (kRingDepth - 1)) * ring_stride;
-      float f[VE];
-      unpack16<T, VE>(lds128(slot), f);
+      const uint4 w = lds128(slot);
       if (i + kRingDepth < iters) {
         cp_async16(slot, gp);
         gp += gstep_elems;
       }
       cp_async_commit();
-      welford_step<VE>(f, mean, m2, cnt);
+      if constexpr (kShifted) {
+        shifted_step<T, VE, KN>(w, K, mean, m2);
+      } else {
+        float f[VE];
+        unpack16<T, VE>(w, f);
+        welford_step<VE>(f, mean, m2, cnt);
+      }
     }
+    if constexpr (kShifted) shifted_finish<VE, KN>(K, iters, mean, m2, cnt);
   } else {
     const T* gp = gsrc;
     for (int i = 0; i < iters; ++i) {
@@ -75,64 +133,121 @@ __device__ __forceinline__ void stream_moments(const T* __restrict__ gsrc, size_
   }
 }
 
-// Fused path, phase 1: the thread's rows (ty, ty + TY, ...) of its column vector are copied into
-// the shared-memory tile with cp.async - one commit group per row, eight rows in flight per
-// thread - and consumed (Welford) as they land.  Every thread reads back only what it copied
-// itself, so no block barrier is needed.
+constexpr int kFirstRows = 8;  // rows per thread copied ahead at the start of a CTA's first item
+
+// Fused path: `iters` of the thread's rows (ty, ty + TY, ...) of its column vector are copied into
+// the shared-memory tile with cp.async, one commit group per row.
+// Every thread reads back only what it copied itself, so no block barrier is needed.
 template <typename T, int VE>
-__device__ __forceinline__ void tile_fill_moments(const T* __restrict__ gsrc, size_t gstep_elems, uint32_t stile,
-                                                  uint32_t sstep_bytes, int iters, float (&mean)[VE], float (&m2)[VE],
-                                                  float& cnt) {
+__device__ __forceinline__ void tile_issue(const T* __restrict__ gsrc, size_t gstep_elems, uint32_t stile,
+                                           uint32_t sstep_bytes, int iters) {
   if constexpr (sizeof(T) * VE == 16) {
-    // one commit group per row, kTileDepth rows in flight per thread
-    constexpr int kTileDepth = 8;
-    const T* gp = gsrc;
-    uint32_t wp = stile;
-#pragma unroll
-    for (int d = 0; d < kTileDepth; ++d) {
-      if (d < iters) {
-        cp_async16(wp, gp);
-        wp += sstep_bytes;
-        gp += gstep_elems;
-      }
-      cp_async_commit();
-    }
-    uint32_t rp = stile;
-#pragma unroll 2
+#pragma unroll 4
     for (int i = 0; i < iters; ++i) {
-      cp_async_wait<kTileDepth - 1>();
-      float f[VE];
-      unpack16<T, VE>(lds128(rp), f);
-      rp += sstep_bytes;
-      if (i + kTileDepth < iters) {
-        cp_async16(wp, gp);
-        wp += sstep_bytes;
-        gp += gstep_elems;
-      }
+      cp_async16(stile, gsrc);
       cp_async_commit();
-      welford_step<VE>(f, mean, m2, cnt);
+      stile += sstep_bytes;
+      gsrc += gstep_elems;
     }
   } else {
-    const T* gp = gsrc;
     T* sp = reinterpret_cast<T*>(__cvta_shared_to_generic(stile));
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) sp[e] = gsrc[e];
+      gsrc += gstep_elems;
+      sp += sstep_bytes / sizeof(T);
+    }
+  }
+}
+
+// Fused path, phase 1: moments of the thread's rows in the tile, consumed as they land.  The rows
+// were copied by cp.async, one commit group per row in row order, and on entry no younger group of
+// the thread is in flight: row j may be read once at most iters - 1 - j groups are pending.
+// `feed`: only the first kLag rows have been issued so far (a CTA's first item); the others are
+// issued here, one per consumed row, from gfeed (row kLag of the thread) onwards - copying every
+// row at once at kernel start, when all CTAs do the same, floods the memory system.
+template <typename T, int VE, bool UNI>
+__device__ __forceinline__ void tile_moments(uint32_t stile, uint32_t sstep_bytes, int iters, float (&mean)[VE],
+                                             float (&m2)[VE], float& cnt, bool feed, const T* __restrict__ gfeed,
+                                             size_t gstep_elems) {
+  if constexpr (sizeof(T) * VE == 16) {
+    constexpr int kLag = kFirstRows;  // rows that may be in flight behind the one being consumed
+    constexpr bool kShifted = sizeof(T) == 2;
+    constexpr int KN = UNI ? 1 : VE;
+    float K[KN];
+    uint32_t rp = stile;
+    auto consume = [&]() {
+      const uint4 w = lds128(rp);
+      rp += sstep_bytes;
+      if constexpr (kShifted) {
+        shifted_step<T, VE, KN>(w, K, mean, m2);
+      } else {
+        float f[VE];
+        unpack16<T, VE>(w, f);
+        welford_step<VE>(f, mean, m2, cnt);
+      }
+    };
+    if constexpr (kShifted) {  // the shift: the values of row 0
+#pragma unroll
+      for (int e = 0; e < KN; ++e) K[e] = 0.f;
+      if (iters > 0) {
+        cp_async_wait_dyn8(min(iters, kLag) - 1);
+        float f0[VE];
+        unpack16<T, VE>(lds128(stile), f0);
+#pragma unroll
+        for (int e = 0; e < KN; ++e) K[e] = f0[e];
+      }
+    }
+    int i = 0;
+    uint32_t wp = stile + kLag * sstep_bytes;
+#pragma unroll 2
+    for (; i < iters - kLag; ++i) {
+      cp_async_wait<kLag - 1>();
+      consume();
+      if (feed) {
+        cp_async16(wp, gfeed);
+        cp_async_commit();
+        wp += sstep_bytes;
+        gfeed += gstep_elems;
+      }
+    }
+    const int rem = iters - i;  // <= kLag rows left: row (iters - 1 - t) needs at most t pending groups
+#define GNB200_TAIL_ROW(t) \
+  if (rem > t) {           \
+    cp_async_wait<t>();    \
+    consume();             \
+  }
+    GNB200_TAIL_ROW(7)
+    GNB200_TAIL_ROW(6)
+    GNB200_TAIL_ROW(5)
+    GNB200_TAIL_ROW(4)
+    GNB200_TAIL_ROW(3)
+    GNB200_TAIL_ROW(2)
+    GNB200_TAIL_ROW(1)
+    GNB200_TAIL_ROW(0)
+#undef GNB200_TAIL_ROW
+    static_assert(kLag == 8, "the tail above is written out for eight rows");
+    if constexpr (kShifted) shifted_finish<VE, KN>(K, iters, mean, m2, cnt);
+  } else {
+    const T* sp = reinterpret_cast<const T*>(__cvta_shared_to_generic(stile));
     for (int i = 0; i < iters; ++i) {
       float f[VE];
 #pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        sp[e] = gp[e];
-        f[e] = load_param<T>(gp, e);
-      }
-      gp += gstep_elems;
+      for (int e = 0; e < VE; ++e) f[e] = load_param<T>(sp, e);
       sp += sstep_bytes / sizeof(T);
       welford_step<VE>(f, mean, m2, cnt);
     }
   }
 }
 
-// Fused path, phase 2: y = act(x * a + b) from the tile to global memory.
+// Fused path, phase 2: y = act(x * a + b) from the tile to global memory.  With `refill` set, each
+// tile slot is refilled with the same row of the cluster's next item (`gnext`) as soon as it has
+// been read - one cp.async commit group per row - so the next item streams in while this one
+// streams out and the tile never sits half empty.
 template <typename T, int VE, int ACT>
 __device__ __forceinline__ void tile_apply(uint32_t stile, uint32_t sstep_bytes, T* __restrict__ gdst,
-                                           size_t gstep_elems, int iters, const float (&a)[VE], const float (&b)[VE]) {
+                                           size_t gstep_elems, int iters, const float (&a)[VE], const float (&b)[VE],
+                                           bool refill, const T* __restrict__ gnext) {
   constexpr bool FAST = sizeof(T) == 2;
   if constexpr (sizeof(T) * VE == 16) {
     uint32_t sp = stile;
@@ -141,6 +256,11 @@ __device__ __forceinline__ void tile_apply(uint32_t stile, uint32_t sstep_bytes,
     for (int i = 0; i < iters; ++i) {
       float f[VE];
       unpack16<T, VE>(lds128(sp), f);
+      if (refill) {
+        cp_async16(sp, gnext);
+        cp_async_commit();
+        gnext += gstep_elems;
+      }
       sp += sstep_bytes;
 #pragma unroll
       for (int e = 0; e < VE; ++e) f[e] = fmaf(f[e], a[e], b[e]);
@@ -148,11 +268,15 @@ __device__ __forceinline__ void tile_apply(uint32_t stile, uint32_t sstep_bytes,
       gp += gstep_elems;
     }
   } else {
-    const T* sp = reinterpret_cast<const T*>(__cvta_shared_to_generic(stile));
+    T* sp = reinterpret_cast<T*>(__cvta_shared_to_generic(stile));
     T* gp = gdst;
     for (int i = 0; i < iters; ++i) {
 #pragma unroll
-      for (int e = 0; e < VE; ++e) gp[e] = store_param<T>(act_fwd<ACT, FAST>(fmaf(load_param<T>(sp, e), a[e], b[e])));
+      for (int e = 0; e < VE; ++e) {
+        gp[e] = store_param<T>(act_fwd<ACT, FAST>(fmaf(load_param<T>(sp, e), a[e], b[e])));
+        if (refill) sp[e] = gnext[e];
+      }
+      if (refill) gnext += gstep_elems;
       sp += sstep_bytes / sizeof(T);
       gp += gstep_elems;
     }
@@ -232,6 +356,34 @@ __device__ __forceinline__ void lane_affine(const T* gamma, const T* beta, const
   }
 }
 
+// The same from parameter vectors fetched earlier (raw 16-byte loads issued before phase 1 so that
+// their latency is off the critical path between the statistics and the output pass).
+template <typename T, int VE, bool UNI>
+__device__ __forceinline__ void lane_affine_raw(const uint4& ga_raw, const uint4& be_raw, const float* stat_mean,
+                                                const float* stat_rstd, int g_base, int c_first, const FastDiv div_D,
+                                                float (&a)[VE], float (&b)[VE]) {
+  static_assert(sizeof(T) * VE == 16, "16-byte vectors only");
+  float ga[VE], be[VE];
+  unpack16<T, VE>(ga_raw, ga);
+  unpack16<T, VE>(be_raw, be);
+  if constexpr (UNI) {
+    const int s = div_D.div(c_first) - g_base;
+    const float mu = stat_mean[s], rs = stat_rstd[s];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      a[e] = rs * ga[e];
+      b[e] = fmaf(-mu, a[e], be[e]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const int s = div_D.div(c_first + e) - g_base;
+      a[e] = stat_rstd[s] * ga[e];
+      b[e] = fmaf(-stat_mean[s], a[e], be[e]);
+    }
+  }
+}
+
 // CTA-local moments of every group slot of the column block from the per-thread Welford states:
 // first the slot means (sum of cnt * mean / n), then the squared deviations around them.
 //   slot[s]            = local mean      slot[slots + s] = local M2      slot[2 * slots + s] = local count
@@ -282,117 +434,146 @@ __device__ __forceinline__ void cta_slot_moments(const Geom& g, const float (&me
 }
 
 // ------------------------------------------------------------------------------------------------
-// fused one-pass kernel.  grid.x = N * ncb * k, cluster = (k,1,1).
-// dynamic smem: [tile rows_per_cta * CV packs][red TY*CW][tmp slots][slot 3*slots][stat 2*slots]
+// fused one-pass kernel.  cluster = (k,1,1); an item is one (sample, column block) slab and each
+// CTA of the cluster owns rows_per_cta of its rows.  The grid holds the clusters that are resident
+// at once (or one per item if there are fewer items); cluster c works on items c, c + n_clusters,
+// ...  While a CTA writes the y rows of one item it refills the tile, row by row, with the x rows
+// of its next item, so DRAM reads and writes overlap and the exchange of statistics of one item
+// is the only time a CTA does not move data.
+// dynamic smem: [tile rows_per_cta * CV packs][red][tmp slots][slot 2 x 3*slots][stat 2*slots]
 // ------------------------------------------------------------------------------------------------
-template <typename T, int VE, int ACT, bool UNI>
-__global__ void __launch_bounds__(kMaxThreads)
+// MAXT: CTA size class.  128-thread launches are compiled for six CTAs per SM (<= 80 registers).
+template <typename T, int VE, int ACT, bool UNI, int MAXT>
+__global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
     gn_fwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                         T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, float eps,
                         const Geom g) {
   extern __shared__ uint4 smem_raw[];
   using P = Pack<T, VE>;
+  constexpr bool kVec = sizeof(T) * VE == 16;
   const unsigned k = cluster_nctarank(), rank = cluster_ctarank();
-  const int item = blockIdx.x / k;  // (n, cb); k is a power of two
-  const int n = g.div_ncb.div(item), cb = item - n * g.ncb;
-  const int c0 = cb * g.CW;
+  const int n_items = g.N * g.ncb;
+  const int n_clusters = (int)(gridDim.x / k);  // k is a power of two
   const int r0 = min((int)rank * g.rows_per_cta, g.R);
   const int nrows = min(g.rows_per_cta, g.R - r0);
 
-  P* tile = reinterpret_cast<P*>(smem_raw);
   const size_t tile_bytes = ((size_t)g.rows_per_cta * g.CV * sizeof(P) + 15) & ~(size_t)15;
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
   float* tmp = red + g.red_floats;
-  float* slot = tmp + g.slots;        // local mean | local M2 | local count
-  float* stat = slot + 3 * g.slots;   // mean[slots], rstd[slots]
+  float* slots2 = tmp + g.slots;       // two copies of: local mean | local M2 | local count
+  float* stat = slots2 + 6 * g.slots;  // mean[slots], rstd[slots]
 
   const int tid = threadIdx.x;
   const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
-  const bool streaming = (ty < g.TY) && (c0 + tx * VE < g.C);
-  float mean[VE], m2[VE], cnt = 0.f;
-#pragma unroll
-  for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
-  if (g.dbg == 1) return;
-  // this thread's rows: r0 + ty, r0 + ty + TY, ...; its tile slots are CV * TY vectors apart
-  const size_t base = ((size_t)n * g.R + r0 + ty) * g.C + c0 + (size_t)tx * VE;
+  // the fused plans use column blocks that divide C, so a thread's column is valid for every item
+  const bool streaming = (ty < g.TY) && (tx * VE < g.CW);
   const int iters = (streaming && ty < nrows) ? (nrows - ty + g.TY - 1) / g.TY : 0;
-  const uint32_t stile = smem_addr(tile + ty * g.CV + tx);
+  const uint32_t stile = smem_addr(reinterpret_cast<P*>(smem_raw) + ty * g.CV + tx);
   const uint32_t sstep = (uint32_t)(g.TY * g.CV * sizeof(P));
   const size_t gstep = (size_t)g.TY * g.C;
-  tile_fill_moments<T, VE>(x + base, gstep, stile, sstep, iters, mean, m2, cnt);
-  if (g.dbg == 2) {
-    if (mean[0] + m2[VE - 1] + cnt == -1.f) mean_out[0] = 0.f;
-    return;
-  }
-  int g_lo, n_slots;
-  cb_groups(g, c0, g_lo, n_slots);
-  if (UNI && g.shuf) {
-    // shuffle reductions: red doubles as the two warp-sum buffers
-    float sm = 0.f;
-#pragma unroll
-    for (int e = 0; e < VE; ++e) sm += mean[e];
-    const float n_loc = (float)nrows * (float)g.D;
-    const float tot = cta_slot_sum_shuf(g, cnt * sm, tx, red);
-    const float lm = n_loc > 0.f ? tot / n_loc : 0.f;
-    float acc = 0.f, dev = 0.f;
-#pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const float d = mean[e] - lm;
-      dev = fmaf(d, d, dev);
-      acc += m2[e];
-    }
-    const float m2loc = cta_slot_sum_shuf(g, fmaf(cnt, dev, acc), tx, red + 512);
-    if (tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
-      const int s = tid >> g.tps_shift;
-      slot[s] = lm;
-      slot[g.slots + s] = m2loc;
-      slot[2 * g.slots + s] = n_loc;
-    }
-  } else {
-    cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
-  }
+  const size_t row_off = ((size_t)r0 + ty) * g.C + (size_t)tx * VE;
 
-  // combine the k CTA-local moments (rank order -> every CTA of the cluster gets bit-identical
-  // statistics):  mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2
-  if (g.dbg == 3) return;
-  cluster_sync_all();
-  float* stage = red;  // k * 3 * slots floats: the peers' slot arrays, gathered in parallel
-  cluster_gather(slot, 3 * g.slots, k, stage);
-  for (int s = tid; s < n_slots; s += blockDim.x) {
-    float wsum = 0.f, ntot = 0.f;
-    for (unsigned q = 0; q < k; ++q) {
-      const float* pq = stage + q * 3 * g.slots;
-      wsum = fmaf(pq[2 * g.slots + s], pq[s], wsum);
-      ntot += pq[2 * g.slots + s];
-    }
-    const float mu = wsum / ntot;
-    float m2tot = 0.f;
-    for (unsigned q = 0; q < k; ++q) {
-      const float* pq = stage + q * 3 * g.slots;
-      const float d = pq[s] - mu;
-      m2tot += fmaf(pq[2 * g.slots + s] * d, d, pq[g.slots + s]);
-    }
-    const float rs = rsqrtf(fmaxf(m2tot / ntot, 0.f) + eps);
-    stat[s] = mu;
-    stat[g.slots + s] = rs;
-    if (rank == 0) {
-      mean_out[(size_t)n * g.G + g_lo + s] = mu;
-      rstd_out[(size_t)n * g.G + g_lo + s] = rs;
-    }
+  int item = (int)(blockIdx.x / k);
+  unsigned parity = 0;
+  if (item < n_items) {
+    const int n = g.div_ncb.div(item), cb = item - n * g.ncb;
+    tile_issue<T, VE>(x + (size_t)n * g.R * g.C + cb * g.CW + row_off, gstep, stile, sstep,
+                      kVec ? min(iters, kFirstRows) : iters);
   }
-  cluster_arrive();  // this CTA no longer reads its peers' shared memory
-  __syncthreads();
-  if (g.dbg == 4) {
-    cluster_wait();
-    return;
-  }
+  bool first = true;
+  for (; item < n_items; item += n_clusters, parity ^= 1u) {
+    const int n = g.div_ncb.div(item), cb = item - n * g.ncb;
+    const int c0 = cb * g.CW;
+    const size_t base = (size_t)n * g.R * g.C + c0 + row_off;
+    float* slot = slots2 + parity * 3 * g.slots;
+    uint4 ga_raw = make_uint4(0, 0, 0, 0), be_raw = make_uint4(0, 0, 0, 0);
+    if constexpr (kVec) {
+      if (streaming) {
+        ga_raw = *reinterpret_cast<const uint4*>(gamma + c0 + tx * VE);
+        be_raw = *reinterpret_cast<const uint4*>(beta + c0 + tx * VE);
+      }
+    }
+    float mean[VE], m2[VE], cnt = 0.f;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
+    tile_moments<T, VE, UNI>(stile, sstep, iters, mean, m2, cnt, first, x + base + (size_t)kFirstRows * gstep, gstep);
+    first = false;
+    int g_lo, n_slots;
+    cb_groups(g, c0, g_lo, n_slots);
+    if (UNI && g.shuf) {
+      // shuffle reductions: red doubles as the two warp-sum buffers
+      float sm = 0.f;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) sm += mean[e];
+      const float n_loc = (float)nrows * (float)g.D;
+      const float tot = cta_slot_sum_shuf(g, cnt * sm, tx, red);
+      const float lm = n_loc > 0.f ? tot / n_loc : 0.f;
+      float acc = 0.f, dev = 0.f;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float d = mean[e] - lm;
+        dev = fmaf(d, d, dev);
+        acc += m2[e];
+      }
+      const float m2loc = cta_slot_sum_shuf(g, fmaf(cnt, dev, acc), tx, red + 512);
+      if (tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
+        const int s = tid >> g.tps_shift;
+        slot[s] = lm;
+        slot[g.slots + s] = m2loc;
+        slot[2 * g.slots + s] = n_loc;
+      }
+    } else {
+      cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
+    }
 
-  if (streaming) {
-    float a[VE], b[VE];
-    lane_affine<T, VE, UNI>(gamma, beta, stat, stat + g.slots, g_lo, c0 + tx * VE, g.div_D, a, b);
-    tile_apply<T, VE, ACT>(stile, sstep, y + base, gstep, iters, a, b);
+    // combine the k CTA-local moments (rank order -> every CTA of the cluster gets bit-identical
+    // statistics):  mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2.
+    // One cluster barrier per item: `slot` alternates between two copies, and a CTA rewrites a
+    // copy only after the next item's barrier, which no peer passes before its reads of this one.
+    cluster_sync_all();
+    float* stage = red;  // k * 3 * slots floats: the peers' slot arrays, gathered in parallel
+    cluster_gather(slot, 3 * g.slots, k, stage);
+    for (int s = tid; s < n_slots; s += blockDim.x) {
+      float wsum = 0.f, ntot = 0.f;
+      for (unsigned q = 0; q < k; ++q) {
+        const float* pq = stage + q * 3 * g.slots;
+        wsum = fmaf(pq[2 * g.slots + s], pq[s], wsum);
+        ntot += pq[2 * g.slots + s];
+      }
+      const float mu = wsum / ntot;
+      float m2tot = 0.f;
+      for (unsigned q = 0; q < k; ++q) {
+        const float* pq = stage + q * 3 * g.slots;
+        const float d = pq[s] - mu;
+        m2tot += fmaf(pq[2 * g.slots + s] * d, d, pq[g.slots + s]);
+      }
+      const float rs = rsqrtf(fmaxf(m2tot / ntot, 0.f) + eps);
+      stat[s] = mu;
+      stat[g.slots + s] = rs;
+      if (rank == 0) {
+        mean_out[(size_t)n * g.G + g_lo + s] = mu;
+        rstd_out[(size_t)n * g.G + g_lo + s] = rs;
+      }
+    }
+    __syncthreads();
+
+    if (streaming) {
+      float a[VE], b[VE];
+      if constexpr (kVec)
+        lane_affine_raw<T, VE, UNI>(ga_raw, be_raw, stat, stat + g.slots, g_lo, c0 + tx * VE, g.div_D, a, b);
+      else
+        lane_affine<T, VE, UNI>(gamma, beta, stat, stat + g.slots, g_lo, c0 + tx * VE, g.div_D, a, b);
+      // the cluster's next item, whose rows take over the tile slots as they are read
+      const int nxt = item + n_clusters;
+      const bool refill = nxt < n_items;
+      const int n2 = refill ? g.div_ncb.div(nxt) : 0, cb2 = nxt - n2 * g.ncb;
+      tile_apply<T, VE, ACT>(stile, sstep, y + base, gstep, iters, a, b, refill,
+                             x + (size_t)n2 * g.R * g.C + (refill ? cb2 * g.CW : 0) + row_off);
+    }
+    // No barrier here: the next item's reductions write red / tmp / slot before their first
+    // barrier, none of which is read by the output pass, and `stat` is rewritten only after it.
   }
-  cluster_wait();  // do not exit (and release shared memory) while a peer may still read `slot`
+  cluster_sync_all();  // do not exit (and release shared memory) while a peer may still read `slots2`
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -425,7 +606,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
   const size_t base = ((size_t)n * g.R + r0 + ty) * g.C + c0 + (size_t)tx * VE;
   const int iters = (streaming && ty < nrows) ? (nrows - ty + g.TY - 1) / g.TY : 0;
-  stream_moments<T, VE>(x + base, (size_t)g.TY * g.C, iters, smem_addr(smem_raw) + tid * 16, blockDim.x * 16, mean, m2,
+  stream_moments<T, VE, UNI>(x + base, (size_t)g.TY * g.C, iters, smem_addr(smem_raw) + tid * 16, blockDim.x * 16, mean, m2,
                         cnt);
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
@@ -507,7 +688,7 @@ __global__ void __launch_bounds__(kMaxThreads)
 // ------------------------------------------------------------------------------------------------
 template <typename T, int VE, int ACT, bool UNI>
 static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t stream) {
-  auto kern = gn_fwd_fused_kernel<T, VE, ACT, UNI>;
+  auto kern = p.threads <= 128 ? gn_fwd_fused_kernel<T, VE, ACT, UNI, 128> : gn_fwd_fused_kernel<T, VE, ACT, UNI, kMaxThreads>;
   cudaError_t err = ensure_kernel_attributes((const void*)kern, p.smem_bytes, p.geom.k > 8);
   if (err != cudaSuccess) return err;
   cudaLaunchConfig_t cfg = {};
@@ -522,6 +703,14 @@ static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t st
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (p.geom.persist) {  // as many clusters as are resident at once
+    int clusters = 0;
+    err = resident_clusters((const void*)kern, &cfg, &clusters);
+    if (err != cudaSuccess) return err;
+    const long long items = (long long)p.geom.N * p.geom.ncb;
+    if (clusters > items) clusters = (int)items;
+    cfg.gridDim.x = (unsigned)clusters * (unsigned)p.geom.k;
+  }
   return cudaLaunchKernelEx(&cfg, kern, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, (T*)c.y, c.mean, c.rstd,
                             c.eps, p.geom);
 }

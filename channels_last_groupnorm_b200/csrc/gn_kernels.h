@@ -59,6 +59,10 @@ size_t plan_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtyp
 // device and kernel; later calls with a request that is already covered cost one map lookup.
 cudaError_t ensure_kernel_attributes(const void* func, size_t smem_bytes, bool nonportable_cluster);
 
+// Number of clusters of `cfg` (cluster dimension, block size and dynamic shared memory set) that
+// can be resident on the current device at once (>= 1), cached per device, kernel and shape.
+cudaError_t resident_clusters(const void* func, const cudaLaunchConfig_t* cfg, int* clusters);
+
 cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream);
 cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream);
 

@@ -65,7 +65,7 @@ size_t fwd_red_floats(int CW, int TY, int slots) {
 }
 size_t fwd_fold_floats(int CW, int TY, int slots, int threads) {
   (void)threads;
-  return fwd_red_floats(CW, TY, slots) + (size_t)6 * slots + 8;
+  return fwd_red_floats(CW, TY, slots) + (size_t)9 * slots + 8;
 }
 size_t bwd_red_floats(int CW, int TY, int slots) {
   size_t r = (size_t)2 * TY * CW;
@@ -146,9 +146,10 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   p.ws_bytes = sh.direction == 0 ? 0 : (size_t)sh.N * k * sh.C * 2 * sizeof(float);  // channel sums per cluster rank
   p.launches = sh.direction == 0 ? 1 : 2;
   p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, rows, k, slots, k};
+  // forward: launch only the clusters that are resident at once; each loops over its items
+  p.geom.persist = (sh.direction == 0 && env_int("GNB200_PERSIST", 1) != 0) ? 1 : 0;
   fill_divisors(&p.geom, ve, sh.direction);
   if (p.grid > 0x7fffffffLL) return false;
-  *out = p;
 
   // Heuristic fitted to measurements on B200 (bf16 / fp16, N x 256 x 64 x 64 and similar):
   // the kernels are bound by instruction issue and latency rather than DRAM, so co-resident CTAs
@@ -175,6 +176,7 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   const double rpt_eff = rpt >= 16 ? 1.0 : rpt >= 8 ? 0.93 : rpt >= 4 ? 0.85 : 0.75;
   const double sync_eff = 1.0 - 0.004 * k;  // mild preference for smaller clusters
   *score = sms * seg_eff * occ * rpt_eff * sync_eff;
+  *out = p;
   return true;
 }
 
@@ -267,6 +269,7 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
     p.launches = 4;
   }
   p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, (int)rows, (int)chunks, slots, 1};
+  p.geom.persist = 0;
   fill_divisors(&p.geom, ve, sh.direction);
   *out = p;
   return true;
@@ -312,6 +315,45 @@ cudaError_t ensure_kernel_attributes(const void* func, size_t smem_bytes, bool n
     if (err != cudaSuccess) return err;
     st.second = true;
   }
+  return cudaSuccess;
+}
+
+cudaError_t resident_clusters(const void* func, const cudaLaunchConfig_t* cfg, int* clusters) {
+  struct Key {
+    int dev;
+    const void* func;
+    unsigned threads, k;
+    size_t smem;
+    bool operator<(const Key& o) const {
+      if (dev != o.dev) return dev < o.dev;
+      if (func != o.func) return func < o.func;
+      if (threads != o.threads) return threads < o.threads;
+      if (k != o.k) return k < o.k;
+      return smem < o.smem;
+    }
+  };
+  static std::mutex mu;
+  static std::map<Key, int> cache;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  unsigned k = 1;
+  for (unsigned i = 0; i < cfg->numAttrs; ++i)
+    if (cfg->attrs[i].id == cudaLaunchAttributeClusterDimension) k = cfg->attrs[i].val.clusterDim.x;
+  const Key key = {dev, func, cfg->blockDim.x, k, cfg->dynamicSmemBytes};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    // the query wants a grid that is a multiple of the cluster size; the answer does not depend on it
+    cudaLaunchConfig_t q = *cfg;
+    q.gridDim = dim3(k, 1, 1);
+    int n = 0;
+    err = cudaOccupancyMaxActiveClusters(&n, func, &q);
+    if (err != cudaSuccess) return err;
+    if (n < 1) n = 1;
+    it = cache.emplace(key, n).first;
+  }
+  *clusters = it->second;
   return cudaSuccess;
 }
 
