@@ -149,13 +149,6 @@ __device__ __forceinline__ void stream_bwd_sums(const T* __restrict__ gx, const 
 
 constexpr int kXRing = 4;  // x rows in flight per thread in the fused backward kernel
 
-// One row of the fused path's copy pipeline: x into ring slot `slot`, dy into its tile row.
-template <typename T>
-__device__ __forceinline__ void bwd_issue_row(const T* gx, const T* gd, uint32_t ring_slot, uint32_t tile_row) {
-  cp_async16(ring_slot, gx);
-  cp_async16(tile_row, gd);
-}
-
 // Phase 1 of the fused path.  dy rows are copied straight into the shared-memory tile, x rows go
 // through a kXRing-deep shared-memory ring (cp.async, one commit group per row, kXRing rows in
 // flight per thread).  dyh = dy * act'(yh) is accumulated into the channel sums and written back
@@ -175,14 +168,32 @@ __device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, con
       a[e] = L.r[e] * L.ga[e];
       b[e] = fmaf(L.nmr[e], L.ga[e], L.be[e]);
     }
+    // dy needs no ring - every row has its own tile slot - so it runs kXRing rows ahead of x:
+    // commit group j holds x row j and dy row j + kXRing, after a first group with dy rows
+    // 0 .. kXRing - 1.  Twice the bytes in flight for the same shared memory.
     uint32_t wd = sd;
+    int dy_issued = 0;
 #pragma unroll
     for (int d = 0; d < kXRing; ++d) {
       if (d < iters) {
-        bwd_issue_row<T>(gx, gd, ring + d * ring_stride, wd);
-        gx += gstep_elems;
+        cp_async16(wd, gd);
         gd += gstep_elems;
         wd += sstep_bytes;
+        ++dy_issued;
+      }
+    }
+    cp_async_commit();
+#pragma unroll
+    for (int d = 0; d < kXRing; ++d) {
+      if (d < iters) {
+        cp_async16(ring + d * ring_stride, gx);
+        gx += gstep_elems;
+      }
+      if (dy_issued < iters) {
+        cp_async16(wd, gd);
+        gd += gstep_elems;
+        wd += sstep_bytes;
+        ++dy_issued;
       }
       cp_async_commit();
     }
@@ -194,10 +205,14 @@ __device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, con
       unpack16<T, VE>(lds128(slot), fx);
       unpack16<T, VE>(lds128(rd), fd);
       if (i + kXRing < iters) {
-        bwd_issue_row<T>(gx, gd, slot, wd);
+        cp_async16(slot, gx);
         gx += gstep_elems;
+      }
+      if (dy_issued < iters) {
+        cp_async16(wd, gd);
         gd += gstep_elems;
         wd += sstep_bytes;
+        ++dy_issued;
       }
       cp_async_commit();
       if constexpr (kRaw)
@@ -410,16 +425,11 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   float s1[VE], s2[VE];
 #pragma unroll
   for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
-  if (g.dbg == 1) return;
   if (streaming) {
     lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
     tile_fill_bwd_sums<T, VE, ACT>(x + base, dy + base, gstep, ring, ring_stride, sd, sstep, iters, L, s1, s2);
   }
 
-  if (g.dbg == 2) {
-    if (s1[0] + s2[VE - 1] == -1.2345f) sums[0] = 0.f;
-    return;
-  }
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
   const int c_valid = min(g.CW, g.C - c0);
@@ -485,12 +495,10 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
     coef[s] = a1 * inv_m;
     coef[g.slots + s] = a2 * inv_m;
   }
-  cluster_arrive();  // this CTA no longer reads its peers' shared memory
+  // This CTA no longer reads its peers' shared memory.  The arrival publishes nothing, so it does
+  // not have to wait for the channel sums stored to global memory above.
+  cluster_arrive_relaxed();
   __syncthreads();
-  if (g.dbg == 4) {
-    cluster_wait();
-    return;
-  }
 
   if (streaming) {
     float A[VE], B[VE];

@@ -568,6 +568,11 @@ __device__ __forceinline__ unsigned cluster_nctarank() {
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
+// Arrival that publishes nothing: it only tells the peers that this CTA is done reading their
+// shared memory.  Unlike the release form it does not wait for the CTA's outstanding global stores.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -610,7 +615,7 @@ struct Geom {
   // threads per group row (D / VE) are powers of two and CV <= 32.  tps_shift = log2(D / VE).
   int shuf, tps_shift;
   int red_floats;  // size of the reduction scratch `red` (forward kernels), set by the planner
-  int persist;     // fused forward: the grid holds the resident clusters only, each looping over items
+  int persist;     // fused kernels: the grid holds the resident clusters only, each looping over items
   int dbg;         // experiments only: stop the fused forward kernel after stage `dbg` (0 = run normally)
 };
 
@@ -705,10 +710,18 @@ __device__ __forceinline__ void cta_channel_sums(const Geom& g, const float (&s1
   float* red1 = red;
   float* red2 = red + TY * CW;
   if (ty < TY) {
+    if constexpr (VE % 4 == 0) {  // 16-byte stores: no bank conflicts (CW is a multiple of VE)
 #pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      red1[ty * CW + tx * VE + e] = s1[e];
-      red2[ty * CW + tx * VE + e] = s2[e];
+      for (int e = 0; e < VE; e += 4) {
+        *reinterpret_cast<float4*>(red1 + ty * CW + tx * VE + e) = make_float4(s1[e], s1[e + 1], s1[e + 2], s1[e + 3]);
+        *reinterpret_cast<float4*>(red2 + ty * CW + tx * VE + e) = make_float4(s2[e], s2[e + 1], s2[e + 2], s2[e + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        red1[ty * CW + tx * VE + e] = s1[e];
+        red2[ty * CW + tx * VE + e] = s2[e];
+      }
     }
   }
   __syncthreads();

@@ -556,6 +556,9 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
       }
     }
     __syncthreads();
+    // Last item: this CTA will not read its peers' shared memory again.  Saying so now, before the
+    // y rows are written, keeps the exit barrier below from waiting for those stores.
+    if (item + n_clusters >= n_items) cluster_arrive_relaxed();
 
     if (streaming) {
       float a[VE], b[VE];
@@ -573,7 +576,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
     // No barrier here: the next item's reductions write red / tmp / slot before their first
     // barrier, none of which is read by the output pass, and `stat` is rewritten only after it.
   }
-  cluster_sync_all();  // do not exit (and release shared memory) while a peer may still read `slots2`
+  cluster_wait();  // do not exit (and release shared memory) while a peer may still read `slots2`
 }
 
 // ------------------------------------------------------------------------------------------------
