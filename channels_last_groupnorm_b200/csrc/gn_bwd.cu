@@ -155,11 +155,59 @@ constexpr int kXRing = 4;  // x rows in flight per thread in the fused backward 
 // over the dy tile, rounded to T, so that phase 2 does not evaluate the activation derivative
 // again.  (For 16-bit T this rounds dyh once more than a recompute would: half a unit in the last
 // place of T on one term of dx.)  x is not kept on chip: phase 2 reads it again from L2.
+// State of the copy pipeline between its start (tile_fill_start) and the loop that consumes it.
+template <typename T>
+struct BwdPipe {
+  const T* gx;
+  const T* gd;
+  uint32_t wd;
+  int dy_issued;
+};
+
+// Starts the copies of phase 1.  dy needs no ring - every row has its own tile slot - so it runs
+// kXRing rows ahead of x: commit group j holds x row j and dy row j + kXRing, after a first group
+// with dy rows 0 .. kXRing - 1.  Called before the thread fetches its parameters and statistics,
+// so that their latency overlaps the first rows' instead of preceding it.
+template <typename T, int VE>
+__device__ __forceinline__ BwdPipe<T> tile_fill_start(const T* __restrict__ gx, const T* __restrict__ gd,
+                                                      size_t gstep_elems, uint32_t ring, uint32_t ring_stride,
+                                                      uint32_t sd, uint32_t sstep_bytes, int iters) {
+  BwdPipe<T> p = {gx, gd, sd, 0};
+  if constexpr (sizeof(T) * VE == 16) {
+#pragma unroll
+    for (int d = 0; d < kXRing; ++d) {
+      if (d < iters) {
+        cp_async16(p.wd, p.gd);
+        p.gd += gstep_elems;
+        p.wd += sstep_bytes;
+        ++p.dy_issued;
+      }
+    }
+    cp_async_commit();
+#pragma unroll
+    for (int d = 0; d < kXRing; ++d) {
+      if (d < iters) {
+        cp_async16(ring + d * ring_stride, p.gx);
+        p.gx += gstep_elems;
+      }
+      if (p.dy_issued < iters) {
+        cp_async16(p.wd, p.gd);
+        p.gd += gstep_elems;
+        p.wd += sstep_bytes;
+        ++p.dy_issued;
+      }
+      cp_async_commit();
+    }
+  }
+  return p;
+}
+
 template <typename T, int VE, int ACT>
-__device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, const T* __restrict__ gd,
-                                                   size_t gstep_elems, uint32_t ring, uint32_t ring_stride,
-                                                   uint32_t sd, uint32_t sstep_bytes, int iters,
+__device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep_elems, uint32_t ring,
+                                                   uint32_t ring_stride, uint32_t sd, uint32_t sstep_bytes, int iters,
                                                    const BwdLane<T, VE>& L, float (&s1)[VE], float (&s2)[VE]) {
+  const T* gx = pipe.gx;
+  const T* gd = pipe.gd;
   if constexpr (sizeof(T) * VE == 16) {
     constexpr bool kRaw = sizeof(T) == 2;
     float a[VE], b[VE];
@@ -168,35 +216,8 @@ __device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, con
       a[e] = L.r[e] * L.ga[e];
       b[e] = fmaf(L.nmr[e], L.ga[e], L.be[e]);
     }
-    // dy needs no ring - every row has its own tile slot - so it runs kXRing rows ahead of x:
-    // commit group j holds x row j and dy row j + kXRing, after a first group with dy rows
-    // 0 .. kXRing - 1.  Twice the bytes in flight for the same shared memory.
-    uint32_t wd = sd;
-    int dy_issued = 0;
-#pragma unroll
-    for (int d = 0; d < kXRing; ++d) {
-      if (d < iters) {
-        cp_async16(wd, gd);
-        gd += gstep_elems;
-        wd += sstep_bytes;
-        ++dy_issued;
-      }
-    }
-    cp_async_commit();
-#pragma unroll
-    for (int d = 0; d < kXRing; ++d) {
-      if (d < iters) {
-        cp_async16(ring + d * ring_stride, gx);
-        gx += gstep_elems;
-      }
-      if (dy_issued < iters) {
-        cp_async16(wd, gd);
-        gd += gstep_elems;
-        wd += sstep_bytes;
-        ++dy_issued;
-      }
-      cp_async_commit();
-    }
+    uint32_t wd = pipe.wd;
+    int dy_issued = pipe.dy_issued;
     uint32_t rd = sd;
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kXRing - 1>();
@@ -245,6 +266,22 @@ __device__ __forceinline__ void tile_fill_bwd_sums(const T* __restrict__ gx, con
   }
 }
 
+// Starts the ring of phase 2: the thread's first kXRing x rows, one commit group each.
+template <typename T, int VE>
+__device__ __forceinline__ void tile_bwd_dx_start(const T* __restrict__ gx, size_t gstep_elems, uint32_t ring,
+                                                  uint32_t ring_stride, int iters) {
+  if constexpr (sizeof(T) * VE == 16) {
+#pragma unroll
+    for (int d = 0; d < kXRing; ++d) {
+      if (d < iters) {
+        cp_async16(ring + d * ring_stride, gx);
+        gx += gstep_elems;
+      }
+      cp_async_commit();
+    }
+  }
+}
+
 // Phase 2 of the fused path: dx = ag * dyh + (nb * xh + na); dyh from the shared-memory tile, x
 // a second time from global memory (an L2 hit: it was read microseconds earlier) through the same
 // ring.  ag = rstd * gamma, nb = -rstd * B, na = -rstd * A per lane.
@@ -270,14 +307,7 @@ __device__ __forceinline__ void tile_bwd_dx(const T* __restrict__ gx, uint32_t r
       c1[e] = nb[e] * L.r[e];
       c2[e] = fmaf(nb[e], L.nmr[e], na[e]);
     }
-#pragma unroll
-    for (int d = 0; d < kXRing; ++d) {
-      if (d < iters) {
-        cp_async16(ring + d * ring_stride, gx);
-        gx += gstep_elems;
-      }
-      cp_async_commit();
-    }
+    gx += (size_t)min(iters, kXRing) * gstep_elems;  // tile_bwd_dx_start has issued these rows
     T* gp = gdst;
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kXRing - 1>();
@@ -380,7 +410,8 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
 
 // ------------------------------------------------------------------------------------------------
 // fused kernel.  grid.x = N * ncb * k, cluster (k,1,1).
-// dynamic smem: [dyh tile][x ring kXRing*threads*16 B, shared with red][part 2*max(threads,CW)][chan 2*CW][slot partial 2*slots][coef 2*slots]
+// dynamic smem: [dyh tile][x ring kXRing*threads*16 B][red][generic reductions only: part 2*max(threads,CW), chan 2*CW]
+//               [group partials 2*slots][coef 2*slots]
 // scratch out : sums[((n * k + rank) * C + c) * 2 + {0,1}] = S1, S2 over this CTA's rows
 // ------------------------------------------------------------------------------------------------
 // MAXT: CTA size class.  128-thread launches are compiled for five CTAs per SM (<= 96 registers).
@@ -403,13 +434,11 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   P* tile_dy = reinterpret_cast<P*>(smem_raw);
   const uint32_t ring = smem_addr(reinterpret_cast<char*>(smem_raw) + tile_bytes) + threadIdx.x * 16;
   const uint32_t ring_stride = blockDim.x * 16;
-  // the reduction scratch `red` shares its bytes with the ring: the ring is idle between the two
-  // streaming phases, which is exactly when the reductions run
-  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
-  const size_t shared_bytes = max(ring_bytes, (size_t)g.red_floats * sizeof(float));
-  float* part = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes + shared_bytes);
-  float* chan = part + 2 * max((int)blockDim.x, g.CW);
-  float* spart = chan + 2 * g.CW;  // [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 over this CTA's rows
+  float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes + ring_bytes);
+  const bool shuf = UNI && g.shuf;
+  float* part = red + g.red_floats;                      // generic reductions only
+  float* chan = part + 2 * max((int)blockDim.x, g.CW);  // generic reductions only
+  float* spart = shuf ? part : chan + 2 * g.CW;  // [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 over this CTA's rows
   float* coef = spart + 2 * g.slots;  // A[s], B[slots + s]
 
   const int tid = threadIdx.x;
@@ -426,15 +455,16 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
 #pragma unroll
   for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
   if (streaming) {
+    const BwdPipe<T> pipe = tile_fill_start<T, VE>(x + base, dy + base, gstep, ring, ring_stride, sd, sstep, iters);
     lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
-    tile_fill_bwd_sums<T, VE, ACT>(x + base, dy + base, gstep, ring, ring_stride, sd, sstep, iters, L, s1, s2);
+    tile_fill_bwd_sums<T, VE, ACT>(pipe, gstep, ring, ring_stride, sd, sstep, iters, L, s1, s2);
+    // the first x rows of phase 2 (L2 hits) travel while the cluster exchanges its sums
+    tile_bwd_dx_start<T, VE>(x + base, gstep, ring, ring_stride, iters);
   }
 
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
   const int c_valid = min(g.CW, g.C - c0);
-  const bool shuf = UNI && g.shuf;
-  __syncthreads();  // every thread is done with its ring slots: `red` may now be written
   if (shuf) {
     // gamma-weighted group sums straight from registers: xor-butterflies + one pass over the warps
     float a1 = 0.f, a2 = 0.f;
@@ -446,7 +476,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
       }
     }
     const float t1 = cta_slot_sum_shuf(g, a1, tx, red);
-    const float t2 = cta_slot_sum_shuf(g, a2, tx, red + 512);
+    const float t2 = cta_slot_sum_shuf(g, a2, tx, red + g.wsum_stride);
     if (tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
       const int s = tid >> g.tps_shift;
       spart[2 * s] = t1;
@@ -476,10 +506,13 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   cluster_arrive();  // publishes spart
   // Channel sums of this CTA's rows go to scratch (summed over samples and cluster ranks by the
   // parameter-gradient kernel).  On the shuffle path this work overlaps the wait for the peers.
-  if (shuf) cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
   {
     float2* out = reinterpret_cast<float2*>(sums) + (((size_t)n * k + rank) * g.C + c0);
-    for (int c = tid; c < c_valid; c += blockDim.x) out[c] = make_float2(chan[c], chan[g.CW + c]);
+    if constexpr (VE % 4 == 0) {
+      if (shuf) cta_channel_sums_shuf<VE>(g, s1, s2, tx, red + g.wpart_off, out, c_valid);
+    }
+    if (!shuf)
+      for (int c = tid; c < c_valid; c += blockDim.x) out[c] = make_float2(chan[c], chan[g.CW + c]);
   }
   cluster_wait();
 

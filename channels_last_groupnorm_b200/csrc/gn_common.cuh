@@ -240,6 +240,48 @@ __device__ __forceinline__ void cp_async_wait_dyn8(int pending) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Mixed-precision arithmetic of sm_100: one instruction converts a 16-bit operand and combines it
+// with fp32 operands (PTX add / sub / fma with types .f32.f16 and .f32.bf16), so a 16-bit tensor
+// element enters an fp32 sum without a separate unpack instruction.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void split_halves(uint32_t w, uint16_t& lo, uint16_t& hi) {
+  asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(w));
+}
+// float(a) - c, exact conversion of a, one rounding
+template <typename T>
+__device__ __forceinline__ float mixed_sub(uint16_t a, float c) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  float d;
+  if constexpr (std::is_same<T, __half>::value)
+    asm("sub.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
+  else
+    asm("sub.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
+  return d;
+}
+// float(a) + c
+template <typename T>
+__device__ __forceinline__ float mixed_add(uint16_t a, float c) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  float d;
+  if constexpr (std::is_same<T, __half>::value)
+    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
+  else
+    asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
+  return d;
+}
+// float(a) * float(b) + c, product exact
+template <typename T>
+__device__ __forceinline__ float mixed_fma(uint16_t a, uint16_t b, float c) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  float d;
+  if constexpr (std::is_same<T, __half>::value)
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+  else
+    asm("fma.rn.f32.bf16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+  return d;
+}
+
 // 16 bytes of T viewed as a uint4 <-> fp32 lanes
 template <typename T, int VE>
 __device__ __forceinline__ void unpack16(const uint4& w, float (&f)[VE]) {
@@ -467,48 +509,6 @@ __device__ __forceinline__ __half2 act_grad_h2(__half2 v) {
   }
 }
 
-// ---------------------------------------------------------------------------------------------
-// Mixed-precision arithmetic of sm_100: one instruction converts a 16-bit operand and combines it
-// with fp32 operands (PTX add / sub / fma with types .f32.f16 and .f32.bf16), so a 16-bit tensor
-// element enters an fp32 sum without a separate unpack instruction.
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void split_halves(uint32_t w, uint16_t& lo, uint16_t& hi) {
-  asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(w));
-}
-// float(a) - c, exact conversion of a, one rounding
-template <typename T>
-__device__ __forceinline__ float mixed_sub(uint16_t a, float c) {
-  static_assert(sizeof(T) == 2, "16-bit element types only");
-  float d;
-  if constexpr (std::is_same<T, __half>::value)
-    asm("sub.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
-  else
-    asm("sub.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
-  return d;
-}
-// float(a) + c
-template <typename T>
-__device__ __forceinline__ float mixed_add(uint16_t a, float c) {
-  static_assert(sizeof(T) == 2, "16-bit element types only");
-  float d;
-  if constexpr (std::is_same<T, __half>::value)
-    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
-  else
-    asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(a), "f"(c));
-  return d;
-}
-// float(a) * float(b) + c, product exact
-template <typename T>
-__device__ __forceinline__ float mixed_fma(uint16_t a, uint16_t b, float c) {
-  static_assert(sizeof(T) == 2, "16-bit element types only");
-  float d;
-  if constexpr (std::is_same<T, __half>::value)
-    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
-  else
-    asm("fma.rn.f32.bf16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
-  return d;
-}
-
 // Forward epilogue for one 16-byte vector: out = T(act(yh)) packed.
 template <typename T, int VE, int ACT>
 __device__ __forceinline__ uint4 act_pack16(const float (&yh)[VE]) {
@@ -614,9 +614,9 @@ struct Geom {
   // Shuffle reductions (fused kernels): usable when every vector lies in one group, CV and the
   // threads per group row (D / VE) are powers of two and CV <= 32.  tps_shift = log2(D / VE).
   int shuf, tps_shift;
-  int red_floats;  // size of the reduction scratch `red` (forward kernels), set by the planner
+  int red_floats;  // size of the reduction scratch `red`, set by the planner
+  int wsum_stride, wpart_off;  // fused backward, shuffle reductions: layout of `red` (floats)
   int persist;     // fused kernels: the grid holds the resident clusters only, each looping over items
-  int dbg;         // experiments only: stop the fused forward kernel after stage `dbg` (0 = run normally)
 };
 
 // Groups touched by column block starting at channel c0 (width CW, clipped to C):
@@ -751,6 +751,46 @@ __device__ __forceinline__ void cta_channel_sums(const Geom& g, const float (&s1
     chan[CW + c] = a2;
   }
   __syncthreads();
+}
+
+// The same for the shuffle geometry (Geom::shuf), without the TY x CW staging area: lanes of a warp
+// that hold the same column vector (equal lane mod CV) are combined with xor-butterflies, the warp
+// sums go through `wpart` (nwarps * 2 * CW floats) and thread c < c_valid adds them in warp order
+// and stores (S1, S2) of channel c to out[c].  One __syncthreads inside.
+template <int VE>
+__device__ __forceinline__ void cta_channel_sums_shuf(const Geom& g, const float (&s1)[VE], const float (&s2)[VE],
+                                                      int tx, float* wpart, float2* out, int c_valid) {
+  static_assert(VE % 4 == 0, "vector path only");
+  float v1[VE], v2[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) v1[e] = s1[e], v2[e] = s2[e];
+  for (int b = g.CV; b < 32; b <<= 1) {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      v1[e] += __shfl_xor_sync(0xffffffffu, v1[e], b);
+      v2[e] += __shfl_xor_sync(0xffffffffu, v2[e], b);
+    }
+  }
+  const int CW = g.CW;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  if (lane < g.CV) {
+    float* w1 = wpart + (size_t)(2 * warp) * CW + tx * VE;
+    float* w2 = w1 + CW;
+#pragma unroll
+    for (int e = 0; e < VE; e += 4) {
+      *reinterpret_cast<float4*>(w1 + e) = make_float4(v1[e], v1[e + 1], v1[e + 2], v1[e + 3]);
+      *reinterpret_cast<float4*>(w2 + e) = make_float4(v2[e], v2[e + 1], v2[e + 2], v2[e + 3]);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < c_valid; c += blockDim.x) {
+    float a1 = 0.f, a2 = 0.f;
+    for (int w = 0; w < nwarps; ++w) {
+      a1 += wpart[(size_t)(2 * w) * CW + c];
+      a2 += wpart[(size_t)(2 * w + 1) * CW + c];
+    }
+    out[c] = make_float2(a1, a2);
+  }
 }
 
 }  // namespace gnb200

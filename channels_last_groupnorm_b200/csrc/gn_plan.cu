@@ -67,30 +67,60 @@ size_t fwd_fold_floats(int CW, int TY, int slots, int threads) {
   (void)threads;
   return fwd_red_floats(CW, TY, slots) + (size_t)9 * slots + 8;
 }
-size_t bwd_red_floats(int CW, int TY, int slots) {
+int round_up4(int v) { return (v + 3) & ~3; }
+
+// backward scratch of the CTA reductions.
+// Generic reductions: red = the per-row-lane channel sums (2 * TY * CW floats), then part and chan.
+// Shuffle reductions (fused kernel only): red = [two warp-sum buffers of wsum_stride floats,
+// overlaid later by the gathered group sums of up to 16 cluster peers][per-warp channel sums
+// nwarps * 2 * CW from wpart_off]; part and chan are not used.
+int bwd_wsum_stride(int threads, int CV, int tps_shift) { return round_up4(((threads + 31) / 32) * (CV >> tps_shift)); }
+int bwd_wpart_off(int threads, int CV, int tps_shift, int slots) {
+  const int a = 2 * bwd_wsum_stride(threads, CV, tps_shift), b = 16 * 2 * slots;
+  return round_up4(a > b ? a : b);
+}
+size_t bwd_red_floats(int CW, int CV, int TY, int slots, int threads, bool shuf, int tps_shift) {
+  if (shuf) return (size_t)bwd_wpart_off(threads, CV, tps_shift, slots) + (size_t)((threads + 31) / 32) * 2 * CW;
   size_t r = (size_t)2 * TY * CW;
   if (r < 1024) r = 1024;
   if (r < (size_t)16 * 2 * slots) r = (size_t)16 * 2 * slots;
   return r;
 }
-size_t bwd_fold_floats(int CW, int TY, int slots, int threads) {
-  return bwd_red_floats(CW, TY, slots) + (size_t)2 * (threads > CW ? threads : CW) + (size_t)2 * CW + (size_t)4 * slots + 8;
+size_t bwd_fold_floats(int CW, int CV, int TY, int slots, int threads, bool shuf, int tps_shift) {
+  const size_t lanes = shuf ? 0 : (size_t)2 * (threads > CW ? threads : CW) + (size_t)2 * CW;  // part, chan
+  return bwd_red_floats(CW, CV, TY, slots, threads, shuf, tps_shift) + lanes + (size_t)4 * slots + 8;
 }
 
 bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
-void fill_divisors(Geom* g, int ve, int direction) {
-  g->red_floats = (int)(direction == 0 ? fwd_red_floats(g->CW, g->TY, g->slots) : bwd_red_floats(g->CW, g->TY, g->slots));
+// Shuffle reductions of the fused kernels: every 16-byte vector lies in one group, and CV and the
+// threads per group row (D / ve) are powers of two with CV <= 32.
+bool shuffle_geometry(int D, int ve, int CV, int* tps_shift) {
+  *tps_shift = 0;
+  if (ve < 4 || D % ve != 0) return false;
+  const int tps = D / ve;
+  if (!(is_pow2(CV) && CV <= 32 && is_pow2(tps) && tps <= CV) || getenv("GNB200_NO_SHUF") != nullptr) return false;
+  while ((1 << *tps_shift) < tps) ++*tps_shift;
+  return true;
+}
+
+// `fused`: the plan is for the fused kernels (the multi-kernel path never uses shuffle reductions)
+void fill_divisors(Geom* g, int ve, int direction, int threads, bool fused) {
   g->shuf = 0;
   g->tps_shift = 0;
-  g->dbg = env_int("GNB200_DBG_STOP", 0);
-  if (ve > 0 && g->D % ve == 0) {
-    const int tps = g->D / ve;
-    if (is_pow2(g->CV) && g->CV <= 32 && is_pow2(tps) && tps <= g->CV && getenv("GNB200_NO_SHUF") == nullptr) {
-      g->shuf = 1;
-      while ((1 << g->tps_shift) < tps) ++g->tps_shift;
-    }
+  int tps_shift = 0;
+  if (fused && shuffle_geometry(g->D, ve, g->CV, &tps_shift)) {
+    g->shuf = 1;
+    g->tps_shift = tps_shift;
   }
+  g->wsum_stride = 512;
+  g->wpart_off = 0;
+  if (direction == 1 && g->shuf) {
+    g->wsum_stride = bwd_wsum_stride(threads, g->CV, tps_shift);
+    g->wpart_off = bwd_wpart_off(threads, g->CV, tps_shift, g->slots);
+  }
+  g->red_floats = (int)(direction == 0 ? fwd_red_floats(g->CW, g->TY, g->slots)
+                                       : bwd_red_floats(g->CW, g->CV, g->TY, g->slots, threads, g->shuf != 0, tps_shift));
   g->div_D = make_fast_div(g->D);
   g->div_CV = make_fast_div(g->CV);
   g->div_CW = make_fast_div(g->CW);
@@ -129,12 +159,11 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   if (target_threads > 128 && env_int("GNB200_THREADS", 0) == 0 && rows / TY < 16) return false;
   // forward: the x tile.  backward: the dy * act' tile plus a 4-row cp.async ring for x
   const size_t ring = (sh.direction == 1 && ve > 1) ? (size_t)4 * threads * 16 : 0;
-  const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15);
-  size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots, threads) : bwd_fold_floats(cw, TY, slots, threads)) * 4;
-  if (sh.direction == 1) {  // the ring and the reduction scratch `red` share their bytes
-    const size_t red = bwd_red_floats(cw, TY, slots) * 4;
-    fold = fold - red + (ring > red ? ring : red);
-  }
+  const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15) + ring;
+  int tps_shift = 0;
+  const bool shuf = shuffle_geometry(sh.D, ve, CV, &tps_shift);
+  const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots, threads)
+                                         : bwd_fold_floats(cw, CV, TY, slots, threads, shuf, tps_shift)) * 4;
   if (tile + fold > kSmemMaxOptin - 1024) return false;
 
   Plan p = {};
@@ -148,7 +177,7 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, rows, k, slots, k};
   // forward: launch only the clusters that are resident at once; each loops over its items
   p.geom.persist = (sh.direction == 0 && env_int("GNB200_PERSIST", 1) != 0) ? 1 : 0;
-  fill_divisors(&p.geom, ve, sh.direction);
+  fill_divisors(&p.geom, ve, sh.direction, threads, true);
   if (p.grid > 0x7fffffffLL) return false;
 
   // Heuristic fitted to measurements on B200 (bf16 / fp16, N x 256 x 64 x 64 and similar):
@@ -264,13 +293,13 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
     p.ws_bytes = (size_t)p.grid * slots * 3 * sizeof(float);
     p.launches = 3;
   } else {
-    p.smem_bytes = 2 * ring + bwd_fold_floats(cw, TY, slots, threads) * 4;
+    p.smem_bytes = 2 * ring + bwd_fold_floats(cw, CV, TY, slots, threads, false, 0) * 4;
     p.ws_bytes = ((size_t)sh.N * chunks * sh.C * 2 + (size_t)sh.N * sh.C * 2 + (size_t)sh.N * sh.G * 2) * sizeof(float);
     p.launches = 4;
   }
   p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, CV, TY, ncb, (int)rows, (int)chunks, slots, 1};
   p.geom.persist = 0;
-  fill_divisors(&p.geom, ve, sh.direction);
+  fill_divisors(&p.geom, ve, sh.direction, threads, false);
   *out = p;
   return true;
 }
