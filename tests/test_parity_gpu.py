@@ -176,6 +176,62 @@ def test_large_mean_small_variance_fp32(nt):
         check_against(out, want, torch.float32, scale=100.0)
 
 
+@pytest.mark.parametrize("dt", ["float16", "bfloat16"])
+def test_large_mean_small_variance_16bit(nt, dt):
+    # 16-bit statistics use shifted sums (s = sum(x - K), q = sum((x - K)^2) about the thread's
+    # first row): values quantised around a large mean must not cancel.  The oracle sees the
+    # same quantised inputs.
+    g = torch.Generator().manual_seed(5)
+    base = 60.0 if dt == "float16" else 100.0
+    x = (base + 2.0 * torch.randn(3, 24, 24, 64, generator=g)).to(DT[dt]).permute(0, 3, 1, 2)
+    ga = (torch.rand(64, generator=g) + 0.5).to(DT[dt])
+    be = (0.1 * torch.randn(64, generator=g)).to(DT[dt])
+    dy = torch.randn(3, 24, 24, 64, generator=g).to(DT[dt]).permute(0, 3, 1, 2)
+    want = O.oracle_c(x, ga, be, dy, 8, 1e-5, "silu")
+    for path in ("auto", "twopass"):
+        if path == "twopass":
+            os.environ["GNB200_FORCE_PATH"] = "twopass"
+        try:
+            out = run_cabi(nt, x, ga, be, dy, 8, 1e-5, "silu")
+        finally:
+            os.environ.pop("GNB200_FORCE_PATH", None)
+        check_against(out, want, DT[dt])
+        # the statistics themselves: mean to 1e-3 relative, rstd to 2e-3 relative
+        xf = x.double().reshape(3, 8, 8, -1)
+        mu = xf.mean((2, 3))
+        rs = 1.0 / torch.sqrt(xf.var((2, 3), correction=0) + 1e-5)
+        assert ((out["mean"].cpu().double() - mu).abs() / mu.abs()).max() < 1e-3
+        assert ((out["rstd"].cpu().double() - rs).abs() / rs).max() < 2e-3
+
+
+@pytest.mark.parametrize("case", [
+    # (N, C, spatial, G, dtype, act): more (sample, column block) items than resident clusters, so
+    # every cluster of the fused forward kernel walks through several items and refills its tile
+    (96, 320, (32, 32), 32, "float16", "silu"),      # D = 10: vectors straddle groups
+    (40, 256, (64, 64), 32, "bfloat16", "gelu"),     # items not a multiple of the cluster count
+    (24, 128, (96, 96), 16, "float32", "relu"),      # fp32 (Welford) statistics
+    (150, 64, (48, 48), 64, "float16", "identity"),  # instance-norm-like: D = 1, scalar groups
+], ids=lambda c: "%dx%dx%s-g%d-%s-%s" % (c[0], c[1], "x".join(map(str, c[2])), c[3], c[4], c[5]))
+def test_persistent_clusters_over_many_items(nt, case):
+    N, C, sp, G, dt, act = case
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    shape = (N, *sp, C)
+    # a different offset per sample and channel, so that an item computed with another item's
+    # statistics or rows cannot pass
+    off = torch.randn(N, 1, 1, C, device="cuda", generator=gen) * 2.0
+    x = (torch.randn(shape, device="cuda", generator=gen) + off).to(DT[dt]).permute(0, 3, 1, 2)
+    dy = torch.randn(shape, device="cuda", generator=gen).to(DT[dt]).permute(0, 3, 1, 2)
+    ga = (torch.rand(C, device="cuda", generator=gen) + 0.5).to(DT[dt])
+    be = (torch.randn(C, device="cuda", generator=gen) * 0.1).to(DT[dt])
+    assert " fused " in nt.describe_plan(N, sp[0] * sp[1], C, G, DT[dt], 0)
+    out = run_cabi(nt, x, ga, be, dy, G, 1e-5, act)
+    want = _cuda_fp64_reference(x, ga, be, dy, G, 1e-5, act)
+    check_against(out, want, DT[dt])
+    again = run_cabi(nt, x, ga, be, dy, G, 1e-5, act)
+    for k in ("y", "dx", "dparam", "mean", "rstd"):
+        assert torch.equal(out[k], again[k]), k
+
+
 def test_misaligned_pointers_use_the_scalar_path(nt):
     N, C, sp, G = 2, 24, (5, 7), 3
     x, ga, be, dy = O.make_inputs(N, C, sp, torch.float16, seed=4)
