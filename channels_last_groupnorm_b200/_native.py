@@ -79,6 +79,18 @@ def describe_plan(N, R, C, G, dtype, direction):
     return buf.value.decode()
 
 
+lib.gnb200_wait_timeouts.restype = ctypes.c_longlong
+lib.gnb200_wait_timeouts.argtypes = []
+
+
+def wait_timeouts():
+    """Exchange waits of the fused kernels that gave up on the current device (0 in a healthy run)."""
+    v = lib.gnb200_wait_timeouts()
+    if v < 0:
+        raise Gnb200Error(lib.gnb200_last_error().decode())
+    return int(v)
+
+
 def launch_count(N, R, C, G, dtype, direction):
     return lib.gnb200_launch_count(N, R, C, G, DTYPE_CODES[dtype], direction)
 

@@ -411,7 +411,7 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
 // ------------------------------------------------------------------------------------------------
 // fused kernel.  grid.x = N * ncb * k, cluster (k,1,1).
 // dynamic smem: [dyh tile][x ring kXRing*threads*16 B][red][generic reductions only: part 2*max(threads,CW), chan 2*CW]
-//               [group partials 2*slots][coef 2*slots]
+//               [group partials 2*slots][coef 2*slots][inbox 4*k*slots][mbarrier]
 // scratch out : sums[((n * k + rank) * C + c) * 2 + {0,1}] = S1, S2 over this CTA's rows
 // ------------------------------------------------------------------------------------------------
 // MAXT: CTA size class.  128-thread launches are compiled for five CTAs per SM (<= 96 registers).
@@ -438,8 +438,13 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   const bool shuf = UNI && g.shuf;
   float* part = red + g.red_floats;                      // generic reductions only
   float* chan = part + 2 * max((int)blockDim.x, g.CW);  // generic reductions only
-  float* spart = shuf ? part : chan + 2 * g.CW;  // [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 over this CTA's rows
-  float* coef = spart + 2 * g.slots;  // A[s], B[slots + s]
+  float* spart = shuf ? part : chan + 2 * g.CW;  // generic reductions: [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 of this CTA
+  float* coef = spart + 2 * g.slots;             // A[s], B[slots + s]
+  // inbox of the exchange: entry (q, s) = the group sums (gamma S1, gamma S2, -, -) of rank q's
+  // rows, 16-byte aligned, followed by its mbarrier
+  float* inbox = coef + 2 * g.slots;
+  inbox += (4 - ((reinterpret_cast<uintptr_t>(inbox) >> 2) & 3)) & 3;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(inbox + 4 * k * g.slots);
 
   const int tid = threadIdx.x;
   const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
@@ -454,14 +459,25 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   float s1[VE], s2[VE];
 #pragma unroll
   for (int e = 0; e < VE; ++e) s1[e] = 0.f, s2[e] = 0.f;
+  BwdPipe<T> pipe = {x + base, dy + base, sd, 0};
+  if (streaming) pipe = tile_fill_start<T, VE>(x + base, dy + base, gstep, ring, ring_stride, sd, sstep, iters);
+  // The inbox barrier: one arrival (thread 0, which also announces the bytes) per use, one use
+  // per launch.  Every CTA of the cluster must have initialised its barrier before a peer pushes
+  // to it: the cluster barrier that guarantees this is entered here and left after phase 1.
+  if (tid == 0) {
+    mbar_init(mbar, 1);
+    fence_mbar_init_cluster();
+    mbar_arrive_expect_tx(mbar, k * g.slots * 16);
+  }
+  cluster_arrive_relaxed();
   if (streaming) {
-    const BwdPipe<T> pipe = tile_fill_start<T, VE>(x + base, dy + base, gstep, ring, ring_stride, sd, sstep, iters);
     lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
     tile_fill_bwd_sums<T, VE, ACT>(pipe, gstep, ring, ring_stride, sd, sstep, iters, L, s1, s2);
     // the first x rows of phase 2 (L2 hits) travel while the cluster exchanges its sums
     tile_bwd_dx_start<T, VE>(x + base, gstep, ring, ring_stride, iters);
   }
 
+  cluster_wait();  // the peers' inbox barriers exist (every CTA arrived long ago)
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
   const int c_valid = min(g.CW, g.C - c0);
@@ -479,8 +495,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
     const float t2 = cta_slot_sum_shuf(g, a2, tx, red + g.wsum_stride);
     if (tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
       const int s = tid >> g.tps_shift;
-      spart[2 * s] = t1;
-      spart[2 * s + 1] = t2;
+      for (unsigned q = 0; q < k; ++q) st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, q, t1, t2, 0.f, 0.f);
     }
   } else {
     cta_channel_sums<VE>(g, s1, s2, tx, ty, c0, red, part, chan);
@@ -503,7 +518,14 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
       }
     }
   }
-  cluster_arrive();  // publishes spart
+  if (!shuf) {
+    __syncthreads();
+    for (int s = tid; s < g.slots; s += blockDim.x) {
+      const bool live = s < n_slots;
+      const float a1 = live ? spart[2 * s] : 0.f, a2 = live ? spart[2 * s + 1] : 0.f;
+      for (unsigned q = 0; q < k; ++q) st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, q, a1, a2, 0.f, 0.f);
+    }
+  }
   // Channel sums of this CTA's rows go to scratch (summed over samples and cluster ranks by the
   // parameter-gradient kernel).  On the shuffle path this work overlaps the wait for the peers.
   {
@@ -514,23 +536,19 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
     if (!shuf)
       for (int c = tid; c < c_valid; c += blockDim.x) out[c] = make_float2(chan[c], chan[g.CW + c]);
   }
-  cluster_wait();
-
+  // every CTA of the cluster pushed its group sums into every inbox: no cluster barrier, no fence
+  mbar_wait_bounded(mbar, 0, g.wait_timeouts);
   const float inv_m = 1.0f / ((float)g.D * (float)g.R);
-  float* stage = red;  // k * 2 * slots floats: the peers' group sums, gathered in parallel
-  cluster_gather(spart, 2 * g.slots, k, stage);
   for (int s = tid; s < n_slots; s += blockDim.x) {
     float a1 = 0.f, a2 = 0.f;
     for (unsigned q = 0; q < k; ++q) {
-      a1 += stage[q * 2 * g.slots + 2 * s];
-      a2 += stage[q * 2 * g.slots + 2 * s + 1];
+      const float4 v = *reinterpret_cast<const float4*>(inbox + 4 * (q * g.slots + s));
+      a1 += v.x;
+      a2 += v.y;
     }
     coef[s] = a1 * inv_m;
     coef[g.slots + s] = a2 * inv_m;
   }
-  // This CTA no longer reads its peers' shared memory.  The arrival publishes nothing, so it does
-  // not have to wait for the channel sums stored to global memory above.
-  cluster_arrive_relaxed();
   __syncthreads();
 
   if (streaming) {
@@ -550,7 +568,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
     }
     tile_bwd_dx<T, VE>(x + base, ring, ring_stride, sd, sstep, dx + base, gstep, iters, L, A, B);
   }
-  cluster_wait();
+  // No exit barrier: nothing reaches into this CTA's shared memory once its wait has completed.
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -741,9 +759,11 @@ static cudaError_t launch_param(const BwdCall& c, const float* sums, int rows, c
 
 template <typename T, int VE, int ACT, bool UNI>
 static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t stream) {
-  const Geom& g = p.geom;
+  Geom g = p.geom;
   if (p.fused) {
     float* sums = reinterpret_cast<float*>(c.workspace);
+    cudaError_t werr = wait_timeout_counter(&g.wait_timeouts);
+    if (werr != cudaSuccess) return werr;
     auto kern = p.threads <= 128 ? gn_bwd_fused_kernel<T, VE, ACT, UNI, 128> : gn_bwd_fused_kernel<T, VE, ACT, UNI, kMaxThreads>;
     cudaError_t err = ensure_kernel_attributes((const void*)kern, p.smem_bytes, g.k > 8);
     if (err != cudaSuccess) return err;

@@ -3,6 +3,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "../../include/gnb200.h"
 #include "gn_kernels.h"
 
@@ -21,6 +23,27 @@ int fail(int code, const char* fmt, ...) {
 }  // namespace
 
 namespace gnb200 {
+__device__ unsigned int g_wait_timeouts = 0;
+
+cudaError_t wait_timeout_counter(unsigned int** counter) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static unsigned int* addr[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    err = cudaGetSymbolAddress(&p, g_wait_timeouts);
+    if (err != cudaSuccess) return err;
+    addr[dev] = static_cast<unsigned int*>(p);
+  }
+  *counter = addr[dev];
+  return cudaSuccess;
+}
+
 // Same thread-local text as fail(), for entry points that live in other translation units.
 int report_error(int code, const char* fmt, ...) {
   va_list ap;
@@ -137,6 +160,13 @@ int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, 
     buf[buf_len - 1] = '\0';
   }
   return need;
+}
+
+long long gnb200_wait_timeouts(void) {
+  unsigned int v = 0;
+  const cudaError_t err = cudaMemcpyFromSymbol(&v, gnb200::g_wait_timeouts, sizeof(v));
+  if (err != cudaSuccess) return fail(GNB200_ERR_CUDA, "gnb200_wait_timeouts: CUDA error: %s", cudaGetErrorString(err));
+  return (long long)v;
 }
 
 int gnb200_launch_count(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction) {

@@ -568,8 +568,8 @@ __device__ __forceinline__ unsigned cluster_nctarank() {
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
-// Arrival that publishes nothing: it only tells the peers that this CTA is done reading their
-// shared memory.  Unlike the release form it does not wait for the CTA's outstanding global stores.
+// Arrival without memory ordering of its own (pairs with a preceding fence where one is needed);
+// unlike the release form it does not wait for the CTA's outstanding stores.
 __device__ __forceinline__ void cluster_arrive_relaxed() {
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 }
@@ -580,14 +580,59 @@ __device__ __forceinline__ void cluster_sync_all() {
   cluster_arrive();
   cluster_wait();
 }
-// Read one float from the shared memory of CTA `rank` of this cluster (DSMEM).
-__device__ __forceinline__ float dsmem_ld_f32(const float* local_smem_ptr, unsigned rank) {
-  const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(local_smem_ptr));
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
+// ---------------------------------------------------------------------------------------------
+// Exchange between the CTAs of a cluster without a cluster barrier: every CTA pushes its values
+// into its peers' shared memory with st.async, which also counts the bytes on an mbarrier of the
+// receiving CTA; the receiver waits for the byte count.  No fence is involved, so the exchange
+// does not wait for the CTA's outstanding global stores as a release barrier would.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init_cluster() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// one arrival of this thread plus the announcement that `bytes` will be delivered by st.async
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the phase with the given parity, at most about a second; a wait that gives up is
+// counted in *timeouts (read by gnb200_wait_timeouts) and the caller carries on, with values that
+// are then meaningless.
+__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned int* timeouts) {
+  if (mbar_try_wait(bar, parity)) return;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > 2000000000LL) {
+      atomicAdd(timeouts, 1u);
+      return;
+    }
+  }
+}
+// 16 bytes into the shared memory of CTA `rank` at the offset of `local_dst`, counted on that
+// CTA's mbarrier at the offset of `local_bar`
+__device__ __forceinline__ void st_async_f32x4(float* local_dst, uint64_t* local_bar, unsigned rank, float a, float b,
+                                               float c, float d) {
+  uint32_t rdst, rbar;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rdst) : "r"(smem_addr(local_dst)), "r"(rank));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(smem_addr(local_bar)), "r"(rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(rdst),
+               "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(__float_as_uint(c)), "r"(__float_as_uint(d)),
+               "r"(rbar)
+               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -615,8 +660,9 @@ struct Geom {
   // threads per group row (D / VE) are powers of two and CV <= 32.  tps_shift = log2(D / VE).
   int shuf, tps_shift;
   int red_floats;  // size of the reduction scratch `red`, set by the planner
-  int wsum_stride, wpart_off;  // fused backward, shuffle reductions: layout of `red` (floats)
-  int persist;     // fused kernels: the grid holds the resident clusters only, each looping over items
+  int wsum_stride, wpart_off;  // shuffle reductions: second warp-sum buffer and (backward) per-warp channel sums in `red`, in floats
+  unsigned int* wait_timeouts;  // device counter of exchange waits that gave up (set by the launcher)
+  int persist;     // fused forward: the grid holds the resident clusters only, each looping over items
 };
 
 // Groups touched by column block starting at channel c0 (width CW, clipped to C):
@@ -687,18 +733,6 @@ __device__ __forceinline__ float cta_slot_sum_shuf(const Geom& g, float v, int t
   float t = 0.f;
   for (int w = 0; w < nwarps; ++w) t += wsum[w * n_slots + s];
   return t;
-}
-
-// Copies `count` floats per CTA of the cluster from the peers' shared memory (same offset
-// `remote` in every CTA) into local shared memory: stage[q * count + i] = peer q's remote[i].
-// The loads of all (peer, element) pairs are spread over the threads so that they are in flight
-// together.  Call after the cluster barrier that publishes `remote`; ends with __syncthreads().
-__device__ __forceinline__ void cluster_gather(const float* remote, int count, unsigned k, float* stage) {
-  for (int i = threadIdx.x; i < (int)k * count; i += blockDim.x) {
-    const unsigned q = (unsigned)i / (unsigned)count;
-    stage[i] = dsmem_ld_f32(remote + (i - (int)q * count), q);
-  }
-  __syncthreads();
 }
 
 // Per-channel sums over the row lanes of two values (backward): chan[c] = sum_ty s1, chan[CW + c]

@@ -439,8 +439,12 @@ __device__ __forceinline__ void cta_slot_moments(const Geom& g, const float (&me
 // at once (or one per item if there are fewer items); cluster c works on items c, c + n_clusters,
 // ...  While a CTA writes the y rows of one item it refills the tile, row by row, with the x rows
 // of its next item, so DRAM reads and writes overlap and the exchange of statistics of one item
-// is the only time a CTA does not move data.
-// dynamic smem: [tile rows_per_cta * CV packs][red][tmp slots][slot 2 x 3*slots][stat 2*slots]
+// is the only time a CTA does not move data.  The exchange itself needs no cluster barrier: every
+// CTA pushes its (mean, M2, count) into the inboxes of all CTAs of the cluster (st.async) and
+// waits on its own mbarrier for the k contributions; inboxes alternate between two copies, and a
+// copy is pushed to again only by peers that have seen this CTA's contribution to the next item.
+// dynamic smem: [tile rows_per_cta * CV packs][red][tmp slots][slot 3*slots][stat 2*slots]
+//               [2 inboxes of k*slots entries of 4 floats][2 mbarriers]
 // ------------------------------------------------------------------------------------------------
 // MAXT: CTA size class.  128-thread launches are compiled for six CTAs per SM (<= 80 registers).
 template <typename T, int VE, int ACT, bool UNI, int MAXT>
@@ -460,8 +464,13 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
   const size_t tile_bytes = ((size_t)g.rows_per_cta * g.CV * sizeof(P) + 15) & ~(size_t)15;
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes);
   float* tmp = red + g.red_floats;
-  float* slots2 = tmp + g.slots;       // two copies of: local mean | local M2 | local count
-  float* stat = slots2 + 6 * g.slots;  // mean[slots], rstd[slots]
+  float* slot = tmp + g.slots;       // generic reductions: local mean | local M2 | local count
+  float* stat = slot + 3 * g.slots;  // mean[slots], rstd[slots]
+  // push exchange: two inboxes of k * slots entries (mean, M2, count, -), 16-byte aligned, and
+  // their mbarriers
+  float* inbox2 = stat + 2 * g.slots;
+  inbox2 += (4 - ((reinterpret_cast<uintptr_t>(inbox2) >> 2) & 3)) & 3;
+  uint64_t* mbar2 = reinterpret_cast<uint64_t*>(inbox2 + 2 * 4 * k * g.slots);
 
   const int tid = threadIdx.x;
   const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
@@ -473,8 +482,17 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
   const size_t gstep = (size_t)g.TY * g.C;
   const size_t row_off = ((size_t)r0 + ty) * g.C + (size_t)tx * VE;
 
+  // Inbox barriers: one arrival (thread 0, which also announces the bytes) per use.  Every CTA of
+  // the cluster must have initialised them before a peer pushes to them: the cluster barrier that
+  // guarantees this is entered here and left just before this CTA's first push.
+  if (threadIdx.x == 0) {
+    mbar_init(mbar2, 1);
+    mbar_init(mbar2 + 1, 1);
+    fence_mbar_init_cluster();
+  }
+  cluster_arrive_relaxed();
   int item = (int)(blockIdx.x / k);
-  unsigned parity = 0;
+  unsigned parity = 0, uses = 0;
   if (item < n_items) {
     const int n = g.div_ncb.div(item), cb = item - n * g.ncb;
     tile_issue<T, VE>(x + (size_t)n * g.R * g.C + cb * g.CW + row_off, gstep, stile, sstep,
@@ -485,7 +503,6 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
     const int n = g.div_ncb.div(item), cb = item - n * g.ncb;
     const int c0 = cb * g.CW;
     const size_t base = (size_t)n * g.R * g.C + c0 + row_off;
-    float* slot = slots2 + parity * 3 * g.slots;
     uint4 ga_raw = make_uint4(0, 0, 0, 0), be_raw = make_uint4(0, 0, 0, 0);
     if constexpr (kVec) {
       if (streaming) {
@@ -493,10 +510,14 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
         be_raw = *reinterpret_cast<const uint4*>(beta + c0 + tx * VE);
       }
     }
+    float* inbox = inbox2 + parity * 4 * k * g.slots;
+    uint64_t* mbar = mbar2 + parity;
+    if (tid == 0) mbar_arrive_expect_tx(mbar, k * g.slots * 16);
     float mean[VE], m2[VE], cnt = 0.f;
 #pragma unroll
     for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
     tile_moments<T, VE, UNI>(stile, sstep, iters, mean, m2, cnt, first, x + base + (size_t)kFirstRows * gstep, gstep);
+    if (first) cluster_wait();  // the peers' inbox barriers exist (every CTA arrived long ago)
     first = false;
     int g_lo, n_slots;
     cb_groups(g, c0, g_lo, n_slots);
@@ -515,50 +536,50 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
         dev = fmaf(d, d, dev);
         acc += m2[e];
       }
-      const float m2loc = cta_slot_sum_shuf(g, fmaf(cnt, dev, acc), tx, red + 512);
+      const float m2loc = cta_slot_sum_shuf(g, fmaf(cnt, dev, acc), tx, red + g.wsum_stride);
       if (tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
         const int s = tid >> g.tps_shift;
-        slot[s] = lm;
-        slot[g.slots + s] = m2loc;
-        slot[2 * g.slots + s] = n_loc;
+        for (unsigned q = 0; q < k; ++q) st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, q, lm, m2loc, n_loc, 0.f);
       }
     } else {
       cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
-    }
-
-    // combine the k CTA-local moments (rank order -> every CTA of the cluster gets bit-identical
-    // statistics):  mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2.
-    // One cluster barrier per item: `slot` alternates between two copies, and a CTA rewrites a
-    // copy only after the next item's barrier, which no peer passes before its reads of this one.
-    cluster_sync_all();
-    float* stage = red;  // k * 3 * slots floats: the peers' slot arrays, gathered in parallel
-    cluster_gather(slot, 3 * g.slots, k, stage);
-    for (int s = tid; s < n_slots; s += blockDim.x) {
-      float wsum = 0.f, ntot = 0.f;
-      for (unsigned q = 0; q < k; ++q) {
-        const float* pq = stage + q * 3 * g.slots;
-        wsum = fmaf(pq[2 * g.slots + s], pq[s], wsum);
-        ntot += pq[2 * g.slots + s];
-      }
-      const float mu = wsum / ntot;
-      float m2tot = 0.f;
-      for (unsigned q = 0; q < k; ++q) {
-        const float* pq = stage + q * 3 * g.slots;
-        const float d = pq[s] - mu;
-        m2tot += fmaf(pq[2 * g.slots + s] * d, d, pq[g.slots + s]);
-      }
-      const float rs = rsqrtf(fmaxf(m2tot / ntot, 0.f) + eps);
-      stat[s] = mu;
-      stat[g.slots + s] = rs;
-      if (rank == 0) {
-        mean_out[(size_t)n * g.G + g_lo + s] = mu;
-        rstd_out[(size_t)n * g.G + g_lo + s] = rs;
+      __syncthreads();
+      for (int s = tid; s < g.slots; s += blockDim.x) {
+        const bool live = s < n_slots;
+        const float a = live ? slot[s] : 0.f, b = live ? slot[g.slots + s] : 0.f, c = live ? slot[2 * g.slots + s] : 0.f;
+        for (unsigned q = 0; q < k; ++q) st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, q, a, b, c, 0.f);
       }
     }
-    __syncthreads();
-    // Last item: this CTA will not read its peers' shared memory again.  Saying so now, before the
-    // y rows are written, keeps the exit barrier below from waiting for those stores.
-    if (item + n_clusters >= n_items) cluster_arrive_relaxed();
+    {
+      // Every CTA of the cluster pushed (mean, M2, count) of each slot into every inbox.  Combine them
+      // in rank order (every CTA gets bit-identical statistics):
+      //   mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2
+      mbar_wait_bounded(mbar, (uses >> 1) & 1u, g.wait_timeouts);
+      ++uses;
+      for (int s = tid; s < n_slots; s += blockDim.x) {
+        float wsum = 0.f, ntot = 0.f;
+        for (unsigned q = 0; q < k; ++q) {
+          const float4 v = *reinterpret_cast<const float4*>(inbox + 4 * (q * g.slots + s));
+          wsum = fmaf(v.z, v.x, wsum);
+          ntot += v.z;
+        }
+        const float mu = wsum / ntot;
+        float m2tot = 0.f;
+        for (unsigned q = 0; q < k; ++q) {
+          const float4 v = *reinterpret_cast<const float4*>(inbox + 4 * (q * g.slots + s));
+          const float d = v.x - mu;
+          m2tot += fmaf(v.z * d, d, v.y);
+        }
+        const float rs = rsqrtf(fmaxf(m2tot / ntot, 0.f) + eps);
+        stat[s] = mu;
+        stat[g.slots + s] = rs;
+        if (rank == 0) {
+          mean_out[(size_t)n * g.G + g_lo + s] = mu;
+          rstd_out[(size_t)n * g.G + g_lo + s] = rs;
+        }
+      }
+      __syncthreads();
+    }
 
     if (streaming) {
       float a[VE], b[VE];
@@ -576,7 +597,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
     // No barrier here: the next item's reductions write red / tmp / slot before their first
     // barrier, none of which is read by the output pass, and `stat` is rewritten only after it.
   }
-  cluster_wait();  // do not exit (and release shared memory) while a peer may still read `slots2`
+  // No exit barrier: nothing reaches into this CTA's shared memory after the wait of its last item.
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -714,8 +735,11 @@ static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t st
     if (clusters > items) clusters = (int)items;
     cfg.gridDim.x = (unsigned)clusters * (unsigned)p.geom.k;
   }
+  Geom g = p.geom;
+  err = wait_timeout_counter(&g.wait_timeouts);
+  if (err != cudaSuccess) return err;
   return cudaLaunchKernelEx(&cfg, kern, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, (T*)c.y, c.mean, c.rstd,
-                            c.eps, p.geom);
+                            c.eps, g);
 }
 
 template <typename T, int VE, int ACT, bool UNI>

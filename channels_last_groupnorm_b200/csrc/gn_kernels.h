@@ -63,6 +63,9 @@ cudaError_t ensure_kernel_attributes(const void* func, size_t smem_bytes, bool n
 // can be resident on the current device at once (>= 1), cached per device, kernel and shape.
 cudaError_t resident_clusters(const void* func, const cudaLaunchConfig_t* cfg, int* clusters);
 
+// Device address of the counter of exchange waits that gave up, on the current device.
+cudaError_t wait_timeout_counter(unsigned int** counter);
+
 cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream);
 cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream);
 

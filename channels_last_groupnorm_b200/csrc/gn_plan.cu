@@ -57,27 +57,33 @@ FastDiv make_fast_div(int d) {
 // shared-memory floats of the CTA reductions (layouts in gn_fwd.cu / gn_bwd.cu)
 // forward `red` scratch: the per-row-lane values of the generic reduction, or two warp-sum buffers
 // of the shuffle reduction, or the gathered slot arrays of up to 16 cluster peers
-size_t fwd_red_floats(int CW, int TY, int slots) {
+int round_up4(int v) { return (v + 3) & ~3; }
+// warp-sum buffer of the shuffle reductions: one float per (warp, group slot)
+int wsum_stride_floats(int threads, int CV, int tps_shift) { return round_up4(((threads + 31) / 32) * (CV >> tps_shift)); }
+
+size_t fwd_red_floats(int CW, int CV, int TY, int slots, int threads, bool shuf, int tps_shift) {
+  if (shuf) {  // two warp-sum buffers, overlaid later by the gathered slot arrays of the peers
+    const int a = 2 * wsum_stride_floats(threads, CV, tps_shift), b = 16 * 3 * slots;
+    return (size_t)round_up4(a > b ? a : b);
+  }
   size_t r = (size_t)TY * CW;
   if (r < 1024) r = 1024;
   if (r < (size_t)16 * 3 * slots) r = (size_t)16 * 3 * slots;
   return r;
 }
-size_t fwd_fold_floats(int CW, int TY, int slots, int threads) {
-  (void)threads;
-  return fwd_red_floats(CW, TY, slots) + (size_t)9 * slots + 8;
+// red, tmp, two slot arrays, stat, and for the push exchange two inboxes of k * slots entries of
+// four floats plus alignment slack and two mbarriers
+size_t fwd_fold_floats(int CW, int CV, int TY, int slots, int threads, bool shuf, int tps_shift, int k) {
+  return fwd_red_floats(CW, CV, TY, slots, threads, shuf, tps_shift) + (size_t)9 * slots + 8 + (size_t)2 * 4 * k * slots + 8;
 }
-int round_up4(int v) { return (v + 3) & ~3; }
-
 // backward scratch of the CTA reductions.
 // Generic reductions: red = the per-row-lane channel sums (2 * TY * CW floats), then part and chan.
 // Shuffle reductions (fused kernel only): red = [two warp-sum buffers of wsum_stride floats,
 // overlaid later by the gathered group sums of up to 16 cluster peers][per-warp channel sums
 // nwarps * 2 * CW from wpart_off]; part and chan are not used.
-int bwd_wsum_stride(int threads, int CV, int tps_shift) { return round_up4(((threads + 31) / 32) * (CV >> tps_shift)); }
 int bwd_wpart_off(int threads, int CV, int tps_shift, int slots) {
-  const int a = 2 * bwd_wsum_stride(threads, CV, tps_shift), b = 16 * 2 * slots;
-  return round_up4(a > b ? a : b);
+  (void)slots;
+  return round_up4(2 * wsum_stride_floats(threads, CV, tps_shift));
 }
 size_t bwd_red_floats(int CW, int CV, int TY, int slots, int threads, bool shuf, int tps_shift) {
   if (shuf) return (size_t)bwd_wpart_off(threads, CV, tps_shift, slots) + (size_t)((threads + 31) / 32) * 2 * CW;
@@ -86,9 +92,10 @@ size_t bwd_red_floats(int CW, int CV, int TY, int slots, int threads, bool shuf,
   if (r < (size_t)16 * 2 * slots) r = (size_t)16 * 2 * slots;
   return r;
 }
-size_t bwd_fold_floats(int CW, int CV, int TY, int slots, int threads, bool shuf, int tps_shift) {
+// k: cluster size (inbox of the exchange: k * slots entries of four floats, alignment slack, mbarrier)
+size_t bwd_fold_floats(int CW, int CV, int TY, int slots, int threads, bool shuf, int tps_shift, int k) {
   const size_t lanes = shuf ? 0 : (size_t)2 * (threads > CW ? threads : CW) + (size_t)2 * CW;  // part, chan
-  return bwd_red_floats(CW, CV, TY, slots, threads, shuf, tps_shift) + lanes + (size_t)4 * slots + 8;
+  return bwd_red_floats(CW, CV, TY, slots, threads, shuf, tps_shift) + lanes + (size_t)4 * slots + 8 + (size_t)4 * k * slots + 8;
 }
 
 bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
@@ -113,13 +120,9 @@ void fill_divisors(Geom* g, int ve, int direction, int threads, bool fused) {
     g->shuf = 1;
     g->tps_shift = tps_shift;
   }
-  g->wsum_stride = 512;
-  g->wpart_off = 0;
-  if (direction == 1 && g->shuf) {
-    g->wsum_stride = bwd_wsum_stride(threads, g->CV, tps_shift);
-    g->wpart_off = bwd_wpart_off(threads, g->CV, tps_shift, g->slots);
-  }
-  g->red_floats = (int)(direction == 0 ? fwd_red_floats(g->CW, g->TY, g->slots)
+  g->wsum_stride = g->shuf ? wsum_stride_floats(threads, g->CV, tps_shift) : 0;
+  g->wpart_off = (direction == 1 && g->shuf) ? bwd_wpart_off(threads, g->CV, tps_shift, g->slots) : 0;
+  g->red_floats = (int)(direction == 0 ? fwd_red_floats(g->CW, g->CV, g->TY, g->slots, threads, g->shuf != 0, tps_shift)
                                        : bwd_red_floats(g->CW, g->CV, g->TY, g->slots, threads, g->shuf != 0, tps_shift));
   g->div_D = make_fast_div(g->D);
   g->div_CV = make_fast_div(g->CV);
@@ -162,8 +165,8 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
   const size_t tile = (((size_t)rows * CV * ve * s + 15) & ~(size_t)15) + ring;
   int tps_shift = 0;
   const bool shuf = shuffle_geometry(sh.D, ve, CV, &tps_shift);
-  const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, TY, slots, threads)
-                                         : bwd_fold_floats(cw, CV, TY, slots, threads, shuf, tps_shift)) * 4;
+  const size_t fold = (sh.direction == 0 ? fwd_fold_floats(cw, CV, TY, slots, threads, shuf, tps_shift, k)
+                                         : bwd_fold_floats(cw, CV, TY, slots, threads, shuf, tps_shift, k)) * 4;
   if (tile + fold > kSmemMaxOptin - 1024) return false;
 
   Plan p = {};
@@ -289,11 +292,11 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
   // shared-memory rings of the streaming kernels: 8 rows x 16 bytes per thread (x; x and dy)
   const size_t ring = ve > 1 ? (size_t)8 * threads * 16 : 0;
   if (sh.direction == 0) {
-    p.smem_bytes = ring + fwd_fold_floats(cw, TY, slots, threads) * 4;
+    p.smem_bytes = ring + fwd_fold_floats(cw, CV, TY, slots, threads, false, 0, 1) * 4;
     p.ws_bytes = (size_t)p.grid * slots * 3 * sizeof(float);
     p.launches = 3;
   } else {
-    p.smem_bytes = 2 * ring + bwd_fold_floats(cw, CV, TY, slots, threads, false, 0) * 4;
+    p.smem_bytes = 2 * ring + bwd_fold_floats(cw, CV, TY, slots, threads, false, 0, 1) * 4;
     p.ws_bytes = ((size_t)sh.N * chunks * sh.C * 2 + (size_t)sh.N * sh.C * 2 + (size_t)sh.N * sh.G * 2) * sizeof(float);
     p.launches = 4;
   }

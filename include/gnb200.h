@@ -127,6 +127,15 @@ int gnb200_bwd_static_scratch(const void* dy, const void* x, const void* gamma, 
 int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction,
                          char* buf, int buf_len);
 
+/*
+ * Diagnostics.  The fused kernels exchange statistics between the CTAs of a cluster through
+ * shared-memory mailboxes; a CTA waits for its peers at most about a second and then carries on
+ * with meaningless values instead of hanging the GPU.  This returns how many such waits have given
+ * up on the current device since the library was loaded (0 in any healthy run; negative = error).
+ * Synchronises with the device.  No counterpart in the reference.
+ */
+long long gnb200_wait_timeouts(void);
+
 /* Number of kernel launches gnb200_fwd / gnb200_bwd enqueue for this problem. */
 int gnb200_launch_count(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction);
 

@@ -232,6 +232,14 @@ def test_persistent_clusters_over_many_items(nt, case):
         assert torch.equal(out[k], again[k]), k
 
 
+def test_no_exchange_wait_gave_up(nt):
+    # the bounded waits of the cluster exchange count the times they gave up; any count means that
+    # a kernel carried on with meaningless statistics
+    x, ga, be, dy, G, eps, act, dtype = _case_inputs(CFG4[0])
+    run_cabi(nt, x, ga, be, dy, G, eps, act)
+    assert nt.wait_timeouts() == 0
+
+
 def test_misaligned_pointers_use_the_scalar_path(nt):
     N, C, sp, G = 2, 24, (5, 7), 3
     x, ga, be, dy = O.make_inputs(N, C, sp, torch.float16, seed=4)
