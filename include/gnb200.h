@@ -26,6 +26,10 @@
  * `stream` and nothing synchronises with the host.  No entry point below allocates device
  * memory: scratch comes from the caller (`workspace`) or, for gnb200_bwd_static_scratch, from a
  * fixed array inside the library.
+ *
+ * The first call of a kernel variant on a device raises its shared-memory limit, asks the
+ * driver how many thread-block clusters fit the device and resolves the address of a diagnostic
+ * counter (all cached afterwards): make one call per problem before a stream capture.
  */
 #ifndef GNB200_H_
 #define GNB200_H_
