@@ -23,39 +23,8 @@ enum : int { kActIdentity = 0, kActRelu = 1, kActSilu = 2, kActGelu = 3, kActGel
 constexpr int kMaxThreads = 512;
 
 // ---------------------------------------------------------------------------------------------
-// Welford / Chan running moments (what Welford.h:24-76 of the reference provides via a struct of
-// four fields; here: mean, sum of squared deviations, count as float)
+// Fixed-order sums
 // ---------------------------------------------------------------------------------------------
-struct Moments {
-  float mean, m2, n;
-};
-
-__device__ __forceinline__ Moments moments_merge(const Moments a, const Moments b) {
-  const float n = a.n + b.n;
-  const float w = (n > 0.f) ? __fdiv_rn(b.n, n) : 0.f;
-  const float d = b.mean - a.mean;
-  Moments r;
-  r.mean = fmaf(d, w, a.mean);
-  r.m2 = a.m2 + b.m2 + d * d * a.n * w;
-  r.n = n;
-  return r;
-}
-
-__device__ __forceinline__ Moments moments_shfl_down(const Moments v, int delta) {
-  Moments o;
-  o.mean = __shfl_down_sync(0xffffffffu, v.mean, delta);
-  o.m2 = __shfl_down_sync(0xffffffffu, v.m2, delta);
-  o.n = __shfl_down_sync(0xffffffffu, v.n, delta);
-  return o;
-}
-
-// Fixed-order warp tree; the full result is valid in lane 0.
-__device__ __forceinline__ Moments moments_warp_reduce(Moments v) {
-#pragma unroll
-  for (int delta = 16; delta >= 1; delta >>= 1) v = moments_merge(v, moments_shfl_down(v, delta));
-  return v;
-}
-
 // Sum over a whole CTA in a fixed order (warp trees, then the warp results in warp order).
 // `scratch` holds one float per warp; the total is returned to every thread.
 __device__ __forceinline__ float warp_sum(float v);
@@ -565,9 +534,6 @@ __device__ __forceinline__ unsigned cluster_nctarank() {
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ void cluster_arrive() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
 // Arrival without memory ordering of its own (pairs with a preceding fence where one is needed);
 // unlike the release form it does not wait for the CTA's outstanding stores.
 __device__ __forceinline__ void cluster_arrive_relaxed() {
@@ -575,10 +541,6 @@ __device__ __forceinline__ void cluster_arrive_relaxed() {
 }
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  cluster_arrive();
-  cluster_wait();
 }
 // ---------------------------------------------------------------------------------------------
 // Exchange between the CTAs of a cluster without a cluster barrier: every CTA pushes its values

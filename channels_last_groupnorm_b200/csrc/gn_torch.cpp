@@ -8,8 +8,9 @@
 // X / dy / Y / dX are logical (N, C, R) tensors with strides (R*C, 1, C), i.e. NHWC storage.
 // Differences from the reference, all deliberate: the namespace (so both libraries can live in one
 // process), means/rstds are fp32, every argument is validated, the tensor's device is made current,
-// and a third op `bwd_f32` returns the parameter gradients as one packed fp32 [2, C] tensor (the
-// buffer a data-parallel caller all-reduces).
+// a third op `bwd_f32` returns the parameter gradients as one packed fp32 [2, C] tensor (the
+// buffer a data-parallel caller all-reduces), and the ops carry explicit schemas with a CUDA
+// implementation (the reference registers catch-all functions, which cannot be traced).
 #include <ATen/Tensor.h>
 #include <ATen/ops/empty.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -145,8 +146,26 @@ std::tuple<at::Tensor, at::Tensor> gnb200_bwd_f32_op(const at::Tensor& dy, const
 
 }  // namespace
 
+// Schemas are declared apart from the implementations so that Python can attach fake-tensor
+// kernels and an autograd formula to them (channels_last_groupnorm_b200/_compile.py), which is what
+// torch.compile needs.  The CPU registration exists only to fail with the message of check_nhwc3
+// instead of the dispatcher's.
 TORCH_LIBRARY(gnb200, m) {
-  m.def("fwd", &gnb200_fwd_op);
-  m.def("bwd", &gnb200_bwd_op);
-  m.def("bwd_f32", &gnb200_bwd_f32_op);
+  m.def("fwd(Tensor X, Tensor weight, Tensor bias, int G, float eps, int act) -> (Tensor, Tensor, Tensor)");
+  m.def("bwd(Tensor dy, Tensor X, Tensor weight, Tensor bias, Tensor means, Tensor rstds, int G, int act) -> "
+        "(Tensor, Tensor, Tensor)");
+  m.def("bwd_f32(Tensor dy, Tensor X, Tensor weight, Tensor bias, Tensor means, Tensor rstds, int G, int act) -> "
+        "(Tensor, Tensor)");
+}
+
+TORCH_LIBRARY_IMPL(gnb200, CUDA, m) {
+  m.impl("fwd", &gnb200_fwd_op);
+  m.impl("bwd", &gnb200_bwd_op);
+  m.impl("bwd_f32", &gnb200_bwd_f32_op);
+}
+
+TORCH_LIBRARY_IMPL(gnb200, CPU, m) {
+  m.impl("fwd", &gnb200_fwd_op);
+  m.impl("bwd", &gnb200_bwd_op);
+  m.impl("bwd_f32", &gnb200_bwd_f32_op);
 }

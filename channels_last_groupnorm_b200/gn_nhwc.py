@@ -9,6 +9,13 @@ against `gnnhwc` only has to change its import.  What differs, on purpose:
   tensors.  Everything that runs goes through the sm_100a kernels.
 * backward accepts any rank >= 3 (the reference's `dy.contiguous(memory_format=channels_last)`
   only works for rank 4, custom_gn.py:44).
+* parameters whose dtype differs from the input's (fp32 weight / bias with fp16 / bf16
+  activations, the autocast convention; the reference raises on the mismatch,
+  custom_gn.cpp:35-36) are rounded to the input dtype for the kernels; their gradients are taken
+  from the fp32 sums the backward kernels write and returned in the parameters' dtype.
+* the module is not excluded from dynamo (the reference decorates `forward` with
+  `torch._dynamo.disable`, custom_gn.py:63): the ops have fake-tensor kernels and an autograd
+  formula (`_compile.py`), so `torch.compile` traces through them.
 * `process_group`: for batch-sharded data-parallel training the packed fp32 `[dgamma | dbeta]`
   buffer written by the backward kernels is summed across the ranks of that group with one
   all-reduce; forward needs no communication.
@@ -56,6 +63,11 @@ class GN_NHWC_Func(torch.autograd.Function):
             raise ValueError("GN_NHWC_Func: X must have shape (N, C, *spatial) with at least one spatial dim")
         ctx.x_shape = X.shape
         X_flat = _as_nhwc_flat(X)
+        ctx.param_dtypes = (weight.dtype, bias.dtype)
+        if weight.dtype != X.dtype:
+            weight = weight.to(X.dtype)
+        if bias.dtype != X.dtype:
+            bias = bias.to(X.dtype)
         Y, means, rstds = torch.ops.gnb200.fwd(X_flat, weight, bias, int(G), float(eps), int(activation))
         ctx.save_for_backward(X_flat, weight, bias, means, rstds)
         ctx.G = int(G)
@@ -67,12 +79,17 @@ class GN_NHWC_Func(torch.autograd.Function):
     def backward(ctx, dy):
         X_flat, weight, bias, means, rstds = ctx.saved_tensors
         dy_flat = _as_nhwc_flat(dy)
-        if ctx.process_group is None:
+        if dy_flat.dtype != X_flat.dtype:
+            dy_flat = dy_flat.to(X_flat.dtype)
+        w_dtype, b_dtype = ctx.param_dtypes
+        same = w_dtype == X_flat.dtype and b_dtype == X_flat.dtype
+        if ctx.process_group is None and same:
             dx, dgamma, dbeta = torch.ops.gnb200.bwd(dy_flat, X_flat, weight, bias, means, rstds, ctx.G, ctx.activation)
         else:
             dx, dparam = torch.ops.gnb200.bwd_f32(dy_flat, X_flat, weight, bias, means, rstds, ctx.G, ctx.activation)
-            torch.distributed.all_reduce(dparam, op=torch.distributed.ReduceOp.SUM, group=ctx.process_group)
-            dgamma, dbeta = dparam[0].to(weight.dtype), dparam[1].to(weight.dtype)
+            if ctx.process_group is not None:
+                torch.distributed.all_reduce(dparam, op=torch.distributed.ReduceOp.SUM, group=ctx.process_group)
+            dgamma, dbeta = dparam[0].to(w_dtype), dparam[1].to(b_dtype)
         return _restore_shape(dx, ctx.x_shape), dgamma, dbeta, None, None, None, None
 
 
@@ -99,7 +116,6 @@ class GN_NHWC(nn.GroupNorm):
         self.act_code = ACTIVATION_CODES[activation]
         self.process_group = process_group
 
-    @torch._dynamo.disable
     def forward(self, x):
         if not x.is_cuda:
             raise ValueError("GN_NHWC: input must be a CUDA tensor; this package has no CPU path")

@@ -127,3 +127,20 @@ def test_torch_ops_are_registered_with_reference_schemas():
     assert len(bwd.returns) == 3
     with pytest.raises(RuntimeError, match="CUDA"):
         torch.ops.gnb200.fwd(torch.randn(1, 8, 4).permute(0, 2, 1), torch.ones(8), torch.zeros(8), 2, 1e-5, 0)
+
+
+def test_fake_tensor_kernels_describe_the_outputs():
+    # shapes, strides and dtypes without a device: what torch.compile sees of the ops
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        X = torch.empty(2, 16, 8, dtype=torch.bfloat16, device="meta").permute(0, 2, 1)
+        w = torch.empty(8, dtype=torch.bfloat16, device="meta")
+        b = torch.empty(8, dtype=torch.bfloat16, device="meta")
+        Y, means, rstds = torch.ops.gnb200.fwd(X, w, b, 2, 1e-5, 3)
+        assert Y.shape == X.shape and Y.stride() == X.stride() and Y.dtype == X.dtype
+        assert means.shape == (2, 2) and means.dtype == torch.float32 and rstds.shape == (2, 2)
+        dX, dw, db = torch.ops.gnb200.bwd(Y, X, w, b, means, rstds, 2, 3)
+        assert dX.stride() == X.stride() and dw.shape == (8,) and db.dtype == torch.bfloat16
+        dX, dparam = torch.ops.gnb200.bwd_f32(Y, X, w, b, means, rstds, 2, 3)
+        assert dparam.shape == (2, 8) and dparam.dtype == torch.float32

@@ -311,6 +311,66 @@ def test_module_forward_backward_matches_oracle(nt):
         assert xd.grad.stride() == xd.stride()
 
 
+@pytest.mark.parametrize("dt", ["float16", "bfloat16"])
+def test_module_with_fp32_parameters_and_16bit_input(nt, dt):
+    # the autocast convention: fp32 weight / bias, 16-bit activations.  The kernels see the
+    # parameters rounded to the activation dtype; gradients come back in fp32.
+    import channels_last_groupnorm_b200 as pkg
+
+    N, C, sp, G = 3, 64, (12, 20), 8
+    x, ga, be, dy = O.make_inputs(N, C, sp, torch.float32, seed=11)
+    x, dy = x.to(DT[dt]), dy.to(DT[dt])
+    m = pkg.GN_NHWC(G, C, activation="silu", eps=1e-5).cuda()
+    with torch.no_grad():
+        m.weight.copy_(ga)
+        m.bias.copy_(be)
+    assert m.weight.dtype == torch.float32
+    xin = x.cuda().to(memory_format=torch.channels_last).requires_grad_(True)
+    y = m(xin)
+    assert y.dtype == DT[dt]
+    y.backward(dy.cuda().to(memory_format=torch.channels_last))
+    assert m.weight.grad.dtype == torch.float32 and m.bias.grad.dtype == torch.float32
+    want = O.oracle_c(x, ga.to(DT[dt]), be.to(DT[dt]), dy, G, 1e-5, "silu")
+    got = {"y": y.detach(), "dx": xin.grad, "dgamma": m.weight.grad, "dbeta": m.bias.grad}
+    check_against(got, want, DT[dt])
+
+
+def test_forward_op_is_differentiable_on_its_own(nt):
+    # torch.ops.gnb200.fwd carries an autograd formula (its backward is torch.ops.gnb200.bwd)
+    N, C, sp, G = 2, 32, (9, 11), 4
+    x, ga, be, dy = O.make_inputs(N, C, sp, torch.float32, seed=12)
+    want = O.oracle_c(x, ga, be, dy, G, 1e-5, "gelu")
+    X = _flat(x.cuda()).permute(0, 2, 1).requires_grad_(True)
+    w, b = ga.cuda().requires_grad_(True), be.cuda().requires_grad_(True)
+    Y, _, _ = torch.ops.gnb200.fwd(X, w, b, G, 1e-5, O.ACT_CODES["gelu"])
+    dX, dw, db = torch.autograd.grad(Y, (X, w, b), _flat(dy.cuda()).permute(0, 2, 1))
+    got = {"y": _unflat(Y.detach().permute(0, 2, 1), x.shape), "dx": _unflat(dX.permute(0, 2, 1), x.shape),
+           "dgamma": dw, "dbeta": db}
+    check_against(got, want, torch.float32)
+
+
+def test_module_under_torch_compile(nt):
+    import channels_last_groupnorm_b200 as pkg
+
+    N, C, sp, G = 2, 64, (16, 16), 8
+    x, ga, be, dy = O.make_inputs(N, C, sp, torch.float16, seed=13)
+    want = O.oracle_c(x, ga, be, dy, G, 1e-5, "silu")
+    m = pkg.GN_NHWC(G, C, activation="silu").cuda().half()
+    with torch.no_grad():
+        m.weight.copy_(ga)
+        m.bias.copy_(be)
+
+    def step(t):
+        return m(t * 1.0) + 0.0
+
+    compiled = torch.compile(step)
+    xin = x.cuda().to(memory_format=torch.channels_last).requires_grad_(True)
+    y = compiled(xin)
+    y.backward(dy.cuda().to(memory_format=torch.channels_last))
+    got = {"y": y.detach(), "dx": xin.grad, "dgamma": m.weight.grad, "dbeta": m.bias.grad}
+    check_against(got, want, torch.float16)
+
+
 def test_module_affine_false_and_state_dict(nt):
     import channels_last_groupnorm_b200 as pkg
 
