@@ -77,23 +77,48 @@ __device__ __forceinline__ void bwd_row_sums(const float (&fx)[VE], float (&fd)[
   }
 }
 
-// 16-bit tensors, fused path: yh straight from x (a = rstd * gamma, b = beta - mean * a) and
-// S2 accumulated against the raw x; the caller converts it with S2 = rstd * (S2raw - mean * S1).
-// One FMA per element less; the conversion's rounding (relative 1e-7 * |mean| * rstd) is far
-// below a 16-bit result.
-template <typename T, int VE, int ACT>
-__device__ __forceinline__ void bwd_row_sums_raw(const float (&fx)[VE], float (&fd)[VE], const float (&a)[VE],
-                                                 const float (&b)[VE], float (&s1)[VE], float (&s2)[VE]) {
-  float yh[VE], gr[VE];
+// 16-bit tensors, fused path: yh straight from x (a = rstd * gamma, b = beta - mean * a) and S2
+// accumulated against the raw x; the caller converts it with S2 = rstd * (S2raw - mean * S1).  One
+// FMA per element less; the conversion's rounding (relative 1e-7 * |mean| * rstd) is far below a
+// 16-bit result.
+// It works on the packed 16-bit values: dyh = dy * act'(yh) is formed two channels at a time in the tensor's own 16-bit format - which is
+// the format it is parked in anyway - and enters the fp32 sums through mixed-precision add / fma,
+// so dy is never unpacked and dyh never packed.  act' is evaluated in f16x2; for bf16 tensors it
+// is rounded to bf16 before the product.  Returns the packed dyh.
+template <typename T, int ACT>
+__device__ __forceinline__ uint4 bwd_row_sums_packed(const uint4& xw, const uint4& dw, const float (&a)[8],
+                                                     const float (&b)[8], float (&s1)[8], float (&s2)[8]) {
+  static_assert(sizeof(T) == 2, "16-bit tensors only");
+  const uint32_t xr[4] = {xw.x, xw.y, xw.z, xw.w}, dr[4] = {dw.x, dw.y, dw.z, dw.w};
+  uint32_t out[4];
 #pragma unroll
-  for (int e = 0; e < VE; ++e) yh[e] = fmaf(fx[e], a[e], b[e]);
-  act_grad_vec<T, VE, ACT>(yh, gr);
-#pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    fd[e] *= gr[e];
-    s1[e] += fd[e];
-    s2[e] = fmaf(fd[e], fx[e], s2[e]);
+  for (int p = 0; p < 4; ++p) {
+    uint16_t x0, x1;
+    split_halves(xr[p], x0, x1);
+    uint32_t dyh = dr[p];
+    if constexpr (ACT != kActIdentity) {
+      const float yh0 = fmaf(mixed_add<T>(x0, -0.0f), a[2 * p], b[2 * p]);
+      const float yh1 = fmaf(mixed_add<T>(x1, -0.0f), a[2 * p + 1], b[2 * p + 1]);
+      const __half2 g = act_grad_h2<ACT>(f32x2_to_h2_sat(yh0, yh1));
+      if constexpr (std::is_same<T, __half>::value) {
+        const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&dr[p]), g);
+        dyh = *reinterpret_cast<const uint32_t*>(&r);
+      } else {
+        const float2 gf = __half22float2(g);
+        const __nv_bfloat162 gb = __floats2bfloat162_rn(gf.x, gf.y);
+        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&dr[p]), gb);
+        dyh = *reinterpret_cast<const uint32_t*>(&r);
+      }
+    }
+    uint16_t d0, d1;
+    split_halves(dyh, d0, d1);
+    s1[2 * p] = mixed_add<T>(d0, s1[2 * p]);
+    s1[2 * p + 1] = mixed_add<T>(d1, s1[2 * p + 1]);
+    s2[2 * p] = mixed_fma<T>(d0, x0, s2[2 * p]);
+    s2[2 * p + 1] = mixed_fma<T>(d1, x1, s2[2 * p + 1]);
+    out[p] = dyh;
   }
+  return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
 constexpr int kRingDepth = 8;  // rows in flight per thread in the multi-kernel reduce kernel
@@ -222,9 +247,7 @@ __device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kXRing - 1>();
       const uint32_t slot = ring + (i & (kXRing - 1)) * ring_stride;
-      float fx[VE], fd[VE];
-      unpack16<T, VE>(lds128(slot), fx);
-      unpack16<T, VE>(lds128(rd), fd);
+      const uint4 xw = lds128(slot), dw = lds128(rd);
       if (i + kXRing < iters) {
         cp_async16(slot, gx);
         gx += gstep_elems;
@@ -236,11 +259,16 @@ __device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep
         ++dy_issued;
       }
       cp_async_commit();
-      if constexpr (kRaw)
-        bwd_row_sums_raw<T, VE, ACT>(fx, fd, a, b, s1, s2);
-      else
+      if constexpr (kRaw) {
+        const uint4 dyh = bwd_row_sums_packed<T, ACT>(xw, dw, a, b, s1, s2);
+        if constexpr (ACT != kActIdentity) sts128(rd, dyh);  // identity: dyh is dy, already in place
+      } else {
+        float fx[VE], fd[VE];
+        unpack16<T, VE>(xw, fx);
+        unpack16<T, VE>(dw, fd);
         bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
-      sts128(rd, pack16<T, VE>(fd));
+        sts128(rd, pack16<T, VE>(fd));
+      }
       rd += sstep_bytes;
     }
     if constexpr (kRaw) {  // S2 = sum dyh * xh = rstd * (sum dyh * x - mean * sum dyh)

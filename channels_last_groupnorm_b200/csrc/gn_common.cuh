@@ -465,7 +465,9 @@ __device__ __forceinline__ __half2 act_fwd_h2(__half2 v) {
 template <int ACT>
 __device__ __forceinline__ __half2 act_grad_h2(__half2 v) {
   const __half2 half_ = __float2half2_rn(0.5f), one = __float2half2_rn(1.0f);
-  if constexpr (ACT == kActSilu) {
+  if constexpr (ACT == kActRelu) {
+    return __hgt2(v, __float2half2_rn(0.0f));  // 1.0 where v > 0, else 0.0
+  } else if constexpr (ACT == kActSilu) {
     const __half2 t = tanh_h2(__hmul2(v, half_));
     const __half2 s = __hfma2(half_, t, half_);
     return __hmul2(s, __hfma2(v, __hsub2(one, s), one));
