@@ -232,6 +232,43 @@ def test_persistent_clusters_over_many_items(nt, case):
         assert torch.equal(out[k], again[k]), k
 
 
+def test_dependent_calls_back_to_back(nt):
+    # A chain in which each call consumes the previous call's output (forward feeding forward, dx
+    # feeding the next backward), issued without any host synchronisation: the persistent forward
+    # kernel, the backward kernel and the parameter-gradient kernel follow each other on the stream.
+    # The chain must give bit-identical results when run twice and when replayed from a CUDA graph.
+    N, C, sp, G = 8, 128, (24, 24), 16
+    x, ga, be, dy = O.make_inputs(N, C, sp, torch.bfloat16, seed=21)
+    xf, dyf, gad, bed = _flat(x.cuda()), _flat(dy.cuda()), ga.cuda(), be.cuda()
+
+    def chain():
+        cur, grads = xf, dyf
+        for _ in range(6):
+            y, mean, rstd = nt.fwd_raw(cur, gad, bed, G, 1e-5, 2)
+            dx, dparam, _, _ = nt.bwd_raw(grads, cur, gad, bed, mean, rstd, G, 2)
+            cur, grads = y, dx
+        return cur.clone(), grads.clone(), dparam.clone()
+
+    want = chain()
+    torch.cuda.synchronize()
+    got = chain()
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        chain()  # warm-up on the capture stream
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            captured = chain()
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    for a, b in zip(captured, want):
+        assert torch.equal(a, b)
+
+
 def test_no_exchange_wait_gave_up(nt):
     # the bounded waits of the cluster exchange count the times they gave up; any count means that
     # a kernel carried on with meaningless statistics
