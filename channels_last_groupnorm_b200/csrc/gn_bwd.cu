@@ -11,9 +11,10 @@
 //
 //  fused   one launch + a tiny parameter-gradient kernel.  A cluster of k CTAs owns one (sample,
 //          column block) slab: it reads x and dy once from HBM, reduces S1/S2, keeps dyh in shared
-//          memory, exchanges the group sums through distributed shared memory and writes dx from
-//          the dyh tile and x, which it reads a second time from L2 a few microseconds after the
-//          first read (the slab share of all resident CTAs is a few tens of MB, far below L2).
+//          memory, exchanges the group sums by pushing them into its peers' shared memory
+//          (st.async + mbarrier, no cluster barrier) and writes dx from the dyh tile and x, which
+//          it reads a second time from L2 a few microseconds after the first read (the slab share
+//          of all resident CTAs is a few tens of MB, far below L2).
 //          HBM traffic: x and dy read once, dx written once.
 //  two-pass  reduce kernel (per-tile channel sums to scratch) -> finalize (fixed-order sums, A, B)
 //          -> parameter-gradient kernel -> apply kernel (reverse tile order for L2 reuse).

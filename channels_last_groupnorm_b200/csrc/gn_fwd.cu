@@ -1,12 +1,13 @@
 // Forward GroupNorm (+activation) kernels for NHWC tensors, sm_100a.
 //
-// Two launch plans (chosen by the host planner in gn_plan.cpp):
+// Two launch plans (chosen by the host planner in gn_plan.cu):
 //
-//  fused   one launch.  A thread-block cluster of k CTAs owns one (sample, column block) slab;
-//          each CTA streams its rows from HBM once (16-byte loads along C), keeps them in shared
-//          memory while accumulating Welford moments, the k partial moments are combined through
-//          distributed shared memory, and the tile is normalised, scaled, shifted, activated and
-//          written from shared memory.  HBM traffic: one read + one write of the tensor.
+//  fused   one launch of persistent thread-block clusters.  A cluster of k CTAs works through
+//          (sample, column block) slabs; each CTA copies its rows from HBM once (16-byte cp.async
+//          along C) into shared memory while accumulating moments, the k partial moments are
+//          pushed into the peers' shared memory (st.async + mbarrier), and the tile is normalised,
+//          scaled, shifted, activated and written from shared memory while its slots are refilled
+//          with the rows of the cluster's next slab.  HBM traffic: one read + one write of the tensor.
 //
 //  two-pass  for slabs that do not fit a cluster's shared memory: stats kernel (partial moments
 //          per CTA to scratch) -> finalize kernel (fixed-order merge -> mean, rstd) -> apply
