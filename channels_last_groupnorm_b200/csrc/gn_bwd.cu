@@ -122,7 +122,7 @@ __device__ __forceinline__ uint4 bwd_row_sums_packed(const uint4& xw, const uint
   return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
-constexpr int kRingDepth = 8;  // rows in flight per thread in the multi-kernel reduce kernel
+constexpr int kRingDepth = 4;  // rows in flight per thread in the multi-kernel reduce kernel
 
 // Phase 1 of the multi-kernel path: S1, S2 over the thread's rows.  16-byte vectors of x and dy
 // travel through two shared-memory rings with cp.async (kRingDepth rows per thread in flight,

@@ -70,7 +70,7 @@ __device__ __forceinline__ void shifted_finish(const float (&K)[KN], int rows, f
   }
 }
 
-constexpr int kRingDepth = 8;  // rows in flight per thread in the multi-kernel streaming kernels
+constexpr int kRingDepth = 4;  // rows in flight per thread in the multi-kernel streaming kernels
 
 // Per-thread running moments over the rows this thread owns (rows ty, ty + TY, ...) in the
 // multi-kernel path.  16-byte vectors go through a shared-memory ring with cp.async: kRingDepth

@@ -289,8 +289,8 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
   p.threads = threads;
   p.grid = (long long)sh.N * chunks * ncb;
   if (p.grid > 0x7fffffffLL) return false;
-  // shared-memory rings of the streaming kernels: 8 rows x 16 bytes per thread (x; x and dy)
-  const size_t ring = ve > 1 ? (size_t)8 * threads * 16 : 0;
+  // shared-memory rings of the streaming kernels: 4 rows x 16 bytes per thread (x; x and dy) - kRingDepth
+  const size_t ring = ve > 1 ? (size_t)4 * threads * 16 : 0;
   if (sh.direction == 0) {
     p.smem_bytes = ring + fwd_fold_floats(cw, CV, TY, slots, threads, false, 0, 1) * 4;
     p.ws_bytes = (size_t)p.grid * slots * 3 * sizeof(float);
