@@ -258,10 +258,11 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
   int slots = (cw - 1) / sh.D + 2;
   if (slots > sh.G) slots = sh.G;
 
-  // rows per CTA tile: large tiles amortise the per-thread set-up and the per-CTA reduction (about
-  // three tiles per SM, up to 512 KB of x per tile), but at least ~4 tiles per SM when the problem allows
+  // rows per CTA tile: large tiles amortise the per-thread set-up and the per-CTA reduction; about
+  // four tiles per SM measured best for the reduce and apply kernels (up to 512 KB of x per tile),
+  // and at least two tiles per SM when the problem allows
   const long long row_bytes = (long long)cw * s;
-  long long tile_target = (long long)sh.N * sh.R * sh.C * s / (3LL * kSmCount);
+  long long tile_target = (long long)sh.N * sh.R * sh.C * s / (4LL * kSmCount);
   if (tile_target < 64 * 1024) tile_target = 64 * 1024;
   if (tile_target > 512 * 1024) tile_target = 512 * 1024;
   long long rows = (tile_target + row_bytes - 1) / row_bytes;
