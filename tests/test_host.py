@@ -89,6 +89,36 @@ def test_planner_paths(shape, dtype, path):
             assert nt.launch_count(*shape, dtype, direction) == (1 if direction == 0 else 2)
 
 
+def test_planner_invariants_over_random_shapes():
+    # every plan must fit the SM (shared memory, threads), keep whole groups inside a cluster's
+    # column block, and never ask for more scratch than the workspace query reports
+    import random
+
+    rng = random.Random(7)
+    codes = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+    for _ in range(400):
+        G = rng.choice([1, 2, 3, 4, 8, 16, 32, 64])
+        D = rng.choice([1, 2, 3, 4, 5, 8, 10, 16, 20, 40, 64])
+        C = G * D
+        R = rng.choice([1, 7, 49, 64, 255, 256, 1024, 3136, 4096, 16384, 65536, 1 << 20])
+        N = rng.choice([1, 2, 3, 8, 64])
+        dtype = rng.choice(list(codes))
+        if N * R * C > 1 << 31:
+            continue
+        for direction in (0, 1):
+            text = nt.describe_plan(N, R, C, G, dtype, direction)
+            fields = dict(kv.split("=") for kv in text.split()[2:])
+            threads, smem, cw, ve, k = (int(fields[x]) for x in ("threads", "smem", "cw", "ve", "k"))
+            assert threads % 32 == 0 and 32 <= threads <= 512, text
+            assert smem <= 227 * 1024, text
+            assert cw % ve == 0 and int(fields["grid"]) >= 1, text
+            if " fused " in text:
+                assert cw % D == 0 and C % cw == 0 and k in (1, 2, 4, 8), text
+                assert int(fields["rows"]) * k >= R, text
+            query = nt.lib.gnb200_fwd_workspace_bytes if direction == 0 else nt.lib.gnb200_bwd_workspace_bytes
+            assert int(fields["ws"]) <= query(N, R, C, G, codes[dtype]), text
+
+
 def test_planner_env_override(monkeypatch):
     monkeypatch.setenv("GNB200_FORCE_PATH", "twopass")
     assert " twopass " in nt.describe_plan(2, 1024, 128, 32, torch.float32, 0)
