@@ -133,6 +133,13 @@ __device__ __forceinline__ void stream_bwd_sums(const T* __restrict__ gx, const 
                                                 uint32_t ring_stride, const BwdLane<T, VE>& L, float (&s1)[VE],
                                                 float (&s2)[VE]) {
   if constexpr (sizeof(T) * VE == 16) {
+    constexpr bool kRaw = sizeof(T) == 2;  // 16-bit tensors: packed arithmetic, S2 against the raw x
+    float a[VE], b[VE];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      a[e] = L.r[e] * L.ga[e];
+      b[e] = fmaf(L.nmr[e], L.ga[e], L.be[e]);
+    }
 #pragma unroll
     for (int d = 0; d < kRingDepth; ++d) {
       if (d < iters) {
@@ -146,9 +153,7 @@ __device__ __forceinline__ void stream_bwd_sums(const T* __restrict__ gx, const 
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kRingDepth - 1>();
       const uint32_t off = (i & (kRingDepth - 1)) * ring_stride;
-      float fx[VE], fd[VE];
-      unpack16<T, VE>(lds128(ring_x + off), fx);
-      unpack16<T, VE>(lds128(ring_d + off), fd);
+      const uint4 xw = lds128(ring_x + off), dw = lds128(ring_d + off);
       if (i + kRingDepth < iters) {
         cp_async16(ring_x + off, gx);
         cp_async16(ring_d + off, gd);
@@ -156,7 +161,18 @@ __device__ __forceinline__ void stream_bwd_sums(const T* __restrict__ gx, const 
         gd += gstep_elems;
       }
       cp_async_commit();
-      bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+      if constexpr (kRaw) {
+        bwd_row_sums_packed<T, ACT>(xw, dw, a, b, s1, s2);
+      } else {
+        float fx[VE], fd[VE];
+        unpack16<T, VE>(xw, fx);
+        unpack16<T, VE>(dw, fd);
+        bwd_row_sums<T, VE, ACT>(fx, fd, L, s1, s2);
+      }
+    }
+    if constexpr (kRaw) {  // S2 = sum dyh * xh = rstd * (sum dyh * x - mean * sum dyh)
+#pragma unroll
+      for (int e = 0; e < VE; ++e) s2[e] = fmaf(L.r[e], s2[e], L.nmr[e] * s1[e]);
     }
   } else {
     for (int i = 0; i < iters; ++i) {
