@@ -460,7 +460,8 @@ __device__ __forceinline__ void stream_bwd_dx(const Pack<T, VE>* xs, const Pack<
 // scratch out : sums[((n * k + rank) * C + c) * 2 + {0,1}] = S1, S2 over this CTA's rows
 // ------------------------------------------------------------------------------------------------
 // MAXT: CTA size class.  128-thread launches are compiled for five CTAs per SM (<= 96 registers).
-template <typename T, int VE, int ACT, bool UNI, int MAXT>
+// SHUF: the shuffle reductions (Geom::shuf) are compiled in instead of the generic ones.
+template <typename T, int VE, int ACT, bool UNI, int MAXT, bool SHUF>
 __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
     gn_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                         const T* __restrict__ beta, const float* __restrict__ mean_in,
@@ -480,7 +481,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   const uint32_t ring = smem_addr(reinterpret_cast<char*>(smem_raw) + tile_bytes) + threadIdx.x * 16;
   const uint32_t ring_stride = blockDim.x * 16;
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + tile_bytes + ring_bytes);
-  const bool shuf = UNI && g.shuf;
+  constexpr bool shuf = SHUF;
   float* part = red + g.red_floats;                      // generic reductions only
   float* chan = part + 2 * max((int)blockDim.x, g.CW);  // generic reductions only
   float* spart = shuf ? part : chan + 2 * g.CW;  // generic reductions: [2*s] = sum gamma S1, [2*s+1] = sum gamma S2 of this CTA
@@ -526,7 +527,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   int g_lo, n_slots;
   cb_groups(g, c0, g_lo, n_slots);
   const int c_valid = min(g.CW, g.C - c0);
-  if (shuf) {
+  if constexpr (shuf) {
     // gamma-weighted group sums straight from registers: xor-butterflies + one pass over the warps
     float a1 = 0.f, a2 = 0.f;
     if (streaming) {
@@ -563,7 +564,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
       }
     }
   }
-  if (!shuf) {
+  if constexpr (!shuf) {
     __syncthreads();
     for (int s = tid; s < g.slots; s += blockDim.x) {
       const bool live = s < n_slots;
@@ -575,11 +576,11 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   // parameter-gradient kernel).  On the shuffle path this work overlaps the wait for the peers.
   {
     float2* out = reinterpret_cast<float2*>(sums) + (((size_t)n * k + rank) * g.C + c0);
-    if constexpr (VE % 4 == 0) {
-      if (shuf) cta_channel_sums_shuf<VE>(g, s1, s2, tx, red + g.wpart_off, out, c_valid);
-    }
-    if (!shuf)
+    if constexpr (shuf) {
+      cta_channel_sums_shuf<VE>(g, s1, s2, tx, red + g.wpart_off, out, c_valid);
+    } else {
       for (int c = tid; c < c_valid; c += blockDim.x) out[c] = make_float2(chan[c], chan[g.CW + c]);
+    }
   }
   // every CTA of the cluster pushed its group sums into every inbox: no cluster barrier, no fence
   mbar_wait_bounded(mbar, 0, g.wait_timeouts);
@@ -809,7 +810,14 @@ static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t st
     float* sums = reinterpret_cast<float*>(c.workspace);
     cudaError_t werr = wait_timeout_counter(&g.wait_timeouts);
     if (werr != cudaSuccess) return werr;
-    auto kern = p.threads <= 128 ? gn_bwd_fused_kernel<T, VE, ACT, UNI, 128> : gn_bwd_fused_kernel<T, VE, ACT, UNI, kMaxThreads>;
+    constexpr bool kCanShuf = UNI && VE >= 4;
+    auto kern = p.threads <= 128 ? gn_bwd_fused_kernel<T, VE, ACT, UNI, 128, false>
+                                 : gn_bwd_fused_kernel<T, VE, ACT, UNI, kMaxThreads, false>;
+    if constexpr (kCanShuf) {
+      if (g.shuf)
+        kern = p.threads <= 128 ? gn_bwd_fused_kernel<T, VE, ACT, UNI, 128, true>
+                                : gn_bwd_fused_kernel<T, VE, ACT, UNI, kMaxThreads, true>;
+    }
     cudaError_t err = ensure_kernel_attributes((const void*)kern, p.smem_bytes, g.k > 8);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};

@@ -680,96 +680,6 @@ __device__ __forceinline__ void cta_group_sum(const Geom& g, const float (&val)[
   __syncthreads();
 }
 
-// Merge of two (count, mean, M2) summaries (Chan et al.); a summary with count 0 is neutral.
-__device__ __forceinline__ void moments_merge(float& n, float& mu, float& m2, float nb, float mub, float m2b) {
-  const float nt = n + nb;
-  if (nt > 0.f) {
-    const float w = __fdividef(nb, nt);
-    const float d = mub - mu;
-    mu = fmaf(d, w, mu);
-    m2 = m2 + m2b + d * d * n * w;
-  }
-  n = nt;
-}
-
-// CTA-local moments of every group slot of the column block in one pass, for geometries without
-// the shuffle reductions: every streaming thread parks (mean, M2) of its VE channels - or, when
-// all of them lie in one group (UNI), of their union - then one warp per slot merges the summaries
-// of the slot, each lane a fixed subsequence, then a fixed shuffle tree, so the result does not
-// depend on timing.  Lane 0 of the warp calls emit(slot, mean, M2, count).  One __syncthreads
-// inside (before the merge); the caller orders the reuse of `red` (2 * TY * CW floats).
-template <int VE, bool UNI, typename Emit>
-__device__ __forceinline__ void cta_slot_moments_merge(const Geom& g, const float (&mean)[VE], const float (&m2)[VE],
-                                                       int tx, int ty, int c0, int nrows, int g_lo, int n_slots,
-                                                       int total_slots, float* red, Emit emit) {
-  constexpr int NV = UNI ? 1 : VE;             // summaries parked per thread
-  const int TY = g.TY, cols = g.CV * NV;       // summaries per row lane
-  const float per = UNI ? (float)VE : 1.0f;    // channels per summary
-  float* rmean = red;
-  float* rm2 = red + TY * cols;
-  if (ty < TY && tx < g.CV) {
-    if constexpr (UNI) {  // equal counts: mean of the means, M2 = sum M2 + rows * sum (mean_e - mean)^2
-      const int rows_t = ty < nrows ? (nrows - ty + TY - 1) / TY : 0;
-      float sm = 0.f;
-#pragma unroll
-      for (int e = 0; e < VE; ++e) sm += mean[e];
-      const float mt = sm * (1.0f / VE);
-      float dev = 0.f, acc = 0.f;
-#pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        const float d = mean[e] - mt;
-        dev = fmaf(d, d, dev);
-        acc += m2[e];
-      }
-      rmean[ty * cols + tx] = mt;
-      rm2[ty * cols + tx] = fmaf((float)rows_t, dev, acc);
-    } else {
-#pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        rmean[ty * cols + tx * VE + e] = mean[e];
-        rm2[ty * cols + tx * VE + e] = m2[e];
-      }
-    }
-  }
-  __syncthreads();
-  const int c_valid = min(g.CW, g.C - c0);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
-  for (int s = warp; s < total_slots; s += nwarps) {
-    float n = 0.f, mu = 0.f, q = 0.f;
-    if (s < n_slots) {
-      int lo = max((g_lo + s) * g.D, c0) - c0;
-      int hi = min((g_lo + s + 1) * g.D, c0 + c_valid) - c0;
-      if constexpr (UNI) {  // channels -> vectors (group boundaries are multiples of VE here)
-        lo /= VE;
-        hi /= VE;
-      }
-      const int w = hi - lo;
-      const int total = TY * w;
-      // entry idx = j * w + c: row lane j, column lo + c; this lane takes idx = lane, lane + 32, ...
-      int j = lane / w, c = lane - j * w;
-      const int dj = 32 / w, dc = 32 - dj * w;
-      for (int idx = lane; idx < total; idx += 32) {
-        const int rows_j = j < nrows ? (nrows - j + TY - 1) / TY : 0;  // rows streamed by row lane j
-        moments_merge(n, mu, q, per * (float)rows_j, rmean[j * cols + lo + c], rm2[j * cols + lo + c]);
-        j += dj;
-        c += dc;
-        if (c >= w) {
-          c -= w;
-          ++j;
-        }
-      }
-#pragma unroll
-      for (int delta = 16; delta >= 1; delta >>= 1) {
-        const float nb = __shfl_down_sync(0xffffffffu, n, delta);
-        const float mub = __shfl_down_sync(0xffffffffu, mu, delta);
-        const float qb = __shfl_down_sync(0xffffffffu, q, delta);
-        moments_merge(n, mu, q, nb, mub, qb);
-      }
-    }
-    if (lane == 0) emit(s, mu, q, n);
-  }
-}
-
 // Sum of one value per thread over the CTA, per group slot, for the shuffle geometry (Geom::shuf):
 // lanes of a warp that share a slot are combined with xor-butterflies (identical result in every
 // lane), warp results go through `wsum` (nwarps * n_slots floats) and are added in warp order.

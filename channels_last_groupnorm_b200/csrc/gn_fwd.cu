@@ -543,12 +543,13 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
         for (unsigned q = 0; q < k; ++q) st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, q, lm, m2loc, n_loc, 0.f);
       }
     } else {
-      // one pass: (mean, M2) of every channel parked in `red`, one warp per slot merges and pushes
-      cta_slot_moments_merge<VE, UNI>(g, mean, m2, tx, ty, c0, nrows, g_lo, n_slots, g.slots, red,
-                                 [&](int s, float mu, float q, float n_loc) {
-                                   for (unsigned p = 0; p < k; ++p)
-                                     st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, p, mu, q, n_loc, 0.f);
-                                 });
+      cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
+      __syncthreads();
+      for (int s = tid; s < g.slots; s += blockDim.x) {
+        const bool live = s < n_slots;
+        const float a = live ? slot[s] : 0.f, b = live ? slot[g.slots + s] : 0.f, c = live ? slot[2 * g.slots + s] : 0.f;
+        for (unsigned q = 0; q < k; ++q) st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, q, a, b, c, 0.f);
+      }
     }
     {
       // Every CTA of the cluster pushed (mean, M2, count) of each slot into every inbox.  Combine them

@@ -66,7 +66,7 @@ size_t fwd_red_floats(int CW, int CV, int TY, int slots, int threads, bool shuf,
     const int a = 2 * wsum_stride_floats(threads, CV, tps_shift), b = 16 * 3 * slots;
     return (size_t)round_up4(a > b ? a : b);
   }
-  size_t r = (size_t)2 * TY * CW;  // fused kernel: (mean, M2) per row lane and channel; stats kernel: half of it
+  size_t r = (size_t)TY * CW;
   if (r < 1024) r = 1024;
   if (r < (size_t)16 * 3 * slots) r = (size_t)16 * 3 * slots;
   return r;
