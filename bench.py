@@ -422,8 +422,9 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
             runs = [_time_graph(g_step, barrier) for _ in range(kReplays)]
             total = statistics.median(r[0] for r in runs)
             wall = (runs[0][1][0], runs[-1][1][1])
-            fwd_t = _time_graph(g_fwd, barrier)[0] / steps
-            bwd_t = _time_graph(g_bwd, barrier)[0] / steps if g_bwd is not None else 0.0
+            fwd_t = statistics.median(_time_graph(g_fwd, barrier)[0] for _ in range(kReplays)) / steps
+            bwd_t = (statistics.median(_time_graph(g_bwd, barrier)[0] for _ in range(kReplays)) / steps
+                     if g_bwd is not None else 0.0)
             return reduce_max(total / steps), fwd_t, bwd_t, wall, "cuda-graph"
         except Exception as exc:  # pragma: no cover - depends on driver / NCCL capture support
             sys.stderr.write("bench: CUDA-graph capture failed (%s); timing the eager loop\n" % str(exc)[:200])
@@ -655,8 +656,8 @@ def _device_arm(args):
 # per-launch DRAM traffic in bytes (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture
 # summarised in profiles/fused_fwd_bwd_cfg4_bf16_gelu.md; keyed by (workload, ranks, direction)
 NCU_TRAFFIC = {
-    ("cfg4", 1, "forward"): 134464768 + 85502976,
-    ("cfg4", 1, "backward"): 268748288 + 106585344,
+    ("cfg4", 1, "forward"): 134569984 + 86704128,
+    ("cfg4", 1, "backward"): 269372928 + 109291008,
 }
 
 
