@@ -81,14 +81,26 @@ def describe_plan(N, R, C, G, dtype, direction):
 
 lib.gnb200_wait_timeouts.restype = ctypes.c_longlong
 lib.gnb200_wait_timeouts.argtypes = []
+lib.gnb200_clear_wait_timeouts.restype = ctypes.c_int
+lib.gnb200_clear_wait_timeouts.argtypes = []
+lib.gnb200_selftest_exchange_timeout.restype = ctypes.c_int
+lib.gnb200_selftest_exchange_timeout.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int64, _c_int64, _c_int64, _c_int64,
+                                                 ctypes.c_double, ctypes.c_int, ctypes.c_int, _c_void_p, _c_void_p,
+                                                 _c_void_p, _c_void_p]
+ERR_EXCHANGE_TIMEOUT = -5
 
 
 def wait_timeouts():
     """Exchange waits of the fused kernels that gave up on the current device (0 in a healthy run)."""
     v = lib.gnb200_wait_timeouts()
     if v < 0:
-        raise Gnb200Error(lib.gnb200_last_error().decode())
+        raise Gnb200Error(int(v), lib.gnb200_last_error().decode())
     return int(v)
+
+
+def clear_wait_timeouts():
+    """Resets the give-up count and re-arms the entry points after GNB200_ERR_EXCHANGE_TIMEOUT."""
+    check(lib.gnb200_clear_wait_timeouts())
 
 
 def launch_count(N, R, C, G, dtype, direction):

@@ -583,8 +583,10 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
     }
   }
   // every CTA of the cluster pushed its group sums into every inbox: no cluster barrier, no fence
-  mbar_wait_bounded(mbar, 0, g.wait_timeouts);
-  const float inv_m = 1.0f / ((float)g.D * (float)g.R);
+  // a wait that gives up yields NaN coefficients: the failure shows in dx (the channel sums in
+  // scratch, hence dgamma / dbeta, come from this CTA's own rows and stay valid)
+  const bool ok = mbar_wait_bounded(mbar, 0, g.wait);
+  const float inv_m = ok ? 1.0f / ((float)g.D * (float)g.R) : __int_as_float(0x7fc00000);
   for (int s = tid; s < n_slots; s += blockDim.x) {
     float a1 = 0.f, a2 = 0.f;
     for (unsigned q = 0; q < k; ++q) {
@@ -808,8 +810,9 @@ static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t st
   Geom g = p.geom;
   if (p.fused) {
     float* sums = reinterpret_cast<float*>(c.workspace);
-    cudaError_t werr = wait_timeout_counter(&g.wait_timeouts);
+    cudaError_t werr = wait_limit_for_device(&g.wait);
     if (werr != cudaSuccess) return werr;
+    g.skip_push_rank = -1;
     constexpr bool kCanShuf = UNI && VE >= 4;
     auto kern = p.threads <= 128 ? gn_bwd_fused_kernel<T, VE, ACT, UNI, 128, false>
                                  : gn_bwd_fused_kernel<T, VE, ACT, UNI, kMaxThreads, false>;

@@ -25,23 +25,59 @@ int fail(int code, const char* fmt, ...) {
 namespace gnb200 {
 __device__ unsigned int g_wait_timeouts = 0;
 
-cudaError_t wait_timeout_counter(unsigned int** counter) {
-  constexpr int kMaxDevices = 64;
-  static std::mutex mu;
-  static unsigned int* addr[kMaxDevices] = {};
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_wait_mu;
+unsigned int* g_counter_addr[kMaxDevices] = {};
+// One word per device in mapped pinned host memory: a kernel whose bounded wait gave up sets its
+// device's word, and the entry points read it on the host without synchronising.
+volatile unsigned int* g_host_mirror = nullptr;
+unsigned int* g_mirror_dev_addr[kMaxDevices] = {};
+}  // namespace
+
+cudaError_t wait_limit_for_device(WaitLimit* out) {
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
   if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!addr[dev]) {
+  std::lock_guard<std::mutex> lock(g_wait_mu);
+  if (!g_host_mirror) {
+    void* h = nullptr;
+    err = cudaHostAlloc(&h, kMaxDevices * sizeof(unsigned int), cudaHostAllocMapped | cudaHostAllocPortable);
+    if (err != cudaSuccess) return err;
+    memset(h, 0, kMaxDevices * sizeof(unsigned int));
+    g_host_mirror = static_cast<volatile unsigned int*>(h);
+  }
+  if (!g_counter_addr[dev]) {
     void* p = nullptr;
     err = cudaGetSymbolAddress(&p, g_wait_timeouts);
     if (err != cudaSuccess) return err;
-    addr[dev] = static_cast<unsigned int*>(p);
+    void* m = nullptr;
+    err = cudaHostGetDevicePointer(&m, const_cast<unsigned int*>(g_host_mirror) + dev, 0);
+    if (err != cudaSuccess) return err;
+    g_counter_addr[dev] = static_cast<unsigned int*>(p);
+    g_mirror_dev_addr[dev] = static_cast<unsigned int*>(m);
   }
-  *counter = addr[dev];
+  out->timeouts = g_counter_addr[dev];
+  out->host_mirror = g_mirror_dev_addr[dev];
+  out->clocks = 2000000000LL;  // about a second
+  out->polls = 1u << 16;
   return cudaSuccess;
+}
+
+// Non-zero once a kernel on the current device has recorded a wait that gave up (no synchronisation:
+// the kernel stores to mapped host memory).
+bool wait_gave_up_on_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+  const volatile unsigned int* m = g_host_mirror;
+  return m != nullptr && m[dev] != 0;
+}
+
+void clear_wait_mirror_on_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return;
+  if (g_host_mirror) g_host_mirror[dev] = 0;
 }
 
 // Same thread-local text as fail(), for entry points that live in other translation units.
@@ -69,6 +105,11 @@ int check_common(int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype)
   if (C % G != 0)
     return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200: num_channels %lld is not divisible by num_groups %lld",
                 (long long)C, (long long)G);
+  if (gnb200::wait_gave_up_on_current_device())
+    return fail(GNB200_ERR_EXCHANGE_TIMEOUT,
+                "gnb200: a kernel of an earlier call on this device gave up waiting for its peers; every result "
+                "since the last check is invalid (NaN where the wait was needed). gnb200_wait_timeouts() gives the "
+                "count, gnb200_clear_wait_timeouts() re-arms the library");
   return GNB200_OK;
 }
 
@@ -106,7 +147,8 @@ int gnb200_fwd(const void* x, const void* gamma, const void* beta, int64_t N, in
   if (!x || !gamma || !beta || !y || !mean || !rstd)
     return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200_fwd: null tensor pointer");
   gnb200::Plan plan;
-  const bool al = aligned16(x) && aligned16(y);
+  // the vector kernels read x, y, gamma and beta with 16-byte accesses: all four must be aligned
+  const bool al = aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
   if (!gnb200::make_plan(N, R, C, G, dtype, 0, al, &plan))
     return fail(GNB200_ERR_UNSUPPORTED, "gnb200_fwd: shape N=%lld R=%lld C=%lld G=%lld is outside the supported index range",
                 (long long)N, (long long)R, (long long)C, (long long)G);
@@ -128,7 +170,7 @@ int gnb200_bwd(const void* dy, const void* x, const void* gamma, const void* bet
   if (!dy || !x || !gamma || !beta || !mean || !rstd || !dx || !dgamma_dbeta_f32)
     return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200_bwd: null tensor pointer");
   gnb200::Plan plan;
-  const bool al = aligned16(x) && aligned16(dy) && aligned16(dx);
+  const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(gamma) && aligned16(beta);
   if (!gnb200::make_plan(N, R, C, G, dtype, 1, al, &plan))
     return fail(GNB200_ERR_UNSUPPORTED, "gnb200_bwd: shape N=%lld R=%lld C=%lld G=%lld is outside the supported index range",
                 (long long)N, (long long)R, (long long)C, (long long)G);
@@ -160,6 +202,39 @@ int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, 
     buf[buf_len - 1] = '\0';
   }
   return need;
+}
+
+int gnb200_clear_wait_timeouts(void) {
+  const unsigned int zero = 0;
+  const cudaError_t err = cudaMemcpyToSymbol(gnb200::g_wait_timeouts, &zero, sizeof(zero));
+  if (err != cudaSuccess) return fail(GNB200_ERR_CUDA, "gnb200_clear_wait_timeouts: CUDA error: %s", cudaGetErrorString(err));
+  gnb200::clear_wait_mirror_on_current_device();
+  return GNB200_OK;
+}
+
+int gnb200_selftest_exchange_timeout(const void* x, const void* gamma, const void* beta, int64_t N, int64_t R,
+                                     int64_t C, int64_t G, double eps, int act, int dtype, void* y, float* mean,
+                                     float* rstd, void* stream) {
+  int rc = check_common(N, R, C, G, act, dtype);
+  if (rc != GNB200_OK) return rc;
+  if (!x || !gamma || !beta || !y || !mean || !rstd)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200_selftest_exchange_timeout: null tensor pointer");
+  gnb200::Plan plan;
+  const bool al = aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
+  if (!gnb200::make_plan(N, R, C, G, dtype, 0, al, &plan) || !plan.fused || plan.geom.k < 2)
+    return fail(GNB200_ERR_UNSUPPORTED,
+                "gnb200_selftest_exchange_timeout: the problem must take the fused forward plan with a cluster of at "
+                "least two CTAs");
+  gnb200::FwdCall call = {x, gamma, beta, y, mean, rstd, nullptr, (float)eps, act, dtype};
+  call.test_skip_push_rank = 1;
+  call.test_wait_clocks = 2000000;  // about a millisecond
+  const cudaError_t err = gnb200::launch_forward(call, plan, reinterpret_cast<cudaStream_t>(stream));
+  if (err == cudaErrorInvalidConfiguration)
+    return fail(GNB200_ERR_UNSUPPORTED,
+                "gnb200_selftest_exchange_timeout: the problem has more (sample, column block) slabs than clusters are "
+                "resident; use a smaller batch");
+  if (err != cudaSuccess) return fail(GNB200_ERR_CUDA, "gnb200_selftest_exchange_timeout: CUDA error: %s", cudaGetErrorString(err));
+  return GNB200_OK;
 }
 
 long long gnb200_wait_timeouts(void) {

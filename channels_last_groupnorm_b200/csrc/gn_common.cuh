@@ -475,8 +475,10 @@ __device__ __forceinline__ __half2 act_grad_h2(__half2 v) {
     __half2 u, du;
     gelu_poly_h2<ACT>(v, u, du, true);
     const __half2 t = tanh_h2(u);
-    // Phi + v * Phi' with Phi' = 0.5 (1 - t^2) u'
-    return __hfma2(__hmul2(__hmul2(v, half_), du), __hfma2(__hneg2(t), t, one), __hfma2(half_, t, half_));
+    // Phi + v * Phi' with Phi' = 0.5 (1 - t^2) u'.  The factor (1 - t^2) is applied before u': for
+    // |v| beyond a few tens it is exactly 0, so the product cannot overflow to inf (and inf * 0 = NaN)
+    // when v * u' exceeds the half-precision range (|v| above about 1.7e4).
+    return __hfma2(__hmul2(__hmul2(v, half_), __hfma2(__hneg2(t), t, one)), du, __hfma2(half_, t, half_));
   }
 }
 
@@ -573,18 +575,39 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
-// Waits for the phase with the given parity, at most about a second; a wait that gives up is
-// counted in *timeouts (read by gnb200_wait_timeouts) and the caller carries on, with values that
-// are then meaningless.
-__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned int* timeouts) {
-  if (mbar_try_wait(bar, parity)) return;
+// Where a wait that gave up is recorded: a device counter (read by gnb200_wait_timeouts) and a
+// word of mapped pinned host memory that the entry points look at, without synchronising, before
+// they launch anything.
+struct WaitLimit {
+  unsigned int* timeouts;      // device counter of waits that gave up
+  unsigned int* host_mirror;   // mapped host word, set non-zero together with the counter
+  long long clocks;            // give up after this many SM clocks ...
+  unsigned int polls;          // ... and at least this many failed polls (a context that was switched
+                               // out lets the clock run on, but polls only count while it executes)
+};
+__device__ __forceinline__ void wait_gave_up(const WaitLimit& lim) {
+  atomicAdd(lim.timeouts, 1u);
+  *reinterpret_cast<volatile unsigned int*>(lim.host_mirror) = 1u;
+  __threadfence_system();
+}
+// Waits for the phase with the given parity.  Returns false if the wait gave up (both limits of
+// `lim` exceeded); the give-up is recorded and the caller must treat what it waited for as missing.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, const WaitLimit& lim) {
+  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  unsigned int polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > 2000000000LL) {
-      atomicAdd(timeouts, 1u);
-      return;
+    ++polls;
+    if (polls > lim.polls && clock64() - t0 > lim.clocks) {
+      wait_gave_up(lim);
+      return false;
     }
   }
+  return true;
+}
+// announces `bytes` more st.async bytes on the current phase without arriving
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
 // 16 bytes into the shared memory of CTA `rank` at the offset of `local_dst`, counted on that
 // CTA's mbarrier at the offset of `local_bar`
@@ -625,7 +648,8 @@ struct Geom {
   int shuf, tps_shift;
   int red_floats;  // size of the reduction scratch `red`, set by the planner
   int wsum_stride, wpart_off;  // shuffle reductions: second warp-sum buffer and (backward) per-warp channel sums in `red`, in floats
-  unsigned int* wait_timeouts;  // device counter of exchange waits that gave up (set by the launcher)
+  WaitLimit wait;  // limits and give-up record of the bounded waits (set by the launcher)
+  int skip_push_rank;  // -1; the exchange self-test names a cluster rank that withholds its pushes
   int persist;     // fused forward: the grid holds the resident clusters only, each looping over items
 };
 

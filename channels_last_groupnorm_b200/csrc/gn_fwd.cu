@@ -486,7 +486,13 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
   // Inbox barriers: one arrival (thread 0, which also announces the bytes) per use.  Every CTA of
   // the cluster must have initialised them before a peer pushes to them: the cluster barrier that
   // guarantees this is entered here and left just before this CTA's first push.
+  // Set by thread 0 when its wait for an exchange gave up.  From then on the CTA is `dead`: it
+  // keeps pushing its contributions (its peers' waits must end) but no longer arrives or waits on
+  // its own barriers, whose phase may never complete - arriving again on such a barrier is
+  // undefined - and it writes NaN statistics, so every output of its remaining items is NaN.
+  __shared__ unsigned int s_dead;
   if (threadIdx.x == 0) {
+    s_dead = 0;
     mbar_init(mbar2, 1);
     mbar_init(mbar2 + 1, 1);
     fence_mbar_init_cluster();
@@ -513,7 +519,17 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
     }
     float* inbox = inbox2 + parity * 4 * k * g.slots;
     uint64_t* mbar = mbar2 + parity;
-    if (tid == 0) mbar_arrive_expect_tx(mbar, k * g.slots * 16);
+    // (thread 0 stored s_dead before the block barrier that ends the previous item)
+    const bool dead = !first && s_dead != 0;
+    if (tid == 0) {
+      // a dead CTA only balances the bytes its peers go on delivering, so that the barrier's
+      // transaction count stays bounded
+      if (!dead)
+        mbar_arrive_expect_tx(mbar, k * g.slots * 16);
+      else
+        mbar_expect_tx(mbar, k * g.slots * 16);
+    }
+    const bool pushing = (int)rank != g.skip_push_rank;
     float mean[VE], m2[VE], cnt = 0.f;
 #pragma unroll
     for (int e = 0; e < VE; ++e) mean[e] = 0.f, m2[e] = 0.f;
@@ -538,14 +554,14 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
         acc += m2[e];
       }
       const float m2loc = cta_slot_sum_shuf(g, fmaf(cnt, dev, acc), tx, red + g.wsum_stride);
-      if (tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
+      if (pushing && tid < g.CV && (tid & ((1 << g.tps_shift) - 1)) == 0) {
         const int s = tid >> g.tps_shift;
         for (unsigned q = 0; q < k; ++q) st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, q, lm, m2loc, n_loc, 0.f);
       }
     } else {
       cta_slot_moments<VE, UNI>(g, mean, m2, cnt, tx, ty, c0, nrows, g_lo, n_slots, red, tmp, slot);
       __syncthreads();
-      for (int s = tid; s < g.slots; s += blockDim.x) {
+      for (int s = tid; pushing && s < g.slots; s += blockDim.x) {
         const bool live = s < n_slots;
         const float a = live ? slot[s] : 0.f, b = live ? slot[g.slots + s] : 0.f, c = live ? slot[2 * g.slots + s] : 0.f;
         for (unsigned q = 0; q < k; ++q) st_async_f32x4(inbox + 4 * (rank * g.slots + s), mbar, q, a, b, c, 0.f);
@@ -555,8 +571,11 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
       // Every CTA of the cluster pushed (mean, M2, count) of each slot into every inbox.  Combine them
       // in rank order (every CTA gets bit-identical statistics):
       //   mean = sum n_q mean_q / sum n_q,  M2 = sum M2_q + n_q (mean_q - mean)^2
-      mbar_wait_bounded(mbar, (uses >> 1) & 1u, g.wait_timeouts);
+      // A wait that gives up (or a dead CTA) yields NaN statistics: the failure is visible in y,
+      // mean and rstd, and the entry points report it from the next call on.
+      const bool ok = !dead && mbar_wait_bounded(mbar, (uses >> 1) & 1u, g.wait);
       ++uses;
+      if (tid == 0 && !ok) s_dead = 1;
       for (int s = tid; s < n_slots; s += blockDim.x) {
         float wsum = 0.f, ntot = 0.f;
         for (unsigned q = 0; q < k; ++q) {
@@ -564,14 +583,14 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
           wsum = fmaf(v.z, v.x, wsum);
           ntot += v.z;
         }
-        const float mu = wsum / ntot;
+        const float mu = ok ? wsum / ntot : __int_as_float(0x7fc00000);
         float m2tot = 0.f;
         for (unsigned q = 0; q < k; ++q) {
           const float4 v = *reinterpret_cast<const float4*>(inbox + 4 * (q * g.slots + s));
           const float d = v.x - mu;
           m2tot += fmaf(v.z * d, d, v.y);
         }
-        const float rs = rsqrtf(fmaxf(m2tot / ntot, 0.f) + eps);
+        const float rs = ok ? rsqrtf(fmaxf(m2tot / ntot, 0.f) + eps) : __int_as_float(0x7fc00000);
         stat[s] = mu;
         stat[g.slots + s] = rs;
         if (rank == 0) {
@@ -737,8 +756,15 @@ static cudaError_t launch_fused(const FwdCall& c, const Plan& p, cudaStream_t st
     cfg.gridDim.x = (unsigned)clusters * (unsigned)p.geom.k;
   }
   Geom g = p.geom;
-  err = wait_timeout_counter(&g.wait_timeouts);
+  err = wait_limit_for_device(&g.wait);
   if (err != cudaSuccess) return err;
+  g.skip_push_rank = c.test_skip_push_rank;
+  if (c.test_wait_clocks > 0) {
+    g.wait.clocks = c.test_wait_clocks;
+    g.wait.polls = 64;
+  }
+  // the exchange self-test wants one item per cluster, so that no barrier is used twice
+  if (c.test_skip_push_rank >= 0 && (long long)g.N * g.ncb * g.k > (long long)cfg.gridDim.x) return cudaErrorInvalidConfiguration;
   return cudaLaunchKernelEx(&cfg, kern, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, (T*)c.y, c.mean, c.rstd,
                             c.eps, g);
 }

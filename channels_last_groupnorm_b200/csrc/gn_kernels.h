@@ -30,6 +30,10 @@ struct FwdCall {
   float eps;
   int act;
   int dtype;
+  // exchange self-test only (gnb200_selftest_exchange_timeout): the cluster rank that withholds
+  // its pushes (-1: none) and the give-up limit of the waits in SM clocks (0: the default)
+  int test_skip_push_rank = -1;
+  long long test_wait_clocks = 0;
 };
 
 struct BwdCall {
@@ -63,8 +67,12 @@ cudaError_t ensure_kernel_attributes(const void* func, size_t smem_bytes, bool n
 // can be resident on the current device at once (>= 1), cached per device, kernel and shape.
 cudaError_t resident_clusters(const void* func, const cudaLaunchConfig_t* cfg, int* clusters);
 
-// Device address of the counter of exchange waits that gave up, on the current device.
-cudaError_t wait_timeout_counter(unsigned int** counter);
+// Limits and give-up record of the kernels' bounded waits on the current device (device counter,
+// mapped host word, default limits).  The first call in a process allocates the host words.
+cudaError_t wait_limit_for_device(WaitLimit* out);
+// True once a kernel on the current device has recorded a wait that gave up; no synchronisation.
+bool wait_gave_up_on_current_device();
+void clear_wait_mirror_on_current_device();
 
 cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream);
 cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream);

@@ -115,6 +115,7 @@ bool shuffle_geometry(int D, int ve, int CV, int* tps_shift) {
 void fill_divisors(Geom* g, int ve, int direction, int threads, bool fused) {
   g->shuf = 0;
   g->tps_shift = 0;
+  g->skip_push_rank = -1;
   int tps_shift = 0;
   if (fused && shuffle_geometry(g->D, ve, g->CV, &tps_shift)) {
     g->shuf = 1;

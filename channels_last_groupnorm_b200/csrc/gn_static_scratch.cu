@@ -79,8 +79,12 @@ extern "C" int gnb200_bwd_static_scratch(const void* dy, const void* x, const vo
                                 (long long)N, (long long)R, (long long)C, (long long)G);
   if (!dy || !x || !gamma || !beta || !mean || !rstd || !dx || !dgamma_dbeta_f32)
     return gnb200::report_error(GNB200_ERR_INVALID_ARGUMENT, "gnb200_bwd_static_scratch: null tensor pointer");
+  if (gnb200::wait_gave_up_on_current_device())
+    return gnb200::report_error(GNB200_ERR_EXCHANGE_TIMEOUT,
+                                "gnb200_bwd_static_scratch: a kernel of an earlier call on this device gave up waiting "
+                                "for its peers; see gnb200_wait_timeouts() / gnb200_clear_wait_timeouts()");
   gnb200::Plan plan;
-  const bool al = is_aligned16(x) && is_aligned16(dy) && is_aligned16(dx);
+  const bool al = is_aligned16(x) && is_aligned16(dy) && is_aligned16(dx) && is_aligned16(gamma) && is_aligned16(beta);
   if (!gnb200::make_plan(N, R, C, G, dtype, 1, al, &plan))
     return gnb200::report_error(GNB200_ERR_UNSUPPORTED,
                                 "gnb200_bwd_static_scratch: shape N=%lld R=%lld C=%lld G=%lld is outside the supported "

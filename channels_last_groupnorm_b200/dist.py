@@ -31,11 +31,30 @@ def shard_batch(t: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
     return t[lo:hi]
 
 
+# (process group, num_channels) pairs whose ranks have been found to agree
+_AGREED = set()
+
+
+def _check_channels_once(num_channels: int, group, world: int):
+    """Host-side check that every rank of `group` brings the same number of channels, done the
+    first time a (group, num_channels) pair is seen: a mismatch raises on all ranks instead of
+    hanging or corrupting the reduction.  Later calls with the same pair skip the (pickled,
+    host-synchronising) exchange; the all-reduce itself costs microseconds."""
+    key = (id(group) if group is not None else None, int(num_channels))
+    if key in _AGREED:
+        return
+    sizes = [None] * world
+    dist.all_gather_object(sizes, int(num_channels), group=group)
+    if len(set(sizes)) != 1:
+        raise RuntimeError("allreduce_param_grads: ranks disagree on num_channels: %s" % sizes)
+    _AGREED.add(key)
+
+
 def allreduce_param_grads(dparam_f32: torch.Tensor, group=None) -> torch.Tensor:
     """Sums the packed fp32 [2, C] parameter-gradient buffer over the ranks of `group`, in place.
 
-    Checks on the host that every rank brings the same number of channels before the collective
-    is issued, so a mismatch raises on all ranks instead of hanging the reduction.
+    The first call for a (group, C) pair checks on the host that all ranks agree on C before the
+    collective is issued.
     """
     if dparam_f32.dtype != torch.float32 or dparam_f32.ndim != 2 or dparam_f32.shape[0] != 2:
         raise ValueError("allreduce_param_grads: expected a float32 [2, C] tensor, got %s %s"
@@ -45,9 +64,6 @@ def allreduce_param_grads(dparam_f32: torch.Tensor, group=None) -> torch.Tensor:
     world = dist.get_world_size(group)
     if world == 1:
         return dparam_f32
-    sizes = [None] * world
-    dist.all_gather_object(sizes, int(dparam_f32.shape[1]), group=group)
-    if len(set(sizes)) != 1:
-        raise RuntimeError("allreduce_param_grads: ranks disagree on num_channels: %s" % sizes)
+    _check_channels_once(dparam_f32.shape[1], group, world)
     dist.all_reduce(dparam_f32, op=dist.ReduceOp.SUM, group=group)
     return dparam_f32

@@ -24,6 +24,7 @@ import torch
 import torch.nn as nn
 
 from . import _native  # noqa: F401  (loads the libraries; raises if they are missing)
+from . import dist as _dist
 
 ACTIVATION_CODES = {
     "identity": 0,
@@ -88,7 +89,7 @@ class GN_NHWC_Func(torch.autograd.Function):
         else:
             dx, dparam = torch.ops.gnb200.bwd_f32(dy_flat, X_flat, weight, bias, means, rstds, ctx.G, ctx.activation)
             if ctx.process_group is not None:
-                torch.distributed.all_reduce(dparam, op=torch.distributed.ReduceOp.SUM, group=ctx.process_group)
+                _dist.allreduce_param_grads(dparam, ctx.process_group)
             dgamma, dbeta = dparam[0].to(w_dtype), dparam[1].to(b_dtype)
         return _restore_shape(dx, ctx.x_shape), dgamma, dbeta, None, None, None, None
 

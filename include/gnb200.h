@@ -59,7 +59,9 @@ enum {
   GNB200_ERR_INVALID_ARGUMENT = -1, /* null pointer, bad dtype/activation, C % G != 0, sizes <= 0 ... */
   GNB200_ERR_WORKSPACE = -2,        /* workspace missing or smaller than gnb200_*_workspace_bytes() */
   GNB200_ERR_CUDA = -3,             /* a CUDA runtime call or kernel launch failed */
-  GNB200_ERR_UNSUPPORTED = -4       /* shape outside the supported index range */
+  GNB200_ERR_UNSUPPORTED = -4,      /* shape outside the supported index range */
+  GNB200_ERR_EXCHANGE_TIMEOUT = -5  /* a kernel of an EARLIER call on this device gave up a bounded wait: every
+                                       result since the last check is invalid; see gnb200_wait_timeouts() */
 };
 
 /* Library version, e.g. 100 = 0.1.0 */
@@ -132,13 +134,39 @@ int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, 
                          char* buf, int buf_len);
 
 /*
- * Diagnostics.  The fused kernels exchange statistics between the CTAs of a cluster through
- * shared-memory mailboxes; a CTA waits for its peers at most about a second and then carries on
- * with meaningless values instead of hanging the GPU.  This returns how many such waits have given
- * up on the current device since the library was loaded (0 in any healthy run; negative = error).
- * Synchronises with the device.  No counterpart in the reference.
+ * Diagnostics.  The kernels wait for one another in a few places (the CTAs of a cluster exchange
+ * statistics through shared-memory mailboxes; the persistent multi-pass kernels wait for the CTA
+ * that merges a slab's partial sums).  Every such wait is bounded (about a second of SM clocks
+ * and tens of thousands of polls): a wait that gives up is counted, the statistics or
+ * coefficients it was waiting for become NaN - so y, mean, rstd or dx of the affected slabs are
+ * NaN, never plausible-looking numbers - and the kernel runs to its end instead of hanging the
+ * GPU.  The kernel also sets a word of mapped host memory, which gnb200_fwd / gnb200_bwd /
+ * gnb200_bwd_static_scratch read without synchronising: from the next call on they launch nothing and
+ * return GNB200_ERR_EXCHANGE_TIMEOUT until gnb200_clear_wait_timeouts() is called.
+ * No counterpart in the reference (its kernels never wait for one another).
+ *
+ * gnb200_wait_timeouts        number of waits that gave up on the current device since the library
+ *                             was loaded or cleared (0 in any healthy run; negative = error).
+ *                             Synchronises with the device.
+ * gnb200_clear_wait_timeouts  resets the count and re-arms the entry points.  Synchronises.
  */
 long long gnb200_wait_timeouts(void);
+int gnb200_clear_wait_timeouts(void);
+
+/*
+ * Self-test of the give-up path, for test suites only.  Runs the fused forward plan on the given
+ * problem with a wait limit of about a millisecond while cluster rank 1 of every cluster withholds
+ * its contribution to the exchange (decided on the host; nothing faults, traps or hangs: every CTA
+ * pushes before it waits, every wait runs out, every CTA exits).  Afterwards y, mean and rstd are
+ * NaN, gnb200_wait_timeouts() is positive and the other entry points return
+ * GNB200_ERR_EXCHANGE_TIMEOUT until gnb200_clear_wait_timeouts().  The problem must take the fused
+ * forward plan with a cluster of at least two CTAs and have no more (sample, column block) slabs
+ * than clusters are resident at once (GNB200_ERR_UNSUPPORTED otherwise).
+ * No counterpart in the reference.
+ */
+int gnb200_selftest_exchange_timeout(const void* x, const void* gamma, const void* beta,
+                                     int64_t N, int64_t R, int64_t C, int64_t G, double eps, int act, int dtype,
+                                     void* y, float* mean, float* rstd, void* stream);
 
 /* Number of kernel launches gnb200_fwd / gnb200_bwd enqueue for this problem. */
 int gnb200_launch_count(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction);

@@ -36,7 +36,12 @@ def _worker(rank, world, port, scenario, ret):
             xs, dys = gd.shard_batch(x, rank, world), gd.shard_batch(dy, rank, world)
             local = O.oracle_c(xs, ga, be, dys, G, 1e-5, act)
             packed = torch.stack([local["dgamma"], local["dbeta"]]).float()
+            again = packed.clone()
             gd.allreduce_param_grads(packed)
+            # the ranks' agreement on C is checked once per (group, C); the second call skips it
+            assert len(gd._AGREED) == 1
+            gd.allreduce_param_grads(again)
+            assert len(gd._AGREED) == 1 and torch.equal(again, packed)
             full = O.oracle_c(x, ga, be, dy, G, 1e-5, act)
             ok = (O.rel_err(packed[0], full["dgamma"]) < 1e-5 and O.rel_err(packed[1], full["dbeta"]) < 1e-5
                   and O.rel_err(local["dx"], gd.shard_batch(full["dx"], rank, world)) < 1e-12

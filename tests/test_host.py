@@ -41,9 +41,23 @@ def test_activation_codes_match_reference_table():
     assert nt.lib.gnb200_act_code(b"mish") == -1
 
 
+_KEEP = []
+
+
+def _buffer(nbytes):
+    """A pointer for arguments that a refused call never dereferences.  With a GPU present it is a
+    real device buffer of the stated size, so that a regression of the checks under test could not
+    turn into a stray access; without one (the CPU test pass) nothing can be launched anyway."""
+    if torch.cuda.is_available():
+        t = torch.zeros(max(int(nbytes), 16), dtype=torch.uint8, device="cuda")
+        _KEEP.append(t)
+        return ctypes.c_void_p(t.data_ptr())
+    return ctypes.c_void_p(16)
+
+
 def test_invalid_arguments_are_rejected_before_any_cuda_call():
     f = nt.lib.gnb200_fwd
-    one = ctypes.c_void_p(16)  # never dereferenced: validation fails first
+    one = _buffer(4096)  # validation fails before anything is launched
     assert f(one, one, one, 2, 4, 6, 4, 1e-5, 0, 0, one, one, one, None, 0, None) == -1  # C % G != 0
     assert "divisible" in nt.lib.gnb200_last_error().decode()
     assert f(one, one, one, 2, 4, 8, 4, 1e-5, 9, 0, one, one, one, None, 0, None) == -1  # bad activation
@@ -61,8 +75,9 @@ def test_workspace_is_required_when_the_plan_needs_one():
     N, R, C, G = 1, 1 << 20, 128, 32
     need = nt.lib.gnb200_fwd_workspace_bytes(N, R, C, G, 1)
     assert need > 0
-    one = ctypes.c_void_p(16)
+    one = _buffer(N * R * C * 2)
     rc = nt.lib.gnb200_fwd(one, one, one, N, R, C, G, 1e-5, 2, 1, one, one, one, None, 0, None)
+    _KEEP.clear()
     assert rc == -2 and "workspace" in nt.lib.gnb200_last_error().decode()
 
 

@@ -5,8 +5,6 @@ scratch from the caller, call after call, because all calls share one built-in s
 
 Collected last on purpose: a run that stops at the first failure has then already run every other test.
 """
-import ctypes
-
 import pytest
 import torch
 
@@ -59,8 +57,20 @@ def test_static_scratch_rejects_problems_beyond_its_array():
 
     N, R, C, G = 8192, 64, 256, 32  # the plan keeps 2 * N * C floats = 16 MiB of channel sums
     assert nt.lib.gnb200_bwd_workspace_bytes(N, R, C, G, 2) > nt.STATIC_SCRATCH_BYTES
-    one = ctypes.c_void_p(256)  # never dereferenced: the size check comes before any launch
-    rc = nt.lib.gnb200_bwd_static_scratch(one, one, one, one, one, one, N, R, C, G, 0, 2, one, one, None, None, None)
+    # real buffers of the stated sizes (268 MB per tensor): the call must refuse before it launches,
+    # but if that check ever regressed the kernels would still only touch memory they may touch
+    x = torch.zeros((N, R, C), dtype=torch.bfloat16, device="cuda")
+    dy = torch.zeros_like(x)
+    dx = torch.empty_like(x)
+    ga = torch.ones(C, dtype=torch.bfloat16, device="cuda")
+    be = torch.zeros(C, dtype=torch.bfloat16, device="cuda")
+    mean = torch.zeros((N, G), device="cuda")
+    rstd = torch.ones((N, G), device="cuda")
+    dparam = torch.empty((2, C), device="cuda")
+    rc = nt.lib.gnb200_bwd_static_scratch(dy.data_ptr(), x.data_ptr(), ga.data_ptr(), be.data_ptr(), mean.data_ptr(),
+                                          rstd.data_ptr(), N, R, C, G, 0, 2, dx.data_ptr(), dparam.data_ptr(), None,
+                                          None, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
     assert rc == -2
     msg = nt.lib.gnb200_last_error().decode()
     assert "scratch" in msg and str(nt.STATIC_SCRATCH_BYTES) in msg
