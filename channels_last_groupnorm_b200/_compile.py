@@ -9,26 +9,33 @@ and strides without running a kernel, and `torch.ops.gnb200.fwd` is differentiab
 import torch
 
 
-def _nhwc_like(X):
+def _like(X):
+    """Same sizes and storage order as X (channels-last or channels-first)."""
     n, c, r = X.shape
-    return X.new_empty((n, r, c)).permute(0, 2, 1)
+    if X.stride(1) == 1 or c == 1:
+        return X.new_empty((n, r, c)).permute(0, 2, 1)
+    return X.new_empty((n, c, r))
+
+
+def _stats_dtype(X):
+    return torch.float64 if X.dtype == torch.float64 else torch.float32
 
 
 @torch.library.register_fake("gnb200::fwd")
 def _fwd_fake(X, weight, bias, G, eps, act):
     n = X.shape[0]
-    stats = X.new_empty((n, G), dtype=torch.float32)
-    return _nhwc_like(X), stats, torch.empty_like(stats)
+    stats = X.new_empty((n, G), dtype=_stats_dtype(X))
+    return _like(X), stats, torch.empty_like(stats)
 
 
 @torch.library.register_fake("gnb200::bwd")
 def _bwd_fake(dy, X, weight, bias, means, rstds, G, act):
-    return _nhwc_like(X), torch.empty_like(weight), torch.empty_like(bias)
+    return _like(X), torch.empty_like(weight), torch.empty_like(bias)
 
 
 @torch.library.register_fake("gnb200::bwd_f32")
 def _bwd_f32_fake(dy, X, weight, bias, means, rstds, G, act):
-    return _nhwc_like(X), X.new_empty((2, X.shape[1]), dtype=torch.float32)
+    return _like(X), X.new_empty((2, X.shape[1]), dtype=_stats_dtype(X))
 
 
 def _fwd_setup_context(ctx, inputs, output):
@@ -41,8 +48,11 @@ def _fwd_setup_context(ctx, inputs, output):
 
 def _fwd_backward(ctx, dY, dmeans, drstds):
     X, weight, bias, means, rstds = ctx.saved_tensors
-    # the kernels want dy in the layout of X: (N, C, R) sizes over NHWC storage
-    dy = dY.permute(0, 2, 1).contiguous().permute(0, 2, 1)
+    # the kernels want dy in the storage order of X
+    if X.stride(1) == 1 or X.shape[1] == 1:
+        dy = dY.permute(0, 2, 1).contiguous().permute(0, 2, 1)
+    else:
+        dy = dY.contiguous()
     dx, dgamma, dbeta = torch.ops.gnb200.bwd(dy, X, weight, bias, means, rstds, ctx.G, ctx.act)
     return dx, dgamma, dbeta, None, None, None
 

@@ -52,6 +52,23 @@ lib.gnb200_bwd_static_scratch.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_vo
                                           _c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
                                           _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p]
 STATIC_SCRATCH_BYTES = 4 << 20
+for _name in ("gnb200_fwd_nchw_workspace_bytes", "gnb200_bwd_nchw_workspace_bytes"):
+    getattr(lib, _name).restype = ctypes.c_size_t
+    getattr(lib, _name).argtypes = [_c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int]
+lib.gnb200_fwd_nchw.restype = ctypes.c_int
+lib.gnb200_fwd_nchw.argtypes = lib.gnb200_fwd.argtypes
+lib.gnb200_bwd_nchw.restype = ctypes.c_int
+lib.gnb200_bwd_nchw.argtypes = lib.gnb200_bwd.argtypes
+lib.gnb200_bwd_f64_workspace_bytes.restype = ctypes.c_size_t
+lib.gnb200_bwd_f64_workspace_bytes.argtypes = [_c_int64, _c_int64, _c_int64, _c_int64]
+lib.gnb200_fwd_f64.restype = ctypes.c_int
+lib.gnb200_fwd_f64.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int64, _c_int64, _c_int64, _c_int64,
+                               ctypes.c_double, ctypes.c_int, ctypes.c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p]
+lib.gnb200_bwd_f64.restype = ctypes.c_int
+lib.gnb200_bwd_f64.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                               _c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
+                               _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_size_t, _c_void_p]
+LAYOUT_NHWC, LAYOUT_NCHW = 0, 1
 lib.gnb200_describe_plan.restype = ctypes.c_int
 lib.gnb200_describe_plan.argtypes = [_c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
                                      ctypes.c_char_p, ctypes.c_int]
@@ -161,3 +178,68 @@ def bwd_static_scratch_raw(dy_nhwc, x_nhwc, gamma, beta, mean, rstd, G, act, dx,
     check(lib.gnb200_bwd_static_scratch(_ptr(dy_nhwc), _ptr(x_nhwc), _ptr(gamma), _ptr(beta), _ptr(mean), _ptr(rstd),
                                         N, R, C, G, int(act), DTYPE_CODES[x_nhwc.dtype], _ptr(dx), _ptr(dparam),
                                         _ptr(dgamma), _ptr(dbeta), s))
+
+
+def fwd_nchw_raw(x_nchw, gamma, beta, G, eps, act, stream=None):
+    """Calls gnb200_fwd_nchw. x_nchw: contiguous (N, C, R) tensor. Returns (y, mean, rstd)."""
+    N, C, R = x_nchw.shape
+    code = DTYPE_CODES[x_nchw.dtype]
+    y = torch.empty_like(x_nchw)
+    mean = torch.empty((N, G), device=x_nchw.device, dtype=torch.float32)
+    rstd = torch.empty((N, G), device=x_nchw.device, dtype=torch.float32)
+    need = lib.gnb200_fwd_nchw_workspace_bytes(N, R, C, G, code)
+    ws = torch.empty(max(need, 16), device=x_nchw.device, dtype=torch.uint8)
+    s = torch.cuda.current_stream(x_nchw.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_fwd_nchw(_ptr(x_nchw), _ptr(gamma), _ptr(beta), N, R, C, G, float(eps), int(act), code,
+                              _ptr(y), _ptr(mean), _ptr(rstd), _ptr(ws), ws.numel(), s))
+    return y, mean, rstd
+
+
+def bwd_nchw_raw(dy_nchw, x_nchw, gamma, beta, mean, rstd, G, act, stream=None):
+    """Calls gnb200_bwd_nchw. Returns (dx, dparam_f32[2, C], dgamma, dbeta)."""
+    N, C, R = x_nchw.shape
+    code = DTYPE_CODES[x_nchw.dtype]
+    dx = torch.empty_like(x_nchw)
+    dparam = torch.empty((2, C), device=x_nchw.device, dtype=torch.float32)
+    dgamma = torch.empty(C, device=x_nchw.device, dtype=x_nchw.dtype)
+    dbeta = torch.empty(C, device=x_nchw.device, dtype=x_nchw.dtype)
+    need = lib.gnb200_bwd_nchw_workspace_bytes(N, R, C, G, code)
+    ws = torch.empty(max(need, 16), device=x_nchw.device, dtype=torch.uint8)
+    s = torch.cuda.current_stream(x_nchw.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_bwd_nchw(_ptr(dy_nchw), _ptr(x_nchw), _ptr(gamma), _ptr(beta), _ptr(mean), _ptr(rstd),
+                              N, R, C, G, int(act), code, _ptr(dx), _ptr(dparam), _ptr(dgamma), _ptr(dbeta),
+                              _ptr(ws), ws.numel(), s))
+    return dx, dparam, dgamma, dbeta
+
+
+def fwd_f64_raw(x, gamma, beta, G, eps, act, channels_last, stream=None):
+    """Calls gnb200_fwd_f64. x: contiguous (N, R, C) tensor if channels_last else contiguous (N, C, R)."""
+    if channels_last:
+        N, R, C = x.shape
+    else:
+        N, C, R = x.shape
+    y = torch.empty_like(x)
+    mean = torch.empty((N, G), device=x.device, dtype=torch.float64)
+    rstd = torch.empty((N, G), device=x.device, dtype=torch.float64)
+    s = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_fwd_f64(_ptr(x), _ptr(gamma), _ptr(beta), N, R, C, G, float(eps), int(act),
+                             LAYOUT_NHWC if channels_last else LAYOUT_NCHW, _ptr(y), _ptr(mean), _ptr(rstd), s))
+    return y, mean, rstd
+
+
+def bwd_f64_raw(dy, x, gamma, beta, mean, rstd, G, act, channels_last, stream=None):
+    """Calls gnb200_bwd_f64. Returns (dx, dgamma, dbeta), all float64."""
+    if channels_last:
+        N, R, C = x.shape
+    else:
+        N, C, R = x.shape
+    dx = torch.empty_like(x)
+    dgamma = torch.empty(C, device=x.device, dtype=torch.float64)
+    dbeta = torch.empty(C, device=x.device, dtype=torch.float64)
+    need = lib.gnb200_bwd_f64_workspace_bytes(N, R, C, G)
+    ws = torch.empty(max(need, 16), device=x.device, dtype=torch.uint8)
+    s = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_bwd_f64(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(mean), _ptr(rstd), N, R, C, G, int(act),
+                             LAYOUT_NHWC if channels_last else LAYOUT_NCHW, _ptr(dx), _ptr(dgamma), _ptr(dbeta),
+                             _ptr(ws), ws.numel(), s))
+    return dx, dgamma, dbeta

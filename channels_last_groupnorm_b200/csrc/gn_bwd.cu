@@ -21,106 +21,9 @@
 //
 // Every sum is formed in an order fixed by the launch geometry: no atomics, bit-identical reruns.
 #include "gn_kernels.h"
+#include "gn_math.cuh"
 
 namespace gnb200 {
-
-template <typename T, int VE>
-struct BwdLane {
-  float r[VE];    // rstd of the lane's group
-  float nmr[VE];  // -mean * rstd
-  float ga[VE];   // gamma
-  float be[VE];   // beta
-};
-
-// UNI: all VE channels of the thread belong to one group (one statistics lookup; the compiler
-// then keeps a single register for each of r / nmr).
-template <typename T, int VE, bool UNI>
-__device__ __forceinline__ void lane_setup(const T* gamma, const T* beta, const float* mean_n, const float* rstd_n,
-                                           int c_first, const FastDiv div_D, BwdLane<T, VE>& L) {
-  load_params<T, VE>(gamma, c_first, L.ga);
-  load_params<T, VE>(beta, c_first, L.be);
-  if constexpr (UNI) {
-    const int grp = div_D.div(c_first);
-    const float rs = rstd_n[grp];
-    const float nm = -mean_n[grp] * rs;
-#pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      L.r[e] = rs;
-      L.nmr[e] = nm;
-    }
-  } else {
-#pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const int grp = div_D.div(c_first + e);
-      const float rs = rstd_n[grp];
-      L.r[e] = rs;
-      L.nmr[e] = -mean_n[grp] * rs;
-    }
-  }
-}
-
-// One row of phase 1: dyh = dy * act'(yh) for the thread's VE channels, sums updated.
-template <typename T, int VE, int ACT>
-__device__ __forceinline__ void bwd_row_sums(const float (&fx)[VE], float (&fd)[VE], const BwdLane<T, VE>& L,
-                                             float (&s1)[VE], float (&s2)[VE]) {
-  float xh[VE], yh[VE], gr[VE];
-#pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    xh[e] = fmaf(fx[e], L.r[e], L.nmr[e]);
-    yh[e] = fmaf(xh[e], L.ga[e], L.be[e]);
-  }
-  act_grad_vec<T, VE, ACT>(yh, gr);
-#pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    fd[e] *= gr[e];
-    s1[e] += fd[e];
-    s2[e] = fmaf(fd[e], xh[e], s2[e]);
-  }
-}
-
-// 16-bit tensors, fused path: yh straight from x (a = rstd * gamma, b = beta - mean * a) and S2
-// accumulated against the raw x; the caller converts it with S2 = rstd * (S2raw - mean * S1).  One
-// FMA per element less; the conversion's rounding (relative 1e-7 * |mean| * rstd) is far below a
-// 16-bit result.
-// It works on the packed 16-bit values: dyh = dy * act'(yh) is formed two channels at a time in the tensor's own 16-bit format - which is
-// the format it is parked in anyway - and enters the fp32 sums through mixed-precision add / fma,
-// so dy is never unpacked and dyh never packed.  act' is evaluated in f16x2; for bf16 tensors it
-// is rounded to bf16 before the product.  Returns the packed dyh.
-template <typename T, int ACT>
-__device__ __forceinline__ uint4 bwd_row_sums_packed(const uint4& xw, const uint4& dw, const float (&a)[8],
-                                                     const float (&b)[8], float (&s1)[8], float (&s2)[8]) {
-  static_assert(sizeof(T) == 2, "16-bit tensors only");
-  const uint32_t xr[4] = {xw.x, xw.y, xw.z, xw.w}, dr[4] = {dw.x, dw.y, dw.z, dw.w};
-  uint32_t out[4];
-#pragma unroll
-  for (int p = 0; p < 4; ++p) {
-    uint16_t x0, x1;
-    split_halves(xr[p], x0, x1);
-    uint32_t dyh = dr[p];
-    if constexpr (ACT != kActIdentity) {
-      const float yh0 = fmaf(mixed_add<T>(x0, -0.0f), a[2 * p], b[2 * p]);
-      const float yh1 = fmaf(mixed_add<T>(x1, -0.0f), a[2 * p + 1], b[2 * p + 1]);
-      const __half2 g = act_grad_h2<ACT>(f32x2_to_h2_sat(yh0, yh1));
-      if constexpr (std::is_same<T, __half>::value) {
-        const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&dr[p]), g);
-        dyh = *reinterpret_cast<const uint32_t*>(&r);
-      } else {
-        const float2 gf = __half22float2(g);
-        const __nv_bfloat162 gb = __floats2bfloat162_rn(gf.x, gf.y);
-        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&dr[p]), gb);
-        dyh = *reinterpret_cast<const uint32_t*>(&r);
-      }
-    }
-    uint16_t d0, d1;
-    split_halves(dyh, d0, d1);
-    s1[2 * p] = mixed_add<T>(d0, s1[2 * p]);
-    s1[2 * p + 1] = mixed_add<T>(d1, s1[2 * p + 1]);
-    s2[2 * p] = mixed_fma<T>(d0, x0, s2[2 * p]);
-    s2[2 * p + 1] = mixed_fma<T>(d1, x1, s2[2 * p + 1]);
-    out[p] = dyh;
-  }
-  return make_uint4(out[0], out[1], out[2], out[3]);
-}
 
 constexpr int kRingDepth = 4;  // rows in flight per thread in the multi-kernel reduce kernel
 
@@ -886,7 +789,18 @@ static cudaError_t launch_bwd_ve(const BwdCall& c, const Plan& p, cudaStream_t s
   return p.ve == 1 ? launch_bwd_act<T, 1>(c, p, stream) : launch_bwd_act<T, VFULL>(c, p, stream);
 }
 
+cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, int C, cudaStream_t stream) {
+  Geom g = {};
+  g.C = C;
+  switch (c.dtype) {
+    case 0: return launch_param<float>(c, sums, rows, g, stream);
+    case 1: return launch_param<__half>(c, sums, rows, g, stream);
+    default: return launch_param<__nv_bfloat16>(c, sums, rows, g, stream);
+  }
+}
+
 cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream) {
+  if (p.wave) return launch_backward_wave(c, p, stream);
   switch (c.dtype) {
     case 0: return launch_bwd_ve<float>(c, p, stream);
     case 1: return launch_bwd_ve<__half>(c, p, stream);

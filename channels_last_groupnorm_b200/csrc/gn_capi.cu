@@ -1,6 +1,7 @@
 // extern "C" entry points of libgnb200.so (declared in include/gnb200.h).
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -62,6 +63,14 @@ cudaError_t wait_limit_for_device(WaitLimit* out) {
   out->host_mirror = g_mirror_dev_addr[dev];
   out->clocks = 2000000000LL;  // about a second
   out->polls = 1u << 16;
+  // GNB200_WAIT_CLOCKS: a shorter limit for bring-up of new kernels
+  if (const char* v = getenv("GNB200_WAIT_CLOCKS")) {
+    const long long c = atoll(v);
+    if (c > 0) {
+      out->clocks = c;
+      out->polls = 256;
+    }
+  }
   return cudaSuccess;
 }
 
@@ -157,7 +166,10 @@ int gnb200_fwd(const void* x, const void* gamma, const void* beta, int64_t N, in
                 plan.ws_bytes, workspace_bytes, workspace);
   gnb200::FwdCall call = {x, gamma, beta, y, mean, rstd, workspace, (float)eps, act, dtype};
   const cudaError_t err = gnb200::launch_forward(call, plan, reinterpret_cast<cudaStream_t>(stream));
-  if (err != cudaSuccess) return fail(GNB200_ERR_CUDA, "gnb200_fwd: CUDA error: %s", cudaGetErrorString(err));
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();  // a failed runtime call must not be reported again by a later, healthy call
+    return fail(GNB200_ERR_CUDA, "gnb200_fwd: CUDA error: %s", cudaGetErrorString(err));
+  }
   return GNB200_OK;
 }
 
@@ -179,7 +191,120 @@ int gnb200_bwd(const void* dy, const void* x, const void* gamma, const void* bet
                 plan.ws_bytes, workspace_bytes, workspace);
   gnb200::BwdCall call = {dy, x, gamma, beta, mean, rstd, dx, dgamma_dbeta_f32, dgamma, dbeta, workspace, act, dtype};
   const cudaError_t err = gnb200::launch_backward(call, plan, reinterpret_cast<cudaStream_t>(stream));
-  if (err != cudaSuccess) return fail(GNB200_ERR_CUDA, "gnb200_bwd: CUDA error: %s", cudaGetErrorString(err));
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(GNB200_ERR_CUDA, "gnb200_bwd: CUDA error: %s", cudaGetErrorString(err));
+  }
+  return GNB200_OK;
+}
+
+size_t gnb200_fwd_nchw_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype) {
+  return gnb200::nchw_workspace_bytes(N, R, C, G, dtype, 0);
+}
+
+size_t gnb200_bwd_nchw_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype) {
+  return gnb200::nchw_workspace_bytes(N, R, C, G, dtype, 1);
+}
+
+int gnb200_fwd_nchw(const void* x, const void* gamma, const void* beta, int64_t N, int64_t R, int64_t C, int64_t G,
+                    double eps, int act, int dtype, void* y, float* mean, float* rstd, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  int rc = check_common(N, R, C, G, act, dtype);
+  if (rc != GNB200_OK) return rc;
+  if (!x || !gamma || !beta || !y || !mean || !rstd)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200_fwd_nchw: null tensor pointer");
+  if (!gnb200::nchw_shape_supported(N, R, C, G))
+    return fail(GNB200_ERR_UNSUPPORTED, "gnb200_fwd_nchw: shape N=%lld R=%lld C=%lld G=%lld is outside the supported index range",
+                (long long)N, (long long)R, (long long)C, (long long)G);
+  const size_t need = gnb200::nchw_workspace_bytes(N, R, C, G, dtype, 0);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace))
+    return fail(GNB200_ERR_WORKSPACE, "gnb200_fwd_nchw: needs a 16-byte aligned workspace of %zu bytes, got %zu at %p", need,
+                workspace_bytes, workspace);
+  gnb200::FwdCall call = {x, gamma, beta, y, mean, rstd, workspace, (float)eps, act, dtype};
+  const cudaError_t err = gnb200::launch_forward_nchw(call, N, R, C, G, reinterpret_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(GNB200_ERR_CUDA, "gnb200_fwd_nchw: CUDA error: %s", cudaGetErrorString(err));
+  }
+  return GNB200_OK;
+}
+
+int gnb200_bwd_nchw(const void* dy, const void* x, const void* gamma, const void* beta, const float* mean,
+                    const float* rstd, int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype, void* dx,
+                    float* dgamma_dbeta_f32, void* dgamma, void* dbeta, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  int rc = check_common(N, R, C, G, act, dtype);
+  if (rc != GNB200_OK) return rc;
+  if (!dy || !x || !gamma || !beta || !mean || !rstd || !dx || !dgamma_dbeta_f32)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200_bwd_nchw: null tensor pointer");
+  if (!gnb200::nchw_shape_supported(N, R, C, G))
+    return fail(GNB200_ERR_UNSUPPORTED, "gnb200_bwd_nchw: shape N=%lld R=%lld C=%lld G=%lld is outside the supported index range",
+                (long long)N, (long long)R, (long long)C, (long long)G);
+  const size_t need = gnb200::nchw_workspace_bytes(N, R, C, G, dtype, 1);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace))
+    return fail(GNB200_ERR_WORKSPACE, "gnb200_bwd_nchw: needs a 16-byte aligned workspace of %zu bytes, got %zu at %p", need,
+                workspace_bytes, workspace);
+  gnb200::BwdCall call = {dy, x, gamma, beta, mean, rstd, dx, dgamma_dbeta_f32, dgamma, dbeta, workspace, act, dtype};
+  const cudaError_t err = gnb200::launch_backward_nchw(call, N, R, C, G, reinterpret_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(GNB200_ERR_CUDA, "gnb200_bwd_nchw: CUDA error: %s", cudaGetErrorString(err));
+  }
+  return GNB200_OK;
+}
+
+static int check_f64(int64_t N, int64_t R, int64_t C, int64_t G, int act, int layout, const char* who) {
+  if (act < GNB200_ACT_IDENTITY || act > GNB200_ACT_GELU_TANH)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: unknown activation code %d (valid: 0..4)", who, act);
+  if (layout != GNB200_LAYOUT_NHWC && layout != GNB200_LAYOUT_NCHW)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: unknown layout code %d (0 = NHWC, 1 = NCHW)", who, layout);
+  if (N < 1 || R < 1 || C < 1 || G < 1 || C % G != 0)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: need positive N, R, C, G with C divisible by G (got N=%lld R=%lld C=%lld G=%lld)",
+                who, (long long)N, (long long)R, (long long)C, (long long)G);
+  if (N * G > 0x7fffffffLL || (double)N * (double)R * (double)C > 9.0e15)
+    return fail(GNB200_ERR_UNSUPPORTED, "%s: shape is outside the supported index range", who);
+  return GNB200_OK;
+}
+
+size_t gnb200_bwd_f64_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G) {
+  (void)R;
+  (void)G;
+  return N > 0 && C > 0 ? (size_t)N * (size_t)C * 2 * sizeof(double) : 0;
+}
+
+int gnb200_fwd_f64(const double* x, const double* gamma, const double* beta, int64_t N, int64_t R, int64_t C,
+                   int64_t G, double eps, int act, int layout, double* y, double* mean, double* rstd, void* stream) {
+  int rc = check_f64(N, R, C, G, act, layout, "gnb200_fwd_f64");
+  if (rc != GNB200_OK) return rc;
+  if (!x || !gamma || !beta || !y || !mean || !rstd)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200_fwd_f64: null tensor pointer");
+  const cudaError_t err = gnb200::launch_forward_f64(x, gamma, beta, N, R, C, G, eps, act, layout == GNB200_LAYOUT_NHWC, y,
+                                                     mean, rstd, reinterpret_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(GNB200_ERR_CUDA, "gnb200_fwd_f64: CUDA error: %s", cudaGetErrorString(err));
+  }
+  return GNB200_OK;
+}
+
+int gnb200_bwd_f64(const double* dy, const double* x, const double* gamma, const double* beta, const double* mean,
+                   const double* rstd, int64_t N, int64_t R, int64_t C, int64_t G, int act, int layout, double* dx,
+                   double* dgamma, double* dbeta, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_f64(N, R, C, G, act, layout, "gnb200_bwd_f64");
+  if (rc != GNB200_OK) return rc;
+  if (!dy || !x || !gamma || !beta || !mean || !rstd || !dx || !dgamma || !dbeta)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200_bwd_f64: null tensor pointer");
+  const size_t need = gnb200_bwd_f64_workspace_bytes(N, R, C, G);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace))
+    return fail(GNB200_ERR_WORKSPACE, "gnb200_bwd_f64: needs a 16-byte aligned workspace of %zu bytes, got %zu at %p", need,
+                workspace_bytes, workspace);
+  const cudaError_t err =
+      gnb200::launch_backward_f64(dy, x, gamma, beta, mean, rstd, N, R, C, G, act, layout == GNB200_LAYOUT_NHWC, dx, dgamma,
+                                  dbeta, static_cast<double*>(workspace), reinterpret_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(GNB200_ERR_CUDA, "gnb200_bwd_f64: CUDA error: %s", cudaGetErrorString(err));
+  }
   return GNB200_OK;
 }
 
@@ -191,6 +316,14 @@ int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, 
     snprintf(text, sizeof(text), "unsupported");
   } else {
     const gnb200::Geom& g = p.geom;
+    if (p.wave) {
+      const gnb200::WaveGeom& w = p.wgeom;
+      snprintf(text, sizeof(text),
+               "%s wave ve=%d cw=%d ncb=%d ty=%d threads=%d rows=%d chunks=%d k=1 persist=1 grid=%lld smem=%zu ws=%zu "
+               "launches=%d waves=%d ipw=%d box=%dx%d stages=%d",
+               direction == 0 ? "fwd" : "bwd", p.ve, w.CW, w.ncb, w.TY, p.threads, w.rows_per_chunk, w.chunks, p.grid,
+               p.smem_bytes, p.ws_bytes, p.launches, w.waves, w.ipw, w.CW, w.BR, w.stages);
+    } else
     snprintf(text, sizeof(text),
              "%s %s ve=%d cw=%d ncb=%d ty=%d threads=%d rows=%d chunks=%d k=%d persist=%d grid=%lld smem=%zu ws=%zu launches=%d",
              direction == 0 ? "fwd" : "bwd", p.fused ? "fused" : "twopass", p.ve, g.CW, g.ncb, g.TY, p.threads,

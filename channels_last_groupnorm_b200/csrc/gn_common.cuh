@@ -653,6 +653,27 @@ struct Geom {
   int persist;     // fused forward: the grid holds the resident clusters only, each looping over items
 };
 
+// Geometry of the wave plan (gn_wave.cu): a persistent cooperative kernel that takes the tensor
+// through both passes wave by wave.  A wave is a range of `ipw` (sample, column block) slabs
+// ("items"); every item is cut into `chunks` row chunks ("units") that are dealt to the CTAs.
+constexpr int kWaveConsumers = 256;                 // consumer threads of a wave CTA
+constexpr int kWaveThreads = kWaveConsumers + 32;   // plus the producer warp
+struct WaveGeom {
+  int N, R, C, G, D;
+  int CW, CV, TY;      // channels / 16-byte vectors per column block row; row lanes of the consumers
+  int ncb, slots;      // column blocks per sample; groups per column block
+  int KR, BR;          // rows per consumer thread and rows per TMA box of one stage (BR = KR * TY)
+  int stages;          // depth of the shared-memory ring
+  int box_bytes;       // BR * CW * sizeof(T)
+  int stage_bytes;     // box_bytes rounded up to 128 (TMA destinations are 128-byte aligned)
+  int chunks, rows_per_chunk;  // units per item; rows per unit (a multiple of BR)
+  int items, ipw, waves;
+  int consumers;       // consumer threads (a multiple of 32)
+  int overlap;         // pass A of the next wave runs before pass B of this one (two waves share L2)
+  FastDiv div_D, div_CV, div_ncb;
+  WaitLimit wait;
+};
+
 // Groups touched by column block starting at channel c0 (width CW, clipped to C):
 // first group and how many.
 __device__ __forceinline__ void cb_groups(const Geom& g, int c0, int& g_lo, int& n_slots) {

@@ -17,58 +17,9 @@
 // The reference computes the same quantities with compute_stats_pt1 / compute_stats_pt2 /
 // scale_shift_kernel (src/gnnhwc/csrc/gn_kernel.cu:132-224, 226-292, 305-412).
 #include "gn_kernels.h"
+#include "gn_math.cuh"
 
 namespace gnb200 {
-
-template <int VE>
-__device__ __forceinline__ void welford_step(const float (&f)[VE], float (&mean)[VE], float (&m2)[VE], float& cnt) {
-  cnt += 1.0f;
-  const float inv = __fdividef(1.0f, cnt);
-#pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    const float d = f[e] - mean[e];
-    mean[e] = fmaf(d, inv, mean[e]);
-    m2[e] = fmaf(d, f[e] - mean[e], m2[e]);
-  }
-}
-
-// 16-bit tensors accumulate shifted sums instead: with K a value of the thread's own data (its
-// first row),  s += x - K,  q += (x - K)^2;  the subtraction converts the 16-bit element on the fly
-// (mixed-precision sub), three instructions per element and no division in the loop.  Because K is
-// one of the samples, (K - mean)^2 <= M2, so q <= (n + 1) M2 and the cancellation in
-// M2 = q - s^2 / n costs at most (n + 1) ulp of the thread's M2 - n is the thread's row count, a
-// few hundred at most - where sums of raw squares would lose mean^2 / var.
-template <typename T, int VE, int KN>
-__device__ __forceinline__ void shifted_step(const uint4& w, const float (&K)[KN], float (&s)[VE], float (&q)[VE]) {
-  static_assert(sizeof(T) == 2 && VE == 8, "16-bit elements, 16-byte vectors");
-  const uint32_t r[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    uint16_t lo, hi;
-    split_halves(r[e], lo, hi);
-    const float d0 = mixed_sub<T>(lo, K[KN == 1 ? 0 : 2 * e]);
-    const float d1 = mixed_sub<T>(hi, K[KN == 1 ? 0 : 2 * e + 1]);
-    s[2 * e] += d0;
-    s[2 * e + 1] += d1;
-    q[2 * e] = fmaf(d0, d0, q[2 * e]);
-    q[2 * e + 1] = fmaf(d1, d1, q[2 * e + 1]);
-  }
-}
-
-// (s, q) about K over `rows` rows  ->  per-lane (mean, M2); s and q are overwritten.
-template <int VE, int KN>
-__device__ __forceinline__ void shifted_finish(const float (&K)[KN], int rows, float (&mean)[VE], float (&m2)[VE],
-                                               float& cnt) {
-  cnt = (float)rows;
-  const float inv = rows > 0 ? 1.0f / cnt : 0.f;
-#pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    const float s = mean[e], q = m2[e];
-    const float ds = s * inv;
-    mean[e] = K[KN == 1 ? 0 : e] + ds;
-    m2[e] = fmaxf(fmaf(-s, ds, q), 0.f);
-  }
-}
 
 constexpr int kRingDepth = 4;  // rows in flight per thread in the multi-kernel streaming kernels
 
@@ -329,62 +280,6 @@ __device__ __forceinline__ void stream_apply(const Pack<T, VE>* __restrict__ src
   }
 }
 
-// Per-lane affine coefficients  a = rstd * gamma,  b = beta - mean * a  for the thread's channels.
-// `stat_mean` / `stat_rstd` are indexed by group relative to g_base.  UNI: all VE channels of the
-// thread belong to one group, so the statistics are looked up once.
-template <typename T, int VE, bool UNI>
-__device__ __forceinline__ void lane_affine(const T* gamma, const T* beta, const float* stat_mean,
-                                            const float* stat_rstd, int g_base, int c_first, const FastDiv div_D,
-                                            float (&a)[VE], float (&b)[VE]) {
-  float ga[VE], be[VE];
-  load_params<T, VE>(gamma, c_first, ga);
-  load_params<T, VE>(beta, c_first, be);
-  if constexpr (UNI) {
-    const int s = div_D.div(c_first) - g_base;
-    const float mu = stat_mean[s], rs = stat_rstd[s];
-#pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      a[e] = rs * ga[e];
-      b[e] = fmaf(-mu, a[e], be[e]);
-    }
-  } else {
-#pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const int s = div_D.div(c_first + e) - g_base;
-      a[e] = stat_rstd[s] * ga[e];
-      b[e] = fmaf(-stat_mean[s], a[e], be[e]);
-    }
-  }
-}
-
-// The same from parameter vectors fetched earlier (raw 16-byte loads issued before phase 1 so that
-// their latency is off the critical path between the statistics and the output pass).
-template <typename T, int VE, bool UNI>
-__device__ __forceinline__ void lane_affine_raw(const uint4& ga_raw, const uint4& be_raw, const float* stat_mean,
-                                                const float* stat_rstd, int g_base, int c_first, const FastDiv div_D,
-                                                float (&a)[VE], float (&b)[VE]) {
-  static_assert(sizeof(T) * VE == 16, "16-byte vectors only");
-  float ga[VE], be[VE];
-  unpack16<T, VE>(ga_raw, ga);
-  unpack16<T, VE>(be_raw, be);
-  if constexpr (UNI) {
-    const int s = div_D.div(c_first) - g_base;
-    const float mu = stat_mean[s], rs = stat_rstd[s];
-#pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      a[e] = rs * ga[e];
-      b[e] = fmaf(-mu, a[e], be[e]);
-    }
-  } else {
-#pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const int s = div_D.div(c_first + e) - g_base;
-      a[e] = stat_rstd[s] * ga[e];
-      b[e] = fmaf(-stat_mean[s], a[e], be[e]);
-    }
-  }
-}
-
 // CTA-local moments of every group slot of the column block from the per-thread Welford states:
 // first the slot means (sum of cnt * mean / n), then the squared deviations around them.
 //   slot[s]            = local mean      slot[slots + s] = local M2      slot[2 * slots + s] = local count
@@ -445,7 +340,7 @@ __device__ __forceinline__ void cta_slot_moments(const Geom& g, const float (&me
 // waits on its own mbarrier for the k contributions; inboxes alternate between two copies, and a
 // copy is pushed to again only by peers that have seen this CTA's contribution to the next item.
 // dynamic smem: [tile rows_per_cta * CV packs][red][tmp slots][slot 3*slots][stat 2*slots]
-//               [2 inboxes of k*slots entries of 4 floats][2 mbarriers]
+//               [2 inboxes of k*slots entries of 4 floats][2 mbarriers][dead flag]
 // ------------------------------------------------------------------------------------------------
 // MAXT: CTA size class.  128-thread launches are compiled for six CTAs per SM (<= 80 registers).
 template <typename T, int VE, int ACT, bool UNI, int MAXT>
@@ -490,7 +385,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 6 : 2)
   // keeps pushing its contributions (its peers' waits must end) but no longer arrives or waits on
   // its own barriers, whose phase may never complete - arriving again on such a barrier is
   // undefined - and it writes NaN statistics, so every output of its remaining items is NaN.
-  __shared__ unsigned int s_dead;
+  volatile unsigned int& s_dead = *reinterpret_cast<volatile unsigned int*>(mbar2 + 2);
   if (threadIdx.x == 0) {
     s_dead = 0;
     mbar_init(mbar2, 1);
@@ -813,6 +708,7 @@ static cudaError_t launch_fwd_ve(const FwdCall& c, const Plan& p, cudaStream_t s
 }
 
 cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream) {
+  if (p.wave) return launch_forward_wave(c, p, stream);
   switch (c.dtype) {
     case 0: return launch_fwd_ve<float>(c, p, stream);
     case 1: return launch_fwd_ve<__half>(c, p, stream);

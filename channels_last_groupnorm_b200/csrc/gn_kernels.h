@@ -9,7 +9,8 @@ namespace gnb200 {
 
 // A launch plan for one direction of one problem.
 struct Plan {
-  bool fused;         // true: one cluster kernel holds the slab on chip; false: multi-kernel path
+  bool fused;         // true: one cluster kernel holds the slab on chip; false: a multi-pass path
+  bool wave;          // multi-pass as one persistent cooperative kernel (gn_wave.cu, geometry in wgeom)
   int ve;             // elements per thread-vector (16 bytes worth, or 1)
   int threads;        // CTA size
   long long grid;     // CTAs of the streaming kernels
@@ -17,6 +18,7 @@ struct Plan {
   size_t ws_bytes;    // scratch bytes this plan needs
   int launches;       // kernels enqueued per call
   Geom geom;
+  WaveGeom wgeom;
 };
 
 struct FwdCall {
@@ -73,6 +75,28 @@ cudaError_t wait_limit_for_device(WaitLimit* out);
 // True once a kernel on the current device has recorded a wait that gave up; no synchronisation.
 bool wait_gave_up_on_current_device();
 void clear_wait_mirror_on_current_device();
+
+// wave plan (gn_wave.cu)
+size_t wave_workspace_bytes(const WaveGeom& g, int direction);
+cudaError_t launch_forward_wave(const FwdCall& c, const Plan& p, cudaStream_t stream);
+cudaError_t launch_backward_wave(const BwdCall& c, const Plan& p, cudaStream_t stream);
+// dgamma / dbeta from `rows` rows of per-channel (S1, S2) pairs (gn_bwd.cu)
+cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, int C, cudaStream_t stream);
+
+// channels-first tensors (gn_nchw.cu)
+bool nchw_shape_supported(int64_t N, int64_t R, int64_t C, int64_t G);
+size_t nchw_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction);
+int nchw_launch_count(int direction);
+cudaError_t launch_forward_nchw(const FwdCall& c, int64_t N, int64_t R, int64_t C, int64_t G, cudaStream_t stream);
+cudaError_t launch_backward_nchw(const BwdCall& c, int64_t N, int64_t R, int64_t C, int64_t G, cudaStream_t stream);
+// double precision, either layout (gn_f64.cu); `sums` holds 2 * N * C doubles
+cudaError_t launch_forward_f64(const double* x, const double* gamma, const double* beta, long long N, long long R,
+                               long long C, long long G, double eps, int act, bool nhwc, double* y, double* mean,
+                               double* rstd, cudaStream_t stream);
+cudaError_t launch_backward_f64(const double* dy, const double* x, const double* gamma, const double* beta,
+                                const double* mean, const double* rstd, long long N, long long R, long long C,
+                                long long G, int act, bool nhwc, double* dx, double* dgamma, double* dbeta,
+                                double* sums, cudaStream_t stream);
 
 cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream);
 cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream);

@@ -74,7 +74,8 @@ size_t fwd_red_floats(int CW, int CV, int TY, int slots, int threads, bool shuf,
 // red, tmp, two slot arrays, stat, and for the push exchange two inboxes of k * slots entries of
 // four floats plus alignment slack and two mbarriers
 size_t fwd_fold_floats(int CW, int CV, int TY, int slots, int threads, bool shuf, int tps_shift, int k) {
-  return fwd_red_floats(CW, CV, TY, slots, threads, shuf, tps_shift) + (size_t)9 * slots + 8 + (size_t)2 * 4 * k * slots + 8;
+  // (+ 12: up to 3 floats of alignment slack, two 8-byte mbarriers, the dead flag and its padding)
+  return fwd_red_floats(CW, CV, TY, slots, threads, shuf, tps_shift) + (size_t)9 * slots + 8 + (size_t)2 * 4 * k * slots + 12;
 }
 // backward scratch of the CTA reductions.
 // Generic reductions: red = the per-row-lane channel sums (2 * TY * CW floats), then part and chan.
@@ -172,6 +173,7 @@ bool plan_fused_candidate(const Shape& sh, int cw, int k, int target_threads, Pl
 
   Plan p = {};
   p.fused = true;
+  p.wave = false;
   p.ve = ve;
   p.threads = threads;
   p.grid = (long long)sh.N * ncb * k;
@@ -287,6 +289,7 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
 
   Plan p = {};
   p.fused = false;
+  p.wave = false;
   p.ve = ve;
   p.threads = threads;
   p.grid = (long long)sh.N * chunks * ncb;
@@ -309,6 +312,105 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
   return true;
 }
 
+// Wave plan (gn_wave.cu): one persistent cooperative kernel per direction.  Column blocks are whole
+// groups and whole 16-byte vectors, at most 256 elements wide (the TMA box limit), and as wide as the
+// L2 budget of a wave allows: a wave - `ipw` (sample, column block) slabs - is read twice, and the
+// second read should hit L2.  GNB200_WAVE_MB overrides the budget, GNB200_WAVE_CW the width,
+// GNB200_WAVE_STAGES / _KR / _PER_SM / _GRID the ring depth, rows per thread and stage, CTAs per SM and
+// an upper bound of the grid.
+bool plan_wave(const Shape& sh, Plan* out) {
+  const int ve = sh.ve, s = sh.s;
+  if (ve == 1) return false;  // TMA needs 16-byte aligned rows and bases
+  const long long U = (long long)sh.D / gcd_ll(sh.D, ve) * ve;
+  if (U > 256 || sh.C % U != 0) return false;
+  if ((long long)sh.N * sh.R > 0x7fffffffLL) return false;
+  const int tensors = sh.direction == 0 ? 1 : 2;  // tensors a wave keeps in L2 between its passes
+  const double budget = (double)env_int("GNB200_WAVE_MB", sh.direction == 0 ? 48 : 64) * 1024.0 * 1024.0;
+  const int units = (int)(sh.C / U);
+  int cw = 0, cw_min64 = 0, cw_fit = 0, cw_first = 0;
+  for (int m = 1; m <= units; ++m) {
+    if (units % m) continue;
+    const long long w = U * m;
+    if (w > 256) break;
+    if (!cw_first) cw_first = (int)w;
+    if (!cw_min64 && w * s >= 64) cw_min64 = (int)w;
+    if ((double)sh.R * w * s * tensors <= budget) cw_fit = (int)w;
+  }
+  cw = cw_fit;
+  if (cw_min64 && cw < cw_min64) cw = cw_min64;  // rather a wave above the budget than short row segments
+  if (!cw) cw = cw_first;
+  const int force_cw = env_int("GNB200_WAVE_CW", 0);
+  if (force_cw > 0 && force_cw % U == 0 && sh.C % force_cw == 0 && force_cw <= 256) cw = force_cw;
+
+  WaveGeom g = {};
+  g.N = sh.N, g.R = sh.R, g.C = sh.C, g.G = sh.G, g.D = sh.D;
+  g.CW = cw;
+  g.CV = cw / ve;
+  g.ncb = sh.C / cw;
+  g.slots = cw / sh.D;
+  g.consumers = kWaveConsumers;
+  g.KR = env_int("GNB200_WAVE_KR", sh.direction == 0 ? 4 : 2) == 2 ? 2 : 4;
+  g.TY = g.consumers / g.CV;
+  if (g.TY > 256 / g.KR) g.TY = 256 / g.KR;
+  g.BR = g.KR * g.TY;
+  g.box_bytes = g.BR * g.CW * s;
+  g.stage_bytes = (g.box_bytes + 127) & ~127;
+  g.stages = env_int("GNB200_WAVE_STAGES", sh.direction == 0 ? 3 : 4);
+  if (g.stages < 2) g.stages = 2;
+  if (g.stages > 8) g.stages = 8;
+  const size_t red_floats = sh.direction == 0 ? (size_t)2 * g.consumers * ve + g.consumers + 2 * g.slots
+                                              : (size_t)2 * g.consumers * ve + 2 * g.CW + 2 * g.slots;
+  size_t smem = 0;
+  for (;; --g.stages) {
+    smem = 1024 + (size_t)g.stages * tensors * g.stage_bytes + (size_t)2 * g.stages * 8 + 16 + red_floats * 4 + 16 +
+           (size_t)env_int("GNB200_WAVE_PAD", 0);
+    if (smem <= kSmemMaxOptin - 1024 || g.stages == 2) break;
+  }
+  if (smem > kSmemMaxOptin - 1024) return false;
+  int per_sm = (int)(kSmemMaxOptin / (smem + 1024));
+  const int cap = sh.direction == 0 ? 3 : 2;  // the kernels' __launch_bounds__
+  if (per_sm > cap) per_sm = cap;
+  const int force_per_sm = env_int("GNB200_WAVE_PER_SM", 0);
+  if (force_per_sm > 0 && force_per_sm < per_sm) per_sm = force_per_sm;
+  long long grid = (long long)kSmCount * per_sm;
+
+  g.items = sh.N * g.ncb;
+  const double item_bytes = (double)sh.R * cw * s * tensors;
+  long long ipw = (long long)(budget / item_bytes);
+  if (ipw < 1) ipw = 1;
+  if (ipw > g.items) ipw = g.items;
+  g.waves = (int)((g.items + ipw - 1) / ipw);
+  g.ipw = (g.items + g.waves - 1) / g.waves;
+  g.waves = (g.items + g.ipw - 1) / g.ipw;
+  long long want_chunks = (grid + g.ipw - 1) / g.ipw;
+  long long rows = (sh.R + want_chunks - 1) / want_chunks;
+  rows = (rows + g.BR - 1) / g.BR * g.BR;
+  g.rows_per_chunk = (int)rows;
+  g.chunks = (int)((sh.R + rows - 1) / rows);
+  if ((long long)g.ipw * g.chunks < grid) grid = (long long)g.ipw * g.chunks;
+  const int force_grid = env_int("GNB200_WAVE_GRID", 0);  // tests: fewer CTAs than units, several units per CTA
+  if (force_grid > 0 && force_grid < grid) grid = force_grid;
+  g.overlap = env_int("GNB200_WAVE_OVERLAP", 0) != 0 ? 1 : 0;
+  g.div_D = make_fast_div(sh.D);
+  g.div_CV = make_fast_div(g.CV);
+  g.div_ncb = make_fast_div(g.ncb);
+
+  Plan p = {};
+  p.fused = false;
+  p.wave = true;
+  p.ve = ve;
+  p.threads = kWaveThreads;
+  p.grid = grid;
+  p.smem_bytes = smem;
+  p.ws_bytes = wave_workspace_bytes(g, sh.direction);
+  p.launches = 1;
+  p.wgeom = g;
+  // the fields of `geom` that descriptions and tests read
+  p.geom = Geom{sh.N, sh.R, sh.C, sh.G, sh.D, cw, g.CV, g.TY, g.ncb, g.rows_per_chunk, g.chunks, g.slots, 1};
+  *out = p;
+  return true;
+}
+
 }  // namespace
 
 bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction, bool aligned16, Plan* plan) {
@@ -325,9 +427,12 @@ bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direct
   const int vfull = 16 / sh.s;
   sh.ve = (aligned16 && C % vfull == 0) ? vfull : 1;
   sh.direction = direction;
+  // GNB200_FORCE_PATH = twopass: the multi-kernel plan; wave: the wave plan where the shape allows it
   const char* force = getenv("GNB200_FORCE_PATH");
-  const bool want_fused = !(force && !strcmp(force, "twopass"));
-  if (want_fused && plan_fused(sh, plan)) return true;
+  const bool twopass_only = force && !strcmp(force, "twopass");
+  const bool skip_fused = twopass_only || (force && !strcmp(force, "wave"));
+  if (!skip_fused && plan_fused(sh, plan)) return true;
+  if (!twopass_only && plan_wave(sh, plan)) return true;
   return plan_two_pass(sh, plan);
 }
 
@@ -340,9 +445,14 @@ cudaError_t ensure_kernel_attributes(const void* func, size_t smem_bytes, bool n
   std::lock_guard<std::mutex> lock(mu);
   auto& st = done[std::make_pair(dev, func)];
   if (smem_bytes > 48 * 1024 && smem_bytes > st.first) {
-    err = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMaxOptin);
+    // the opt-in limit covers the kernel's static shared memory too
+    cudaFuncAttributes fa;
+    err = cudaFuncGetAttributes(&fa, func);
     if (err != cudaSuccess) return err;
-    st.first = kSmemMaxOptin;
+    const size_t room = kSmemMaxOptin - fa.sharedSizeBytes;
+    err = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)room);
+    if (err != cudaSuccess) return err;
+    st.first = room;
   }
   if (nonportable_cluster && !st.second) {
     err = cudaFuncSetAttribute(func, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);

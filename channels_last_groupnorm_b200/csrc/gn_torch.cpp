@@ -5,14 +5,18 @@
 //   fwd(Tensor X, Tensor weight, Tensor bias, int G, float eps, int act) -> (Tensor Y, Tensor means, Tensor rstds)
 //   bwd(Tensor dy, Tensor X, Tensor weight, Tensor bias, Tensor means, Tensor rstds, int G, int act)
 //       -> (Tensor dX, Tensor dweight, Tensor dbias)
-// X / dy / Y / dX are logical (N, C, R) tensors with strides (R*C, 1, C), i.e. NHWC storage.
+// X / dy / Y / dX are logical (N, C, R) tensors, either with strides (R*C, 1, C), i.e. NHWC storage -
+// the only layout the reference's ops accept - or contiguous, i.e. NCHW storage, which goes to the
+// native channels-first kernels; results have the storage order of X.
 // Differences from the reference, all deliberate: the namespace (so both libraries can live in one
-// process), means/rstds are fp32, every argument is validated, the tensor's device is made current,
-// a third op `bwd_f32` returns the parameter gradients as one packed fp32 [2, C] tensor (the
-// buffer a data-parallel caller all-reduces), and the ops carry explicit schemas with a CUDA
-// implementation (the reference registers catch-all functions, which cannot be traced).
+// process), means/rstds are fp32 (fp64 for fp64 tensors), every argument is validated, the
+// tensor's device is made current, a third op `bwd_f32` returns the parameter gradients as one packed
+// [2, C] tensor in the statistics' dtype (the buffer a data-parallel caller all-reduces), and the ops
+// carry explicit schemas with a CUDA implementation (the reference registers catch-all functions, which
+// cannot be traced).
 #include <ATen/Tensor.h>
 #include <ATen/ops/empty.h>
+#include <ATen/ops/zeros.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
@@ -21,24 +25,32 @@
 
 namespace {
 
+constexpr int kF64 = 3;  // binding-internal code: double tensors go to the gnb200_*_f64 entry points
+
 int dtype_code(const at::Tensor& t, const char* what) {
   switch (t.scalar_type()) {
     case at::kFloat: return GNB200_F32;
     case at::kHalf: return GNB200_F16;
     case at::kBFloat16: return GNB200_BF16;
+    case at::kDouble: return kF64;
     default:
-      TORCH_CHECK(false, "gnb200: ", what, " has dtype ", t.scalar_type(), "; supported: float32, float16, bfloat16");
+      TORCH_CHECK(false, "gnb200: ", what, " has dtype ", t.scalar_type(),
+                  "; supported: float32, float16, bfloat16, float64");
   }
   return -1;
 }
 
-// (N, C, R) view over NHWC storage: the (N, R, C) permutation must be contiguous.
-void check_nhwc3(const at::Tensor& t, const char* what) {
+// Storage order of a logical (N, C, R) tensor: channels-last (strides (R*C, 1, C), the reference's
+// layout, custom_gn.cpp:24,66-67) or channels-first (contiguous).  Anything else is refused.
+enum Layout { kNHWC = 0, kNCHW = 1 };
+Layout layout_of(const at::Tensor& t, const char* what) {
   TORCH_CHECK(t.device().is_cuda(), "gnb200: ", what, " must be a CUDA tensor (there is no CPU path)");
   TORCH_CHECK(t.dim() == 3, "gnb200: ", what, " must be a rank-3 (N, C, R) view, got rank ", t.dim());
-  TORCH_CHECK(t.permute({0, 2, 1}).is_contiguous(), "gnb200: ", what,
-              " must be channels-last: strides (R*C, 1, C) for sizes (N, C, R); got sizes ", t.sizes(), " strides ",
-              t.strides());
+  if (t.permute({0, 2, 1}).is_contiguous()) return kNHWC;
+  TORCH_CHECK(t.is_contiguous(), "gnb200: ", what,
+              " must be channels-last (strides (R*C, 1, C) for sizes (N, C, R)) or contiguous channels-first; got sizes ",
+              t.sizes(), " strides ", t.strides());
+  return kNCHW;
 }
 
 void check_param(const at::Tensor& p, const at::Tensor& like, int64_t C, const char* what) {
@@ -50,18 +62,27 @@ void check_param(const at::Tensor& p, const at::Tensor& like, int64_t C, const c
               " must be a contiguous vector of num_channels=", C, " elements, got sizes ", p.sizes());
 }
 
-void check_stats(const at::Tensor& s, const at::Tensor& like, int64_t N, int64_t G, const char* what) {
-  TORCH_CHECK(s.device() == like.device() && s.scalar_type() == at::kFloat && s.is_contiguous() && s.dim() == 2 &&
-                  s.size(0) == N && s.size(1) == G,
-              "gnb200: ", what, " must be the contiguous float32 (N, G) tensor returned by gnb200::fwd");
+// statistics are fp32 for fp32 / fp16 / bf16 tensors and fp64 for fp64 tensors
+at::ScalarType stats_dtype(int dtype) { return dtype == kF64 ? at::kDouble : at::kFloat; }
+
+void check_stats(const at::Tensor& s, const at::Tensor& like, int dtype, int64_t N, int64_t G, const char* what) {
+  TORCH_CHECK(s.device() == like.device() && s.scalar_type() == stats_dtype(dtype) && s.is_contiguous() &&
+                  s.dim() == 2 && s.size(0) == N && s.size(1) == G,
+              "gnb200: ", what, " must be the contiguous (N, G) tensor returned by gnb200::fwd for this input");
 }
 
 void check_status(int rc) { TORCH_CHECK(rc == GNB200_OK, gnb200_last_error(), " (status ", rc, ")"); }
 
+// a fresh tensor of X's logical sizes and storage order
+at::Tensor empty_like_layout(const at::Tensor& X, Layout layout) {
+  const int64_t N = X.size(0), C = X.size(1), R = X.size(2);
+  return layout == kNHWC ? at::empty({N, R, C}, X.options()).permute({0, 2, 1}) : at::empty({N, C, R}, X.options());
+}
+
 std::tuple<at::Tensor, at::Tensor, at::Tensor> gnb200_fwd_op(const at::Tensor& X, const at::Tensor& weight,
                                                              const at::Tensor& bias, int64_t G, double eps,
                                                              int64_t act) {
-  check_nhwc3(X, "X");
+  const Layout layout = layout_of(X, "X");
   const int64_t N = X.size(0), C = X.size(1), R = X.size(2);
   const int dtype = dtype_code(X, "X");
   check_param(weight, X, C, "weight");
@@ -69,63 +90,89 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> gnb200_fwd_op(const at::Tensor& X
   TORCH_CHECK(G >= 1 && C % G == 0, "gnb200: num_channels ", C, " is not divisible by num_groups ", G);
   TORCH_CHECK(act >= 0 && act <= 4, "gnb200: activation code ", act, " is not in 0..4");
   c10::cuda::CUDAGuard guard(X.device());
-  at::Tensor Y = at::empty({N, R, C}, X.options());
-  at::Tensor means = at::empty({N, G}, X.options().dtype(at::kFloat));
-  at::Tensor rstds = at::empty({N, G}, X.options().dtype(at::kFloat));
-  if (X.numel() > 0) {
-    const size_t ws_bytes = gnb200_fwd_workspace_bytes(N, R, C, G, dtype);
-    at::Tensor ws = at::empty({(int64_t)ws_bytes}, X.options().dtype(at::kByte));
-    check_status(gnb200_fwd(X.const_data_ptr(), weight.const_data_ptr(), bias.const_data_ptr(), N, R, C, G, eps,
-                            (int)act, dtype, Y.mutable_data_ptr(), means.mutable_data_ptr<float>(),
-                            rstds.mutable_data_ptr<float>(), ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes,
-                            c10::cuda::getCurrentCUDAStream().stream()));
+  at::Tensor Y = empty_like_layout(X, layout);
+  at::Tensor means = at::empty({N, G}, X.options().dtype(stats_dtype(dtype)));
+  at::Tensor rstds = at::empty({N, G}, X.options().dtype(stats_dtype(dtype)));
+  if (X.numel() == 0) return {Y, means, rstds};
+  auto stream = c10::cuda::getCurrentCUDAStream().stream();
+  if (dtype == kF64) {
+    check_status(gnb200_fwd_f64(X.const_data_ptr<double>(), weight.const_data_ptr<double>(),
+                                bias.const_data_ptr<double>(), N, R, C, G, eps, (int)act,
+                                layout == kNHWC ? GNB200_LAYOUT_NHWC : GNB200_LAYOUT_NCHW, Y.mutable_data_ptr<double>(),
+                                means.mutable_data_ptr<double>(), rstds.mutable_data_ptr<double>(), stream));
+    return {Y, means, rstds};
   }
-  return {Y.permute({0, 2, 1}), means, rstds};
+  const size_t ws_bytes = layout == kNHWC ? gnb200_fwd_workspace_bytes(N, R, C, G, dtype)
+                                          : gnb200_fwd_nchw_workspace_bytes(N, R, C, G, dtype);
+  at::Tensor ws = at::empty({(int64_t)ws_bytes}, X.options().dtype(at::kByte));
+  auto fn = layout == kNHWC ? &gnb200_fwd : &gnb200_fwd_nchw;
+  check_status(fn(X.const_data_ptr(), weight.const_data_ptr(), bias.const_data_ptr(), N, R, C, G, eps, (int)act, dtype,
+                  Y.mutable_data_ptr(), means.mutable_data_ptr<float>(), rstds.mutable_data_ptr<float>(),
+                  ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes, stream));
+  return {Y, means, rstds};
 }
 
-// shared body of bwd / bwd_f32
+// shared body of bwd / bwd_f32: (dX, packed [dgamma | dbeta], dweight, dbias)
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bwd_impl(const at::Tensor& dy, const at::Tensor& X,
                                                                     const at::Tensor& weight, const at::Tensor& bias,
                                                                     const at::Tensor& means, const at::Tensor& rstds,
                                                                     int64_t G, int64_t act, bool want_typed) {
-  check_nhwc3(X, "X");
-  check_nhwc3(dy, "dy");
+  const Layout layout = layout_of(X, "X");
   const int64_t N = X.size(0), C = X.size(1), R = X.size(2);
   const int dtype = dtype_code(X, "X");
   TORCH_CHECK(dy.sizes() == X.sizes() && dy.scalar_type() == X.scalar_type() && dy.device() == X.device(),
               "gnb200: dy must match X in sizes, dtype and device");
+  TORCH_CHECK(X.numel() == 0 || layout_of(dy, "dy") == layout || C == 1 || R == 1,
+              "gnb200: dy must have the storage order of X; got sizes ", dy.sizes(), " strides ", dy.strides());
   check_param(weight, X, C, "weight");
   check_param(bias, X, C, "bias");
   TORCH_CHECK(G >= 1 && C % G == 0, "gnb200: num_channels ", C, " is not divisible by num_groups ", G);
   TORCH_CHECK(act >= 0 && act <= 4, "gnb200: activation code ", act, " is not in 0..4");
-  check_stats(means, X, N, G, "means");
-  check_stats(rstds, X, N, G, "rstds");
+  check_stats(means, X, dtype, N, G, "means");
+  check_stats(rstds, X, dtype, N, G, "rstds");
   c10::cuda::CUDAGuard guard(X.device());
-  at::Tensor dX = at::empty({N, R, C}, X.options());
-  at::Tensor dparam = at::empty({2, C}, X.options().dtype(at::kFloat));
+  at::Tensor dX = empty_like_layout(X, layout);
+  at::Tensor dparam = at::empty({2, C}, X.options().dtype(stats_dtype(dtype)));
   at::Tensor dweight, dbias;
-  if (want_typed) {
+  if (want_typed && dtype != kF64) {
     dweight = at::empty({C}, X.options());
     dbias = at::empty({C}, X.options());
   }
-  if (X.numel() > 0) {
-    const size_t ws_bytes = gnb200_bwd_workspace_bytes(N, R, C, G, dtype);
-    at::Tensor ws = at::empty({(int64_t)ws_bytes}, X.options().dtype(at::kByte));
-    check_status(gnb200_bwd(dy.const_data_ptr(), X.const_data_ptr(), weight.const_data_ptr(), bias.const_data_ptr(),
-                            means.const_data_ptr<float>(), rstds.const_data_ptr<float>(), N, R, C, G, (int)act, dtype,
-                            dX.mutable_data_ptr(), dparam.mutable_data_ptr<float>(),
-                            want_typed ? dweight.mutable_data_ptr() : nullptr,
-                            want_typed ? dbias.mutable_data_ptr() : nullptr,
-                            ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes,
-                            c10::cuda::getCurrentCUDAStream().stream()));
-  } else {
+  if (X.numel() == 0) {
     dparam.zero_();
     if (want_typed) {
-      dweight.zero_();
-      dbias.zero_();
+      dweight = at::zeros({C}, X.options());
+      dbias = at::zeros({C}, X.options());
     }
+    return {dX, dparam, dweight, dbias};
   }
-  return {dX.permute({0, 2, 1}), dparam, dweight, dbias};
+  auto stream = c10::cuda::getCurrentCUDAStream().stream();
+  if (dtype == kF64) {
+    // the packed buffer is the result: its two rows are dgamma and dbeta
+    const size_t ws_bytes = gnb200_bwd_f64_workspace_bytes(N, R, C, G);
+    at::Tensor ws = at::empty({(int64_t)ws_bytes}, X.options().dtype(at::kByte));
+    double* dp = dparam.mutable_data_ptr<double>();
+    check_status(gnb200_bwd_f64(dy.const_data_ptr<double>(), X.const_data_ptr<double>(), weight.const_data_ptr<double>(),
+                                bias.const_data_ptr<double>(), means.const_data_ptr<double>(),
+                                rstds.const_data_ptr<double>(), N, R, C, G, (int)act,
+                                layout == kNHWC ? GNB200_LAYOUT_NHWC : GNB200_LAYOUT_NCHW, dX.mutable_data_ptr<double>(),
+                                dp, dp + C, ws.mutable_data_ptr(), ws_bytes, stream));
+    if (want_typed) {
+      dweight = dparam[0];
+      dbias = dparam[1];
+    }
+    return {dX, dparam, dweight, dbias};
+  }
+  const size_t ws_bytes = layout == kNHWC ? gnb200_bwd_workspace_bytes(N, R, C, G, dtype)
+                                          : gnb200_bwd_nchw_workspace_bytes(N, R, C, G, dtype);
+  at::Tensor ws = at::empty({(int64_t)ws_bytes}, X.options().dtype(at::kByte));
+  auto fn = layout == kNHWC ? &gnb200_bwd : &gnb200_bwd_nchw;
+  check_status(fn(dy.const_data_ptr(), X.const_data_ptr(), weight.const_data_ptr(), bias.const_data_ptr(),
+                  means.const_data_ptr<float>(), rstds.const_data_ptr<float>(), N, R, C, G, (int)act, dtype,
+                  dX.mutable_data_ptr(), dparam.mutable_data_ptr<float>(),
+                  want_typed ? dweight.mutable_data_ptr() : nullptr, want_typed ? dbias.mutable_data_ptr() : nullptr,
+                  ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes, stream));
+  return {dX, dparam, dweight, dbias};
 }
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor> gnb200_bwd_op(const at::Tensor& dy, const at::Tensor& X,

@@ -56,8 +56,8 @@ def allreduce_param_grads(dparam_f32: torch.Tensor, group=None) -> torch.Tensor:
     The first call for a (group, C) pair checks on the host that all ranks agree on C before the
     collective is issued.
     """
-    if dparam_f32.dtype != torch.float32 or dparam_f32.ndim != 2 or dparam_f32.shape[0] != 2:
-        raise ValueError("allreduce_param_grads: expected a float32 [2, C] tensor, got %s %s"
+    if dparam_f32.dtype not in (torch.float32, torch.float64) or dparam_f32.ndim != 2 or dparam_f32.shape[0] != 2:
+        raise ValueError("allreduce_param_grads: expected a float32 (float64 for fp64 inputs) [2, C] tensor, got %s %s"
                          % (dparam_f32.dtype, tuple(dparam_f32.shape)))
     if not dist.is_available() or not dist.is_initialized():
         return dparam_f32

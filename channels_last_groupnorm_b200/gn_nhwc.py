@@ -4,9 +4,11 @@
 src/gnnhwc/custom_gn.py:29-90 of latentCall145/channels-last-groupnorm, so a model written
 against `gnnhwc` only has to change its import.  What differs, on purpose:
 
-* there is no NCHW branch: the reference silently falls back to `F.group_norm` for inputs whose
-  channel stride is not 1 (custom_gn.py:75-79); here such inputs raise `ValueError`, as do CPU
-  tensors.  Everything that runs goes through the sm_100a kernels.
+* inputs whose channel stride is not 1 (channels-first): the reference hands them to
+  `F.group_norm` + activation (custom_gn.py:75-79); here they go to native channels-first kernels
+  (csrc/gn_nchw.cu) - no permute, no torch fallback - and come back in the input's layout.  CPU
+  tensors raise `ValueError`.  Everything that runs goes through the sm_100a kernels.
+* fp64 tensors run on a plain double-precision path (csrc/gn_f64.cu), statistics in fp64.
 * backward accepts any rank >= 3 (the reference's `dy.contiguous(memory_format=channels_last)`
   only works for rank 4, custom_gn.py:44).
 * parameters whose dtype differs from the input's (fp32 weight / bias with fp16 / bf16
@@ -36,6 +38,11 @@ ACTIVATION_CODES = {
 }
 
 
+def _is_channels_last(t: torch.Tensor) -> bool:
+    """The reference's layout rule (custom_gn.py:68): unit channel stride means channels-last."""
+    return t.stride(1) == 1 or t.shape[1] == 1
+
+
 def _as_nhwc_flat(t: torch.Tensor) -> torch.Tensor:
     """(N, C, *spatial) tensor with NHWC-contiguous storage -> (N, C, R) view with strides (R*C, 1, C).
 
@@ -47,6 +54,12 @@ def _as_nhwc_flat(t: torch.Tensor) -> torch.Tensor:
     if not nhwc.is_contiguous():
         nhwc = nhwc.contiguous()
     return nhwc.reshape(n, -1, c).permute(0, 2, 1)
+
+
+def _as_nchw_flat(t: torch.Tensor) -> torch.Tensor:
+    """(N, C, *spatial) tensor -> contiguous (N, C, R) view; copies only when it is not contiguous
+    (the reference calls x.contiguous() on this branch too, custom_gn.py:76)."""
+    return t.contiguous().reshape(t.shape[0], t.shape[1], -1)
 
 
 class GN_NHWC_Func(torch.autograd.Function):
@@ -63,7 +76,8 @@ class GN_NHWC_Func(torch.autograd.Function):
         if X.ndim < 3:
             raise ValueError("GN_NHWC_Func: X must have shape (N, C, *spatial) with at least one spatial dim")
         ctx.x_shape = X.shape
-        X_flat = _as_nhwc_flat(X)
+        ctx.channels_last = _is_channels_last(X)
+        X_flat = _as_nhwc_flat(X) if ctx.channels_last else _as_nchw_flat(X)
         ctx.param_dtypes = (weight.dtype, bias.dtype)
         if weight.dtype != X.dtype:
             weight = weight.to(X.dtype)
@@ -74,12 +88,12 @@ class GN_NHWC_Func(torch.autograd.Function):
         ctx.G = int(G)
         ctx.activation = int(activation)
         ctx.process_group = process_group
-        return _restore_shape(Y, ctx.x_shape)
+        return _restore_shape(Y, ctx.x_shape, ctx.channels_last)
 
     @staticmethod
     def backward(ctx, dy):
         X_flat, weight, bias, means, rstds = ctx.saved_tensors
-        dy_flat = _as_nhwc_flat(dy)
+        dy_flat = _as_nhwc_flat(dy) if ctx.channels_last else _as_nchw_flat(dy)
         if dy_flat.dtype != X_flat.dtype:
             dy_flat = dy_flat.to(X_flat.dtype)
         w_dtype, b_dtype = ctx.param_dtypes
@@ -91,13 +105,15 @@ class GN_NHWC_Func(torch.autograd.Function):
             if ctx.process_group is not None:
                 _dist.allreduce_param_grads(dparam, ctx.process_group)
             dgamma, dbeta = dparam[0].to(w_dtype), dparam[1].to(b_dtype)
-        return _restore_shape(dx, ctx.x_shape), dgamma, dbeta, None, None, None, None
+        return _restore_shape(dx, ctx.x_shape, ctx.channels_last), dgamma, dbeta, None, None, None, None
 
 
-def _restore_shape(flat: torch.Tensor, shape) -> torch.Tensor:
-    """(N, C, R) channels-last view -> (N, C, *spatial) view over the same NHWC storage."""
+def _restore_shape(flat: torch.Tensor, shape, channels_last=True) -> torch.Tensor:
+    """(N, C, R) view -> (N, C, *spatial) view over the same storage (NHWC or NCHW)."""
     n, c = shape[0], shape[1]
     spatial = tuple(shape[2:])
+    if not channels_last:
+        return flat.reshape(n, c, *spatial)
     nhwc = flat.permute(0, 2, 1).reshape(n, *spatial, c)
     return nhwc.permute(0, nhwc.ndim - 1, *range(1, nhwc.ndim - 1))
 
@@ -123,10 +139,6 @@ class GN_NHWC(nn.GroupNorm):
         if x.ndim < 3 or x.shape[1] != self.num_channels:
             raise ValueError("GN_NHWC: expected input of shape (N, %d, *spatial), got %s"
                              % (self.num_channels, tuple(x.shape)))
-        if x.stride(1) != 1 and x.shape[1] != 1:
-            raise ValueError(
-                "GN_NHWC: input is not channels-last (stride of dim 1 is %d, expected 1). Convert it with "
-                "x.to(memory_format=torch.channels_last); this package has no NCHW fallback." % x.stride(1))
         if self.affine:
             w, b = self.weight, self.bias
         else:

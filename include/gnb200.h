@@ -104,6 +104,44 @@ int gnb200_bwd(const void* dy, const void* x, const void* gamma, const void* bet
                void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Channels-first (NCHW) tensors: x, y, dy, dx are N * C * R elements with the pixel index fastest,
+ * everything else as for gnb200_fwd / gnb200_bwd (same argument lists, same results, same status
+ * codes; mean / rstd from gnb200_fwd_nchw feed gnb200_bwd_nchw).  The workspace is always needed
+ * (sizes from the two queries below).  These replace the branch of the reference's module that hands
+ * inputs whose channel stride is not 1 to torch's group_norm + activation
+ * (src/gnnhwc/custom_gn.py:75-79): native kernels, no permute, no call into torch.
+ */
+size_t gnb200_fwd_nchw_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype);
+size_t gnb200_bwd_nchw_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype);
+int gnb200_fwd_nchw(const void* x, const void* gamma, const void* beta,
+                    int64_t N, int64_t R, int64_t C, int64_t G, double eps, int act, int dtype,
+                    void* y, float* mean, float* rstd,
+                    void* workspace, size_t workspace_bytes, void* stream);
+int gnb200_bwd_nchw(const void* dy, const void* x, const void* gamma, const void* beta,
+                    const float* mean, const float* rstd,
+                    int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype,
+                    void* dx, float* dgamma_dbeta_f32, void* dgamma, void* dbeta,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Double precision, either layout.  The reference instantiates its launchers for double too
+ * (src/gnnhwc/csrc/custom_gn.cpp:29-33, gn_kernel.cu:533-536, 1057-1060).  Tensors, parameters,
+ * statistics and parameter gradients are all double here; gnb200_bwd_f64 needs a workspace of
+ * gnb200_bwd_f64_workspace_bytes() bytes (2 * N * C doubles).  A compatibility path (one CTA per
+ * (sample, group) slab), not a tuned one.  layout: GNB200_LAYOUT_NHWC or GNB200_LAYOUT_NCHW.
+ */
+enum { GNB200_LAYOUT_NHWC = 0, GNB200_LAYOUT_NCHW = 1 };
+size_t gnb200_bwd_f64_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G);
+int gnb200_fwd_f64(const double* x, const double* gamma, const double* beta,
+                   int64_t N, int64_t R, int64_t C, int64_t G, double eps, int act, int layout,
+                   double* y, double* mean, double* rstd, void* stream);
+int gnb200_bwd_f64(const double* dy, const double* x, const double* gamma, const double* beta,
+                   const double* mean, const double* rstd,
+                   int64_t N, int64_t R, int64_t C, int64_t G, int act, int layout,
+                   double* dx, double* dgamma, double* dbeta,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Backward for callers that must not allocate device memory and therefore cannot supply the
  * `workspace` of gnb200_bwd: plugins of an inference runtime that owns all buffers, real-time
  * loops that may not touch the allocator, code inside a stream capture, thin FFI bindings that

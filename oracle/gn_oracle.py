@@ -28,8 +28,9 @@ LIB_PATH = os.path.join(HERE, "_build", "libgn_oracle.so")
 ACT_NAMES = ["identity", "relu", "silu", "gelu", "gelu_tanh"]
 ACT_CODES = {"identity": 0, "relu": 1, "silu": 2, "swish": 2, "gelu": 3, "gelu_tanh": 4}
 
-# max-abs error relative to max(1, max|oracle|): 1e-5 for fp32 tensors, 1e-2 for 16-bit tensors
-TOLERANCE = {torch.float32: 1e-5, torch.float16: 1e-2, torch.bfloat16: 1e-2}
+# max-abs error relative to max(1, max|oracle|): 1e-5 for fp32 tensors, 1e-2 for 16-bit tensors,
+# 1e-10 for fp64 tensors
+TOLERANCE = {torch.float32: 1e-5, torch.float16: 1e-2, torch.bfloat16: 1e-2, torch.float64: 1e-10}
 
 _lib = None
 

@@ -85,8 +85,8 @@ def test_workspace_is_required_when_the_plan_needs_one():
     ((2, 1024, 128, 32), torch.float32, "fused"),
     ((64, 4096, 256, 32), torch.bfloat16, "fused"),
     ((1, 4096, 320, 32), torch.float16, "fused"),
-    ((1, 1 << 20, 128, 32), torch.float16, "twopass"),
-    ((1, 512 * 512, 256, 32), torch.float16, "twopass"),
+    ((1, 1 << 20, 128, 32), torch.float16, "wave"),
+    ((1, 512 * 512, 256, 32), torch.float16, "wave"),
     ((2, 25, 3909, 3), torch.float32, "twopass"),
 ])
 def test_planner_paths(shape, dtype, path):

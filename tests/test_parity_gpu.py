@@ -79,11 +79,11 @@ def _id(case):
 SMALL_CASES = [CFG1] + CFG2 + CFG3[:1] + CFG4[:1] + CFG5
 
 
-@pytest.mark.parametrize("path", ["auto", "twopass"])
+@pytest.mark.parametrize("path", ["auto", "twopass", "wave"])
 @pytest.mark.parametrize("case", SMALL_CASES, ids=_id)
 def test_baseline_configs_against_oracle(nt, case, path, monkeypatch):
-    if path == "twopass":
-        monkeypatch.setenv("GNB200_FORCE_PATH", "twopass")
+    if path != "auto":  # force the multi-kernel plan / the wave plan (where the shape allows it)
+        monkeypatch.setenv("GNB200_FORCE_PATH", path)
     x, ga, be, dy, G, eps, act, dtype = _case_inputs(case)
     out = run_cabi(nt, x, ga, be, dy, G, eps, act)
     big = x.numel() > 2_000_000
@@ -496,12 +496,15 @@ def test_module_affine_false_and_state_dict(nt):
     assert O.rel_err(m2(xc), ref(xc.contiguous())) < 1e-5
 
 
-def test_module_rejects_channels_first(nt):
+def test_module_accepts_channels_first(nt):
+    # the reference sends such inputs to torch's group_norm; here they take the native NCHW kernels
+    # (tests/test_nchw_f64_gpu.py covers them in depth)
     import channels_last_groupnorm_b200 as pkg
 
     m = pkg.GN_NHWC(4, 32).cuda()
-    with pytest.raises(ValueError, match="channels-last"):
-        m(torch.randn(2, 32, 6, 6, device="cuda"))
+    x = torch.randn(2, 32, 6, 6, device="cuda")
+    y = m(x)
+    assert y.is_contiguous() and O.rel_err(y, torch.nn.functional.group_norm(x, 4, m.weight, m.bias, m.eps)) < 1e-5
 
 
 @pytest.mark.parametrize("N,C,R_list", REFERENCE_TRAILING)
@@ -567,10 +570,10 @@ def test_torch_op_validation_errors(nt):
         torch.ops.gnb200.fwd(x, w, b, 3, 1e-5, 0)
     with pytest.raises(RuntimeError, match="dtype"):
         torch.ops.gnb200.fwd(x, w.half(), b, 2, 1e-5, 0)
-    with pytest.raises(RuntimeError, match="channels-last"):
-        torch.ops.gnb200.fwd(torch.randn(2, 8, 16, device="cuda"), w, b, 2, 1e-5, 0)
-    with pytest.raises(RuntimeError, match="float64|Double|dtype"):
-        torch.ops.gnb200.fwd(x.double(), w.double(), b.double(), 2, 1e-5, 0)
+    with pytest.raises(RuntimeError, match="channels-last"):  # neither channels-last nor contiguous
+        torch.ops.gnb200.fwd(torch.randn(2, 8, 32, device="cuda")[:, :, ::2], w, b, 2, 1e-5, 0)
+    with pytest.raises(RuntimeError, match="dtype"):
+        torch.ops.gnb200.fwd(x.to(torch.int32), w, b, 2, 1e-5, 0)
 
 
 # ------------------------------------------------------------------------------------------------
