@@ -425,6 +425,19 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
             fwd_t = statistics.median(_time_graph(g_fwd, barrier)[0] for _ in range(kReplays)) / steps
             bwd_t = (statistics.median(_time_graph(g_bwd, barrier)[0] for _ in range(kReplays)) / steps
                      if g_bwd is not None else 0.0)
+            # the same K steps issued call by call (host launch overhead included), for comparison
+            done[0] = done[1] = None
+            barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(steps):
+                one(warmup + i)
+            join()
+            e1.record()
+            torch.cuda.synchronize()
+            barrier()
+            run_device_steps.eager_per_step = reduce_max(e0.elapsed_time(e1) * 1e-3 / steps)
             return reduce_max(total / steps), fwd_t, bwd_t, wall, "cuda-graph"
         except Exception as exc:  # pragma: no cover - depends on driver / NCCL capture support
             sys.stderr.write("bench: CUDA-graph capture failed (%s); timing the eager loop\n" % str(exc)[:200])
@@ -463,7 +476,11 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
     total = start.elapsed_time(stop) * 1e-3
     fwd_t = sum(e[0].elapsed_time(e[1]) for e in evs) * 1e-3 / steps
     bwd_t = sum(e[1].elapsed_time(e[2]) for e in evs) * 1e-3 / steps if prob.bwd else 0.0
+    run_device_steps.eager_per_step = reduce_max(total / steps)
     return reduce_max(total / steps), fwd_t, bwd_t, (t_wall0, t_wall1), "eager"
+
+
+run_device_steps.eager_per_step = None
 
 
 def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
@@ -560,6 +577,127 @@ def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
     return per_step, h2d, d2h
 
 
+def _geometry(plan_text):
+    """The fields of a plan description that decide the arithmetic of one (sample, column block) slab."""
+    keep = ("ve", "cw", "ncb", "ty", "threads", "rows", "chunks", "k")
+    words = plan_text.split()
+    fields = dict(w.split("=") for w in words[2:] if "=" in w)
+    return (words[1],) + tuple(fields.get(k) for k in keep)
+
+
+def _rel_err(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).abs().max() / max(1.0, float(b.abs().max())))
+
+
+def run_parity_check(wl, rank, world, x_full, ga, be, dy_full, lo, hi):
+    """Value check of the sharded run on this hardware, outside every timed region.
+
+    Every rank runs the full global batch once on its own GPU, then its shard; the shard's y and dx must
+    equal the matching samples of the full-batch run (bit for bit when both runs use the same slab
+    geometry, else within the 16-bit tolerance), the all-reduced packed [dgamma | dbeta] of the shards
+    must equal the full-batch one within tolerance, and so must the gradients that come out of the
+    public module with process_group set.  The first samples of the shard are also compared with torch's
+    fp64 group_norm + activation on the device.
+    """
+    import torch.distributed as dist
+
+    import channels_last_groupnorm_b200 as pkg
+    from channels_last_groupnorm_b200 import _native as nt
+
+    N, C, H, W, G, eps, act, dt, xs, bwd, dist_name = WORKLOADS[wl]
+    dtype = DT[dt]
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    dev = torch.device("cuda", torch.cuda.current_device())
+    code = ACT_CODES[act]
+    R = H * W
+    xg, dyg = x_full.to(dev).reshape(N, R, C), dy_full.to(dev).reshape(N, R, C)
+    gad, bed = ga.to(dev), be.to(dev)
+    y_f, mean_f, rstd_f = nt.fwd_raw(xg, gad, bed, G, eps, code)
+    errs, ok = {}, True
+    same_geom = _geometry(nt.describe_plan(N, R, C, G, dtype, 0)) == _geometry(nt.describe_plan(hi - lo, R, C, G, dtype, 0))
+    xs_, dys_ = xg[lo:hi].contiguous(), dyg[lo:hi].contiguous()
+    y_s, mean_s, rstd_s = nt.fwd_raw(xs_, gad, bed, G, eps, code)
+    bitwise = bool(torch.equal(y_s, y_f[lo:hi]))
+    errs["y_shard_vs_full"] = _rel_err(y_s, y_f[lo:hi])
+    if bwd:
+        same_geom = same_geom and _geometry(nt.describe_plan(N, R, C, G, dtype, 1)) == _geometry(
+            nt.describe_plan(hi - lo, R, C, G, dtype, 1))
+        dx_f, dparam_f, _, _ = nt.bwd_raw(dyg, xg, gad, bed, mean_f, rstd_f, G, code)
+        dx_s, dparam_s, _, _ = nt.bwd_raw(dys_, xs_, gad, bed, mean_s, rstd_s, G, code)
+        bitwise = bitwise and bool(torch.equal(dx_s, dx_f[lo:hi]))
+        errs["dx_shard_vs_full"] = _rel_err(dx_s, dx_f[lo:hi])
+        if world > 1:
+            dist.all_reduce(dparam_s)
+        errs["dparam_allreduced_vs_full"] = _rel_err(dparam_s, dparam_f)
+        # the public module with process_group: one step on the shard
+        m = pkg.GN_NHWC(G, C, activation=act, eps=eps,
+                        process_group=(dist.group.WORLD if world > 1 else None)).to(dev).to(dtype)
+        with torch.no_grad():
+            m.weight.copy_(ga)
+            m.bias.copy_(be)
+        xin = xs_.reshape(hi - lo, H, W, C).permute(0, 3, 1, 2).detach().requires_grad_(True)
+        ym = m(xin)
+        ym.backward(dys_.reshape(hi - lo, H, W, C).permute(0, 3, 1, 2))
+        errs["module_y_vs_full"] = _rel_err(ym.detach().permute(0, 2, 3, 1).reshape(hi - lo, R, C), y_f[lo:hi])
+        errs["module_dx_vs_full"] = _rel_err(xin.grad.permute(0, 2, 3, 1).reshape(hi - lo, R, C), dx_f[lo:hi])
+        errs["module_dgamma_vs_full"] = _rel_err(m.weight.grad, dparam_f[0])
+        errs["module_dbeta_vs_full"] = _rel_err(m.bias.grad, dparam_f[1])
+    # anchor: the first samples of the shard against torch's fp64 group_norm + activation on the device
+    k = min(2, hi - lo)
+    x64 = xs_[:k].double().reshape(k, H, W, C).permute(0, 3, 1, 2).requires_grad_(bwd)
+    g64, b64 = gad.double().requires_grad_(bwd), bed.double().requires_grad_(bwd)
+    y64 = torch_act(act)(torch.nn.functional.group_norm(x64, G, g64, b64, eps))
+    errs["y_vs_fp64"] = _rel_err(y_s[:k], y64.detach().permute(0, 2, 3, 1).reshape(k, R, C))
+    if bwd:
+        dx64, = torch.autograd.grad(y64, (x64,), dys_[:k].double().reshape(k, H, W, C).permute(0, 3, 1, 2))
+        errs["dx_vs_fp64"] = _rel_err(dx_s[:k], dx64.permute(0, 2, 3, 1).reshape(k, R, C))
+    torch.cuda.synchronize()
+    if same_geom and not bitwise:
+        ok = False
+    ok = ok and all(e <= tol for e in errs.values())
+    ok = ok and nt.wait_timeouts() == 0
+    if world > 1:
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        ok = bool(flag.item())
+        worst = torch.tensor([errs[k_] for k_ in sorted(errs)], device=dev, dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        errs = {k_: float(v) for k_, v in zip(sorted(errs), worst.tolist())}
+    return {"ok": ok, "ranks": world, "tolerance": tol, "same_slab_geometry": bool(same_geom),
+            "shard_bitwise_equal_to_full_batch": bitwise, "max_rel_err": errs}
+
+
+SHAPE_TABLE = ("cfg3_512x128", "cfg3_512x256", "cfg3_256x512", "cfg3_128x1024",
+               "cfg2_320x64", "cfg2_640x32", "cfg2_1280x16", "cfg2_1280x8")
+
+
+def shape_table(peak):
+    """Device time of the VAE-decoder (cfg3) and SD-UNet (cfg2) shapes, same protocol as the headline:
+    buffers rotating over > 1 GiB, 20 calls per CUDA graph, median of five replays."""
+    from channels_last_groupnorm_b200 import _native as nt
+
+    rows = []
+    for wl in SHAPE_TABLE:
+        N, C, H, W, G, eps, act, dt, xs, bwd, dist_name = WORKLOADS[wl]
+        dtype = DT[dt]
+        x, ga, be, dy = make_inputs(N, C, H, W, dtype, 0, xs, dist_name)
+        prob = DeviceProblem(wl, N, x, ga, be, dy)
+        E, es = x.numel(), x.element_size()
+        cur = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+        t, _ = time_cuda(lambda i: prob.fwd(i, cur()))
+        rec = {"workload": workload_config(wl, 1)["workload"], "us_fwd": t * 1e6, "frac_fwd": 2 * E * es / t / 1e9 / peak,
+               "plan": nt.describe_plan(N, H * W, C, G, dtype, 0)}
+        if bwd:
+            t, _ = time_cuda(lambda i: prob.bwd_(i, cur(), True))
+            rec.update(us_bwd=t * 1e6, frac_bwd=3 * E * es / t / 1e9 / peak,
+                       plan_bwd=nt.describe_plan(N, H * W, C, G, dtype, 1))
+        rows.append(rec)
+        del prob
+        torch.cuda.empty_cache()
+    return rows
+
+
 def device_arm(args):
     with _StdoutToStderr():
         line = _device_arm(args)
@@ -590,6 +728,8 @@ def _device_arm(args):
     dtype = DT[dt]
     x, ga, be, dy = make_inputs(N, C, H, W, dtype, 0, xs, dist_name)  # the global seeded batch
     lo, hi = shard_bounds(N, rank, world)
+    parity = None if args.no_parity else run_parity_check(wl, rank, world, x, ga, be, dy, lo, hi)
+    torch.cuda.empty_cache()
     x, dy = x[lo:hi].contiguous(), dy[lo:hi].contiguous()
     n_local = hi - lo
 
@@ -616,11 +756,14 @@ def _device_arm(args):
         dom_bytes, dom_t, dom_name = (bwd_bytes, bwd_t, "backward") if bwd else (fwd_bytes, fwd_t, "forward")
         roof = {"bound": "hbm", "kernel": "%s (%s)" % (dom_name, nt.describe_plan(n_local, H * W, C, G, dtype, 1 if bwd else 0)),
                 "achieved": dom_bytes / dom_t / 1e9, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                "frac": dom_bytes / dom_t / 1e9 / peak, "traffic": NCU_TRAFFIC.get((wl, world, dom_name)),
+                "frac": dom_bytes / dom_t / 1e9 / peak,
+                "frac_of_8TBps_nominal": dom_bytes / dom_t / 1e9 / 8000.0,
+                "traffic": ncu_traffic(dom_name, nt.describe_plan(n_local, H * W, C, G, dtype, 1 if bwd else 0)),
                 "us_per_launch": dom_t * 1e6, "algorithmic_bytes": dom_bytes}
         roof_fwd = {"bound": "hbm", "kernel": "forward (%s)" % nt.describe_plan(n_local, H * W, C, G, dtype, 0),
                     "achieved": fwd_bytes / fwd_t / 1e9, "peak": peak, "unit": "GB/s",
-                    "frac": fwd_bytes / fwd_t / 1e9 / peak, "traffic": NCU_TRAFFIC.get((wl, world, "forward")),
+                    "frac": fwd_bytes / fwd_t / 1e9 / peak, "frac_of_8TBps_nominal": fwd_bytes / fwd_t / 1e9 / 8000.0,
+                    "traffic": ncu_traffic("forward", nt.describe_plan(n_local, H * W, C, G, dtype, 0)),
                     "us_per_launch": fwd_t * 1e6, "algorithmic_bytes": fwd_bytes}
         line = {
             "metric": "gn_nhwc_fwd_bwd_achieved_GBps", "value": alg_global / per_step / 1e9, "unit": "GB/s",
@@ -637,7 +780,15 @@ def _device_arm(args):
             "gpu_launches": args.steps * (nt.launch_count(n_local, H * W, C, G, dtype, 0)
                                           + (nt.launch_count(n_local, H * W, C, G, dtype, 1) if bwd else 0)),
             "clocks": clocks, "issue": issue_mode,
+            "us_per_call_eager": (run_device_steps.eager_per_step * 1e6 if run_device_steps.eager_per_step else None),
+            # what the step costs beyond its two calls timed alone: the collective's exposed part and the
+            # event dependencies between the streams
+            "us_collective_exposed": (per_step - fwd_t - bwd_t) * 1e6,
+            "frac_of_8TBps_nominal": alg_global / per_step / 1e9 / (8000.0 * world),
+            "parity_check": parity,
         }
+        if world == 1 and not args.no_shapes:
+            line["vae_sd_shapes"] = shape_table(peak)
         if world == 1 and not args.no_cpu:
             n_sample = min(N, 8)
             v, med, iters = time_cpu(wl, n_sample, budget_s=args.cpu_seconds)
@@ -645,20 +796,34 @@ def _device_arm(args):
                 "value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
                 "ms_per_sample_step": med * 1e3, "iters": iters,
                 "sample": "%d of %d samples, torch.nn.functional.group_norm + %s on CPU, channels_last %s, "
-                          "autograd backward, median of %d runs" % (n_sample, N, act, dt, iters)}
+                          "autograd backward, median of %d runs (the sample's 17 MB per tensor may stay in the host's "
+                          "L3, which flatters the CPU rate slightly)" % (n_sample, N, act, dt, iters)}
     else:
         line = None
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        sys.stderr.write("bench: parity check failed: %s\n" % json.dumps(parity))
+        sys.exit(1)
     return line
 
 
-# per-launch DRAM traffic in bytes (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture
-# summarised in profiles/fused_fwd_bwd_cfg4_bf16_gelu.md; keyed by (workload, ranks, direction)
-NCU_TRAFFIC = {
-    ("cfg4", 1, "forward"): 134569984 + 86704128,
-    ("cfg4", 1, "backward"): 269372928 + 109291008,
-}
+def ncu_traffic(direction, plan):
+    """Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from
+    the committed ncu summaries, profiles/traffic.json: a list of {"direction", "plan", "traffic",
+    "source"} records.  The figure is only reported when the plan string of this run equals the one the
+    capture was taken with (a changed launch plan means the capture no longer describes the kernel)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            table = json.load(f)
+    except Exception:
+        return None
+    for rec in table:
+        if rec.get("direction") == direction and rec.get("plan") == plan:
+            return rec.get("traffic")
+    return None
 
 
 # ------------------------------------------------------------------------------------------------
@@ -821,6 +986,8 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ref", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the value check that precedes the timed runs")
+    ap.add_argument("--no-shapes", action="store_true", help="skip the table of VAE / SD shapes (1 GPU only)")
     ap.add_argument("--no-graph", action="store_true", help="time the eager loop instead of a CUDA-graph replay")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--profile", type=int, default=0, metavar="CALLS",

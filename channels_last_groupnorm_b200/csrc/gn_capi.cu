@@ -320,9 +320,9 @@ int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, 
       const gnb200::WaveGeom& w = p.wgeom;
       snprintf(text, sizeof(text),
                "%s wave ve=%d cw=%d ncb=%d ty=%d threads=%d rows=%d chunks=%d k=1 persist=1 grid=%lld smem=%zu ws=%zu "
-               "launches=%d waves=%d ipw=%d box=%dx%d stages=%d",
+               "launches=%d waves=%d ipw=%d box=%dx%d stages=%d teams=%d",
                direction == 0 ? "fwd" : "bwd", p.ve, w.CW, w.ncb, w.TY, p.threads, w.rows_per_chunk, w.chunks, p.grid,
-               p.smem_bytes, p.ws_bytes, p.launches, w.waves, w.ipw, w.CW, w.BR, w.stages);
+               p.smem_bytes, p.ws_bytes, p.launches, w.waves, w.ipw, w.CW, w.BR, w.stages, w.teams);
     } else
     snprintf(text, sizeof(text),
              "%s %s ve=%d cw=%d ncb=%d ty=%d threads=%d rows=%d chunks=%d k=%d persist=%d grid=%lld smem=%zu ws=%zu launches=%d",
@@ -336,6 +336,8 @@ int gnb200_describe_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, 
   }
   return need;
 }
+
+void gnb200_debug_set_trace(void* device_buffer, size_t bytes) { gnb200::debug_set_trace(device_buffer, bytes); }
 
 int gnb200_clear_wait_timeouts(void) {
   const unsigned int zero = 0;

@@ -670,8 +670,10 @@ struct WaveGeom {
   int items, ipw, waves;
   int consumers;       // consumer threads (a multiple of 32)
   int overlap;         // pass A of the next wave runs before pass B of this one (two waves share L2)
+  int teams;           // the CTAs form this many teams that take alternate waves independently
   FastDiv div_D, div_CV, div_ncb;
   WaitLimit wait;
+  unsigned long long* trace;  // optional timeline buffer (tuning aid), else null
 };
 
 // Groups touched by column block starting at channel c0 (width CW, clipped to C):

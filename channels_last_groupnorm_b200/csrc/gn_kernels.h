@@ -77,6 +77,7 @@ bool wait_gave_up_on_current_device();
 void clear_wait_mirror_on_current_device();
 
 // wave plan (gn_wave.cu)
+void debug_set_trace(void* ptr, size_t bytes);
 size_t wave_workspace_bytes(const WaveGeom& g, int direction);
 cudaError_t launch_forward_wave(const FwdCall& c, const Plan& p, cudaStream_t stream);
 cudaError_t launch_backward_wave(const BwdCall& c, const Plan& p, cudaStream_t stream);

@@ -316,6 +316,7 @@ bool plan_two_pass(const Shape& sh, Plan* out) {
 // groups and whole 16-byte vectors, at most 256 elements wide (the TMA box limit), and as wide as the
 // L2 budget of a wave allows: a wave - `ipw` (sample, column block) slabs - is read twice, and the
 // second read should hit L2.  GNB200_WAVE_MB overrides the budget, GNB200_WAVE_CW the width,
+// GNB200_WAVE_TEAMS / _OVERLAP the number of teams and the order of the passes,
 // GNB200_WAVE_STAGES / _KR / _PER_SM / _GRID the ring depth, rows per thread and stage, CTAs per SM and
 // an upper bound of the grid.
 bool plan_wave(const Shape& sh, Plan* out) {
@@ -325,7 +326,13 @@ bool plan_wave(const Shape& sh, Plan* out) {
   if (U > 256 || sh.C % U != 0) return false;
   if ((long long)sh.N * sh.R > 0x7fffffffLL) return false;
   const int tensors = sh.direction == 0 ? 1 : 2;  // tensors a wave keeps in L2 between its passes
-  const double budget = (double)env_int("GNB200_WAVE_MB", sh.direction == 0 ? 48 : 64) * 1024.0 * 1024.0;
+  int teams_req = env_int("GNB200_WAVE_TEAMS", 2);
+  if (teams_req < 1) teams_req = 1;
+  if (teams_req > 3) teams_req = 3;
+  // L2 budget of one wave: `teams` waves are in flight at once
+  // (defaults from sweeps over the 1024-px VAE-decoder shapes on B200: two teams, overlapped order, 96 MB
+  // forward / 144 MB backward in flight - somewhat more than L2 holds measured best)
+  const double budget = (double)env_int("GNB200_WAVE_MB", sh.direction == 0 ? 96 : 144) * 1024.0 * 1024.0 / teams_req;
   const int units = (int)(sh.C / U);
   int cw = 0, cw_min64 = 0, cw_fit = 0, cw_first = 0;
   for (int m = 1; m <= units; ++m) {
@@ -376,21 +383,25 @@ bool plan_wave(const Shape& sh, Plan* out) {
 
   g.items = sh.N * g.ncb;
   const double item_bytes = (double)sh.R * cw * s * tensors;
+  g.teams = teams_req > per_sm ? per_sm : teams_req;
   long long ipw = (long long)(budget / item_bytes);
   if (ipw < 1) ipw = 1;
   if (ipw > g.items) ipw = g.items;
   g.waves = (int)((g.items + ipw - 1) / ipw);
   g.ipw = (g.items + g.waves - 1) / g.waves;
   g.waves = (g.items + g.ipw - 1) / g.ipw;
-  long long want_chunks = (grid + g.ipw - 1) / g.ipw;
+  if (g.teams > g.waves) g.teams = g.waves;
+  const long long tgrid = grid / g.teams;  // CTAs of one team: they share a wave's units
+  long long want_chunks = (tgrid + g.ipw - 1) / g.ipw;
   long long rows = (sh.R + want_chunks - 1) / want_chunks;
   rows = (rows + g.BR - 1) / g.BR * g.BR;
   g.rows_per_chunk = (int)rows;
   g.chunks = (int)((sh.R + rows - 1) / rows);
-  if ((long long)g.ipw * g.chunks < grid) grid = (long long)g.ipw * g.chunks;
+  grid = tgrid * g.teams;
+  if ((long long)g.ipw * g.chunks < tgrid) grid = (long long)g.ipw * g.chunks * g.teams;
   const int force_grid = env_int("GNB200_WAVE_GRID", 0);  // tests: fewer CTAs than units, several units per CTA
-  if (force_grid > 0 && force_grid < grid) grid = force_grid;
-  g.overlap = env_int("GNB200_WAVE_OVERLAP", 0) != 0 ? 1 : 0;
+  if (force_grid > 0 && force_grid < grid) grid = force_grid < g.teams ? g.teams : force_grid / g.teams * g.teams;
+  g.overlap = env_int("GNB200_WAVE_OVERLAP", 1) != 0 ? 1 : 0;
   g.div_D = make_fast_div(sh.D);
   g.div_CV = make_fast_div(g.CV);
   g.div_ncb = make_fast_div(g.ncb);
@@ -432,7 +443,20 @@ bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direct
   const bool twopass_only = force && !strcmp(force, "twopass");
   const bool skip_fused = twopass_only || (force && !strcmp(force, "wave"));
   if (!skip_fused && plan_fused(sh, plan)) return true;
-  if (!twopass_only && plan_wave(sh, plan)) return true;
+  if (force && !strcmp(force, "wave")) {
+    if (plan_wave(sh, plan)) return true;
+  } else if (!twopass_only && sh.direction == 1) {
+    // Measured on B200 (1024-px VAE-decoder shapes, fp16 SiLU): the wave plan beats the multi-kernel plan
+    // in the backward direction when its row segments are at least 128 bytes (512@256^2: 70 vs 82 us,
+    // 256@512^2: 130 vs 141 us) and loses with 64-byte segments (128@1024^2: 255 vs 243 us) and in the
+    // forward direction (49 vs 44, 85 vs 78, 182 vs 148 us), where it saves the third pass over the tensor
+    // but pays more for its waves' synchronisation than that pass costs.
+    Plan w;
+    if (plan_wave(sh, &w) && (long long)w.wgeom.CW * sh.s >= 128) {
+      *plan = w;
+      return true;
+    }
+  }
   return plan_two_pass(sh, plan);
 }
 

@@ -30,6 +30,8 @@
 
 namespace gnb200 {
 
+unsigned long long* debug_trace_buffer(size_t need);
+
 namespace {
 
 // ------------------------------------------------------------------------------------------------
@@ -68,34 +70,80 @@ __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_u32(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// counter + 1 with release and acquire semantics in one round trip: the writes this CTA made before
+// its block barrier are released, and if the returned value tells that every other CTA has
+// incremented, their writes are acquired.  Returns the value before the increment.
+__device__ __forceinline__ unsigned int atom_inc_acq_rel(unsigned int* p) {
+  unsigned int v;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
-// Waits until *flag is non-zero.  Bounded like mbar_wait_bounded; false if the wait gave up.
-__device__ __forceinline__ bool flag_wait_bounded(const unsigned int* flag, const WaitLimit& lim) {
-  if (ld_acquire_u32(flag) != 0) return true;
-  const long long t0 = clock64();
-  unsigned int polls = 0;
-  while (ld_acquire_u32(flag) == 0) {
-    ++polls;
-    if (polls > lim.polls && clock64() - t0 > lim.clocks) {
-      wait_gave_up(lim);
-      return false;
+__device__ __forceinline__ void red_inc_release(unsigned int* p) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
+}
+// A pair of floats published as ONE 64-bit word, which is its own flag: the scratch words start as
+// all ones (cudaMemsetAsync with 0xFF; no result of the kernels has that bit pattern - their NaN is
+// 0x7fc00000), the merging CTA stores the pair with one 8-byte store, and a reader that sees
+// anything but all ones has both values.  No fence and no second round trip for the data.
+constexpr unsigned long long kUnset = 0xFFFFFFFFFFFFFFFFull;
+__device__ __forceinline__ void publish_pair(unsigned long long* word, float a, float b) {
+  const unsigned long long v = ((unsigned long long)__float_as_uint(b) << 32) | __float_as_uint(a);
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(word), "l"(v) : "memory");
+}
+// Waits (bounded like mbar_wait_bounded) for a published pair; false if the wait gave up.
+__device__ __forceinline__ bool wait_pair(const unsigned long long* word, const WaitLimit& lim, float& a, float& b) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(word) : "memory");
+  if (v == kUnset) {
+    const long long t0 = clock64();
+    unsigned int polls = 0;
+    for (;;) {
+      asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(word) : "memory");
+      if (v != kUnset) break;
+      if (++polls > lim.polls && clock64() - t0 > lim.clocks) {
+        wait_gave_up(lim);
+        return false;
+      }
+      __nanosleep(32);
     }
-    __nanosleep(40);
   }
+  a = __uint_as_float((unsigned int)(v & 0xffffffffu));
+  b = __uint_as_float((unsigned int)(v >> 32));
   return true;
 }
 
 #define kNaN __int_as_float(0x7fc00000)
 
-// mbarrier wait of the wave kernels.  `gave_up` is the CTA's shared flag: the first wait that runs
+// Optional timeline for tuning (WaveGeom::trace, set with gnb200_debug_set_trace): thread 0 of every CTA
+// stores the global nanosecond timer at a few points of every step: trace[(cta * steps + step) * 4 + k].
+__device__ __forceinline__ void trace_mark(const WaveGeom& g, int step, int k) {
+  if (g.trace != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g.trace[((size_t)blockIdx.x * (2 * g.waves) + step) * 4 + k] = t;  // (a team uses the first 2 * its waves steps)
+  }
+}
+
+// mbarrier waits of the wave kernels.  `gave_up` is the CTA's shared flag: the first wait that runs
 // out sets it (and poisons the results, see the callers); from then on no wait of this CTA spends
 // its limit again, so a broken run ends after about one limit instead of one limit per stage.
-__device__ __forceinline__ void wave_wait(uint64_t* bar, unsigned parity, volatile int* gave_up, const WaitLimit& lim) {
+// producer (a single thread):
+__device__ __forceinline__ void producer_wait(uint64_t* bar, unsigned parity, volatile int* gave_up, const WaitLimit& lim) {
   if (mbar_try_wait(bar, parity)) return;
   if (*gave_up != 0) return;
   if (!mbar_wait_bounded(bar, parity, lim)) *gave_up = 1;
+}
+// consumers (whole warps): if the phase is not complete yet, lane 0 alone polls - 256 polling threads
+// would take issue slots from the CTAs that share the SM - and afterwards every lane observes the
+// completed phase with one more try_wait of its own, which is what makes the TMA's writes visible
+// to it.
+__device__ __forceinline__ void consumer_wait(uint64_t* bar, unsigned parity, volatile int* gave_up, const WaitLimit& lim) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return;
+  if ((threadIdx.x & 31) == 0 && *gave_up == 0) {
+    if (!mbar_wait_bounded(bar, parity, lim)) *gave_up = 1;
+  }
+  __syncwarp();
+  (void)mbar_try_wait(bar, parity);
 }
 
 // One unit of work: the rows [r0, r1) of one (sample, column block) slab.
@@ -120,23 +168,38 @@ __device__ __forceinline__ int wave_units(const WaveGeom& g, int wave) {
   return min(g.ipw, g.items - wave * g.ipw) * g.chunks;
 }
 
-// Order in which a CTA takes the waves through their two passes (pass 0 = A, 1 = B).  Plain:
-// A0 B0 A1 B1 ...  Overlapped (WaveGeom::overlap): A0 A1 B0 A2 B1 ... B(last) - pass A of the next
-// wave runs while the slabs of this wave are being merged, at the price of two waves in L2.
-__device__ __forceinline__ void schedule(const WaveGeom& g, int step, int& pass, int& wave) {
-  const int steps = 2 * g.waves;
+// Teams.  The CTAs are dealt to `teams` teams (team = blockIdx % teams); team t takes the waves t,
+// t + teams, ... through their passes on its own, so the teams drift apart in time: while one team
+// waits for its slabs to be merged or writes results, another reads the next wave from HBM.  Up to
+// `teams` waves share L2.  Within a team the order of the steps is A0 B0 A1 B1 ... or, overlapped
+// (WaveGeom::overlap), A0 A1 B0 A2 B1 ... B(last) with the team's own waves.
+struct Team {
+  int id, cta, ctas, waves, steps;
+};
+__device__ __forceinline__ Team my_team(const WaveGeom& g) {
+  Team t;
+  t.id = (int)(blockIdx.x % (unsigned)g.teams);
+  t.cta = (int)(blockIdx.x / (unsigned)g.teams);
+  t.ctas = (int)(gridDim.x / (unsigned)g.teams);
+  t.waves = t.id < g.waves ? (g.waves - t.id + g.teams - 1) / g.teams : 0;
+  t.steps = 2 * t.waves;
+  return t;
+}
+__device__ __forceinline__ void schedule(const WaveGeom& g, const Team& tm, int step, int& pass, int& wave) {
+  int w;
   if (!g.overlap) {
-    wave = step >> 1;
+    w = step >> 1;
     pass = step & 1;
   } else if (step == 0) {
-    pass = 0, wave = 0;
-  } else if (step == steps - 1) {
-    pass = 1, wave = g.waves - 1;
+    pass = 0, w = 0;
+  } else if (step == tm.steps - 1) {
+    pass = 1, w = tm.waves - 1;
   } else if (step & 1) {
-    pass = 0, wave = (step + 1) >> 1;
+    pass = 0, w = (step + 1) >> 1;
   } else {
-    pass = 1, wave = (step >> 1) - 1;
+    pass = 1, w = (step >> 1) - 1;
   }
+  wave = tm.id + w * g.teams;
 }
 
 // Ring position shared by the producer and the consumers: stage index and the parity of its use.
@@ -160,15 +223,16 @@ __device__ __forceinline__ void produce(const WaveGeom& g, const CUtensorMap* tm
   Ring ring = {0, 0};
   bool wrapped = false;
   const uint32_t box_bytes = (uint32_t)g.box_bytes;
-  for (int step = 0; step < 2 * g.waves; ++step) {
+  const Team tm = my_team(g);
+  for (int step = 0; step < tm.steps; ++step) {
     int pass, wave;
-    schedule(g, step, pass, wave);
+    schedule(g, tm, step, pass, wave);
     const int units = wave_units(g, wave);
-    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+    for (int u = tm.cta; u < units; u += tm.ctas) {
       const Unit t = decode_unit(g, wave, u);
       for (int r = t.r0; r < t.r1; r += g.BR) {
         // the consumers have emptied this stage (its previous use has the opposite parity)
-        if (wrapped) wave_wait(&empty[ring.s], ring.ph ^ 1u, gave_up, g.wait);
+        if (wrapped) producer_wait(&empty[ring.s], ring.ph ^ 1u, gave_up, g.wait);
         mbar_arrive_expect_tx(&full[ring.s], NT * box_bytes);
         const uint32_t dst = stage0 + (uint32_t)ring.s * NT * (uint32_t)g.stage_bytes;
         tma_load_2d(dst, tm_a, t.c0, t.n * g.R + r, &full[ring.s]);
@@ -216,29 +280,15 @@ __device__ __forceinline__ void init_ring(const WaveGeom& g, const Smem& sm) {
   __syncthreads();
 }
 
-// The unit's partials have been stored (by any of the consumer threads).  Every thread makes its own
-// stores visible device-wide before the block barrier, then thread 0 counts the unit as delivered.
-// Returns true (to every consumer thread) if this CTA delivered the slab's last unit and has to merge
-// the slab: all other units' partials are then visible to it.  Two consumer barriers inside.
+// The unit's partials have been stored (by any of the consumer threads).  After a block barrier
+// thread 0 counts the unit as delivered (counters start at all ones, like every scratch word that is
+// cleared).  Returns true (to every consumer thread) if this CTA delivered the slab's last unit and
+// has to merge the slab; all other units' partials are then visible to it.  Two consumer barriers.
 __device__ __forceinline__ bool deliver(const WaveGeom& g, const Smem& sm, unsigned int* count, int item) {
-  __threadfence();
   consumer_sync(g.consumers);
-  if (threadIdx.x == 0) {
-    const unsigned int before = atomicAdd(&count[item], 1u);
-    __threadfence();
-    sm.flags[0] = before == (unsigned)(g.chunks - 1) ? 1 : 0;
-  }
+  if (threadIdx.x == 0) sm.flags[0] = (atom_inc_acq_rel(&count[item]) + 1u) == (unsigned)(g.chunks - 1) ? 1 : 0;
   consumer_sync(g.consumers);
   return sm.flags[0] != 0;
-}
-// The merged values of a slab have been stored: publish the slab.  One consumer barrier inside.
-__device__ __forceinline__ void publish(const WaveGeom& g, unsigned int* ready, unsigned int* done, int item) {
-  __threadfence();
-  consumer_sync(g.consumers);
-  if (threadIdx.x == 0) {
-    st_release_u32(&ready[item], 1u);
-    if (done) atomicAdd(done, 1u);
-  }
 }
 
 constexpr int kMergeUnroll = 8;  // partials a lane has in flight while a slab is merged
@@ -251,7 +301,7 @@ template <typename T, int ACT, bool UNI, int KR>
 __global__ void __launch_bounds__(kWaveThreads, 3)
     gn_fwd_wave_kernel(const __grid_constant__ CUtensorMap tm_x, const T* __restrict__ gamma,
                        const T* __restrict__ beta, T* __restrict__ y, float* mean_out, float* rstd_out, float eps,
-                       float4* part, unsigned int* count, unsigned int* ready, const WaveGeom g) {
+                       float4* part, unsigned int* count, unsigned long long* stat_words, const WaveGeom g) {
   constexpr int VE = 16 / sizeof(T);
   constexpr bool kShifted = sizeof(T) == 2;
   constexpr int KN = UNI ? 1 : VE;
@@ -274,13 +324,15 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
   float* stat = red_cnt + g.consumers;  // mean[slots], rstd[slots]
   Ring ring = {0, 0};
 
-  for (int step = 0; step < 2 * g.waves; ++step) {
+  const Team tm = my_team(g);
+  for (int step = 0; step < tm.steps; ++step) {
     int pass, wave;
-    schedule(g, step, pass, wave);
+    schedule(g, tm, step, pass, wave);
     const int units = wave_units(g, wave);
+    trace_mark(g, step, 0);
     if (pass == 0) {
       // ---------------- pass A: partial moments ----------------
-      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      for (int u = tm.cta; u < units; u += tm.ctas) {
         const Unit t = decode_unit(g, wave, u);
         float mean[VE], m2[VE], cnt = 0.f, K[KN];
 #pragma unroll
@@ -289,7 +341,7 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
         for (int e = 0; e < KN; ++e) K[e] = 0.f;
         int rows_done = 0;
         for (int r = t.r0; r < t.r1; r += g.BR) {
-          wave_wait(&sm.full[ring.s], ring.ph, &sm.flags[1], g.wait);
+          consumer_wait(&sm.full[ring.s], ring.ph, &sm.flags[1], g.wait);
           const uint32_t base = sm.stage0 + (uint32_t)ring.s * g.stage_bytes + my_off;
           uint4 w[KR];
 #pragma unroll
@@ -319,6 +371,7 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
             }
           }
         }
+        trace_mark(g, step, 1);
         if constexpr (kShifted) shifted_finish<VE, KN>(K, rows_done, mean, m2, cnt);
         // CTA reduction: every thread parks its per-lane moments; one warp per group slot merges
         // them in a fixed order (mean first, then the squared deviations about it)
@@ -352,22 +405,24 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
           a2 = warp_sum_all(a2);
           if (lane == 0) part[((size_t)t.item * g.chunks + t.chunk) * g.slots + s] = make_float4(mu, a2, an, 0.f);
         }
-        if (deliver(g, sm, count, t.item)) {
+        const bool last_unit = deliver(g, sm, count, t.item);
+        trace_mark(g, step, 2);
+        if (last_unit) {
           // This CTA brought the slab's last partial: merge all of them and publish mean / rstd.
           // One warp per group slot; a lane keeps kMergeUnroll loads in flight; sums are taken about
           // the first chunk's mean, so that nothing cancels when |mean| is large.
           const int g_lo = g.div_D.div(t.c0);
           const float4* row0 = part + (size_t)t.item * g.chunks * g.slots;
           for (int s = warp; s < g.slots; s += nwarps) {
-            const float K0 = __ldcg(&row0[s]).x;
-            float an = 0.f, ad = 0.f, aq = 0.f;
-            for (int base = lane; base < g.chunks; base += 32 * kMergeUnroll) {
+            float K0 = 0.f, an = 0.f, ad = 0.f, aq = 0.f;
+            for (int base = lane; base < g.chunks + lane; base += 32 * kMergeUnroll) {
               float4 v[kMergeUnroll];
 #pragma unroll
               for (int q = 0; q < kMergeUnroll; ++q) {
                 const int ch = base + 32 * q;
-                v[q] = ch < g.chunks ? __ldcg(&row0[(size_t)ch * g.slots + s]) : make_float4(K0, 0.f, 0.f, 0.f);
+                v[q] = ch < g.chunks ? __ldcg(&row0[(size_t)ch * g.slots + s]) : make_float4(0.f, 0.f, 0.f, 0.f);
               }
+              if (base == lane) K0 = __shfl_sync(0xffffffffu, v[0].x, 0);  // chunk 0's mean, loaded by lane 0
 #pragma unroll
               for (int q = 0; q < kMergeUnroll; ++q) {
                 const float d = v[q].x - K0;
@@ -383,32 +438,37 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
               const bool bad = sm.flags[1] != 0;
               const float dm = ad / an;
               const float var = fmaxf(fmaf(-ad, dm, aq) / an, 0.f);
-              mean_out[(size_t)t.n * g.G + g_lo + s] = bad ? kNaN : K0 + dm;
-              rstd_out[(size_t)t.n * g.G + g_lo + s] = bad ? kNaN : rsqrtf(var + eps);
+              const float mu = bad ? kNaN : K0 + dm, rs = bad ? kNaN : rsqrtf(var + eps);
+              publish_pair(&stat_words[(size_t)t.item * g.slots + s], mu, rs);  // what pass B waits for
+              mean_out[(size_t)t.n * g.G + g_lo + s] = mu;
+              rstd_out[(size_t)t.n * g.G + g_lo + s] = rs;
             }
           }
-          publish(g, ready, nullptr, t.item);
         }
+        trace_mark(g, step, 3);
       }
     } else {
       // ---------------- pass B: normalise, scale, shift, activate ----------------
-      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      for (int u = tm.cta; u < units; u += tm.ctas) {
         const Unit t = decode_unit(g, wave, u);
         const int g_lo = g.div_D.div(t.c0);
-        if (tid == 0 && sm.flags[1] == 0 && !flag_wait_bounded(&ready[t.item], g.wait)) sm.flags[1] = 1;
-        consumer_sync(g.consumers);
-        if (tid < g.slots) {
-          const bool bad = sm.flags[1] != 0;  // a wait of this CTA gave up: poison what depends on it
-          stat[tid] = bad ? kNaN : __ldcg(&mean_out[(size_t)t.n * g.G + g_lo + tid]);
-          stat[g.slots + tid] = bad ? kNaN : __ldcg(&rstd_out[(size_t)t.n * g.G + g_lo + tid]);
+        for (int s = tid; s < g.slots; s += g.consumers) {
+          float mu = kNaN, rs = kNaN;  // a wait that gave up poisons what depends on it
+          if (sm.flags[1] != 0 || !wait_pair(&stat_words[(size_t)t.item * g.slots + s], g.wait, mu, rs)) {
+            sm.flags[1] = 1;
+            mu = rs = kNaN;
+          }
+          stat[s] = mu;
+          stat[g.slots + s] = rs;
         }
         consumer_sync(g.consumers);
+        trace_mark(g, step, 1);
         float a[VE], b[VE];
         if (streaming) lane_affine<T, VE, UNI>(gamma, beta, stat, stat + g.slots, g_lo, t.c0 + tx * VE, g.div_D, a, b);
         T* yrow = y + ((size_t)t.n * g.R + t.r0 + ty) * g.C + t.c0 + tx * VE;
         const size_t ystep = (size_t)g.TY * g.C;
         for (int r = t.r0; r < t.r1; r += g.BR) {
-          wave_wait(&sm.full[ring.s], ring.ph, &sm.flags[1], g.wait);
+          consumer_wait(&sm.full[ring.s], ring.ph, &sm.flags[1], g.wait);
           const uint32_t base = sm.stage0 + (uint32_t)ring.s * g.stage_bytes + my_off;
           uint4 w[KR];
 #pragma unroll
@@ -430,6 +490,7 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
           }
           yrow += (size_t)KR * ystep;
         }
+        trace_mark(g, step, 2);
         consumer_sync(g.consumers);  // `stat` is rewritten by the next unit
       }
     }
@@ -474,8 +535,9 @@ template <typename T, int ACT, bool UNI, int KR>
 __global__ void __launch_bounds__(kWaveThreads, 2)
     gn_bwd_wave_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                        const T* __restrict__ gamma, const T* __restrict__ beta, const float* __restrict__ mean_in,
-                       const float* __restrict__ rstd_in, T* __restrict__ dx, float2* tpart, float2* gpart, float* coef,
-                       unsigned int* count, unsigned int* ready, unsigned int* done, float* __restrict__ dparam_f32,
+                       const float* __restrict__ rstd_in, T* __restrict__ dx, float2* tpart, float2* gpart,
+                       unsigned long long* coef_words, unsigned int* count, unsigned int* done,
+                       float* __restrict__ dparam_f32,
                        T* __restrict__ dgamma, T* __restrict__ dbeta, const WaveGeom g) {
   constexpr int VE = 16 / sizeof(T);
   constexpr bool kRaw = sizeof(T) == 2;  // 16-bit tensors: packed arithmetic, S2 against the raw x
@@ -499,13 +561,14 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
   Ring ring = {0, 0};
   const float inv_m = 1.0f / ((float)g.D * (float)g.R);
 
-  for (int step = 0; step < 2 * g.waves; ++step) {
+  const Team tm = my_team(g);
+  for (int step = 0; step < tm.steps; ++step) {
     int pass, wave;
-    schedule(g, step, pass, wave);
+    schedule(g, tm, step, pass, wave);
     const int units = wave_units(g, wave);
     if (pass == 0) {
       // ---------------- pass A: per-channel sums of dyh and dyh * xh ----------------
-      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      for (int u = tm.cta; u < units; u += tm.ctas) {
         const Unit t = decode_unit(g, wave, u);
         BwdLane<T, VE> L;
         float a[VE], b[VE], s1[VE], s2[VE];
@@ -521,7 +584,7 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
           }
         }
         for (int r = t.r0; r < t.r1; r += g.BR) {
-          wave_wait(&sm.full[ring.s], ring.ph, &sm.flags[1], g.wait);
+          consumer_wait(&sm.full[ring.s], ring.ph, &sm.flags[1], g.wait);
           const uint32_t base = sm.stage0 + (uint32_t)ring.s * 2u * g.stage_bytes + my_off;
           uint4 xw[KR], dw[KR];
 #pragma unroll
@@ -585,7 +648,6 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
         }
         if (deliver(g, sm, count, t.item)) {
           // merge the slab's group sums (one warp per slot, kMergeUnroll loads in flight per lane)
-          const int g_lo = g.div_D.div(t.c0);
           const float2* row0 = gpart + (size_t)t.item * g.chunks * g.slots;
           for (int s = warp; s < g.slots; s += nwarps) {
             float w1 = 0.f, w2 = 0.f;
@@ -603,24 +665,26 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
             w2 = warp_sum_all(w2);
             if (lane == 0) {
               const bool bad = sm.flags[1] != 0;
-              coef[((size_t)t.n * g.G + g_lo + s) * 2] = bad ? kNaN : w1 * inv_m;
-              coef[((size_t)t.n * g.G + g_lo + s) * 2 + 1] = bad ? kNaN : w2 * inv_m;
+              publish_pair(&coef_words[(size_t)t.item * g.slots + s], bad ? kNaN : w1 * inv_m, bad ? kNaN : w2 * inv_m);
             }
           }
-          publish(g, ready, done, t.item);
+          // every unit of the slab has delivered its channel sums: one more slab whose part of tpart is complete
+          if (tid == 0) red_inc_release(done);
         }
       }
     } else {
       // ---------------- pass B: dx ----------------
-      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      for (int u = tm.cta; u < units; u += tm.ctas) {
         const Unit t = decode_unit(g, wave, u);
         const int g_lo = g.div_D.div(t.c0);
-        if (tid == 0 && sm.flags[1] == 0 && !flag_wait_bounded(&ready[t.item], g.wait)) sm.flags[1] = 1;
-        consumer_sync(g.consumers);
-        if (tid < g.slots) {
-          const bool bad = sm.flags[1] != 0;
-          scoef[tid] = bad ? kNaN : __ldcg(&coef[((size_t)t.n * g.G + g_lo + tid) * 2]);
-          scoef[g.slots + tid] = bad ? kNaN : __ldcg(&coef[((size_t)t.n * g.G + g_lo + tid) * 2 + 1]);
+        for (int s = tid; s < g.slots; s += g.consumers) {
+          float A = kNaN, B = kNaN;
+          if (sm.flags[1] != 0 || !wait_pair(&coef_words[(size_t)t.item * g.slots + s], g.wait, A, B)) {
+            sm.flags[1] = 1;
+            A = B = kNaN;
+          }
+          scoef[s] = A;
+          scoef[g.slots + s] = B;
         }
         consumer_sync(g.consumers);
         BwdLane<T, VE> L;
@@ -651,7 +715,7 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
         T* orow = dx + ((size_t)t.n * g.R + t.r0 + ty) * g.C + t.c0 + tx * VE;
         const size_t ostep = (size_t)g.TY * g.C;
         for (int r = t.r0; r < t.r1; r += g.BR) {
-          wave_wait(&sm.full[ring.s], ring.ph, &sm.flags[1], g.wait);
+          consumer_wait(&sm.full[ring.s], ring.ph, &sm.flags[1], g.wait);
           const uint32_t base = sm.stage0 + (uint32_t)ring.s * 2u * g.stage_bytes + my_off;
           uint4 xw[KR], dw[KR];
 #pragma unroll
@@ -698,7 +762,7 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
   if (tid == 0 && sm.flags[1] == 0) {
     const long long t0 = clock64();
     unsigned int polls = 0;
-    while (ld_acquire_u32(done) < (unsigned)g.items) {
+    while (ld_acquire_u32(done) + 1u < (unsigned)g.items) {  // the counter starts at all ones
       if (++polls > g.wait.polls && clock64() - t0 > g.wait.clocks) {
         wait_gave_up(g.wait);
         sm.flags[1] = 1;
@@ -838,29 +902,31 @@ cudaError_t launch_cooperative(Kern kern, const Plan& p, cudaStream_t stream, Ar
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
-// scratch layout of the wave plans (offsets in bytes from a 16-byte aligned base)
+// scratch layout of the wave plans (offsets in bytes from a 16-byte aligned base); everything from
+// `clear` to `total` is set to all ones before the launch
 struct FwdScratch {
-  size_t part, count, ready, total;
+  size_t part, clear, words, count, total;
 };
 FwdScratch fwd_scratch(const WaveGeom& g) {
   FwdScratch s;
   s.part = 0;
-  s.count = (size_t)g.items * g.chunks * g.slots * sizeof(float4);
-  s.ready = s.count + (size_t)g.items * 4;
-  s.total = (s.ready + (size_t)g.items * 4 + 15) & ~(size_t)15;
+  s.clear = (size_t)g.items * g.chunks * g.slots * sizeof(float4);
+  s.words = s.clear;
+  s.count = s.words + (size_t)g.items * g.slots * 8;
+  s.total = (s.count + (size_t)g.items * 4 + 15) & ~(size_t)15;
   return s;
 }
 struct BwdScratch {
-  size_t tpart, gpart, coef, count, ready, done, total;
+  size_t tpart, gpart, clear, words, count, done, total;
 };
 BwdScratch bwd_scratch(const WaveGeom& g) {
   BwdScratch s;
   s.tpart = 0;
   s.gpart = (size_t)g.N * g.chunks * g.C * sizeof(float2);
-  s.coef = s.gpart + (size_t)g.items * g.chunks * g.slots * sizeof(float2);
-  s.count = s.coef + (size_t)g.N * g.G * 2 * sizeof(float);
-  s.ready = s.count + (size_t)g.items * 4;
-  s.done = s.ready + (size_t)g.items * 4;
+  s.clear = s.gpart + (size_t)g.items * g.chunks * g.slots * sizeof(float2);
+  s.words = s.clear;
+  s.count = s.words + (size_t)g.items * g.slots * 8;
+  s.done = s.count + (size_t)g.items * 4;
   s.total = (s.done + 4 + 15) & ~(size_t)15;
   return s;
 }
@@ -870,17 +936,18 @@ cudaError_t launch_fwd_wave_t(const FwdCall& c, const Plan& p, cudaStream_t stre
   WaveGeom g = p.wgeom;
   cudaError_t err = wait_limit_for_device(&g.wait);
   if (err != cudaSuccess) return err;
+  g.trace = debug_trace_buffer((size_t)p.grid * 2 * g.waves * 4 * sizeof(unsigned long long));
   CUtensorMap tm;
   err = make_tensor_map(&tm, c.x, c.dtype, g);
   if (err != cudaSuccess) return err;
   const FwdScratch s = fwd_scratch(g);
   char* ws = static_cast<char*>(c.workspace);
-  err = cudaMemsetAsync(ws + s.count, 0, s.total - s.count, stream);  // arrival counters and flags
+  err = cudaMemsetAsync(ws + s.clear, 0xFF, s.total - s.clear, stream);  // statistics words and arrival counters
   if (err != cudaSuccess) return err;
   auto args = [&](auto kern) {
     return launch_cooperative(kern, p, stream, tm, (const T*)c.gamma, (const T*)c.beta, (T*)c.y, c.mean, c.rstd, c.eps,
                               reinterpret_cast<float4*>(ws + s.part), reinterpret_cast<unsigned int*>(ws + s.count),
-                              reinterpret_cast<unsigned int*>(ws + s.ready), g);
+                              reinterpret_cast<unsigned long long*>(ws + s.words), g);
   };
   return g.KR == 2 ? args(gn_fwd_wave_kernel<T, ACT, UNI, 2>) : args(gn_fwd_wave_kernel<T, ACT, UNI, 4>);
 }
@@ -897,13 +964,13 @@ cudaError_t launch_bwd_wave_t(const BwdCall& c, const Plan& p, cudaStream_t stre
   if (err != cudaSuccess) return err;
   const BwdScratch s = bwd_scratch(g);
   char* ws = static_cast<char*>(c.workspace);
-  err = cudaMemsetAsync(ws + s.count, 0, s.total - s.count, stream);
+  err = cudaMemsetAsync(ws + s.clear, 0xFF, s.total - s.clear, stream);
   if (err != cudaSuccess) return err;
   auto args = [&](auto kern) {
     return launch_cooperative(kern, p, stream, tm_x, tm_dy, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd,
                               (T*)c.dx, reinterpret_cast<float2*>(ws + s.tpart), reinterpret_cast<float2*>(ws + s.gpart),
-                              reinterpret_cast<float*>(ws + s.coef), reinterpret_cast<unsigned int*>(ws + s.count),
-                              reinterpret_cast<unsigned int*>(ws + s.ready), reinterpret_cast<unsigned int*>(ws + s.done),
+                              reinterpret_cast<unsigned long long*>(ws + s.words),
+                              reinterpret_cast<unsigned int*>(ws + s.count), reinterpret_cast<unsigned int*>(ws + s.done),
                               c.dparam_f32, (T*)c.dgamma, (T*)c.dbeta, g);
   };
   return g.KR == 2 ? args(gn_bwd_wave_kernel<T, ACT, UNI, 2>) : args(gn_bwd_wave_kernel<T, ACT, UNI, 4>);
@@ -941,6 +1008,16 @@ cudaError_t launch_bwd_wave_a(const BwdCall& c, const Plan& p, cudaStream_t stre
 }
 
 }  // namespace
+
+namespace {
+unsigned long long* g_trace_ptr = nullptr;
+size_t g_trace_bytes = 0;
+}  // namespace
+void debug_set_trace(void* ptr, size_t bytes) {
+  g_trace_ptr = static_cast<unsigned long long*>(ptr);
+  g_trace_bytes = bytes;
+}
+unsigned long long* debug_trace_buffer(size_t need) { return (g_trace_ptr && g_trace_bytes >= need) ? g_trace_ptr : nullptr; }
 
 size_t wave_workspace_bytes(const WaveGeom& g, int direction) {
   return direction == 0 ? fwd_scratch(g).total : bwd_scratch(g).total;

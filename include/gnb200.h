@@ -206,6 +206,16 @@ int gnb200_selftest_exchange_timeout(const void* x, const void* gamma, const voi
                                      int64_t N, int64_t R, int64_t C, int64_t G, double eps, int act, int dtype,
                                      void* y, float* mean, float* rstd, void* stream);
 
+/*
+ * Tuning aid.  While a device buffer is registered here, the forward kernel of the wave plan (the
+ * persistent kernel used for slabs that do not fit a cluster) stores the GPU's nanosecond timer at a
+ * few points of every pass of every CTA: buffer[(cta * steps + step) * 4 + k], steps = 2 * waves, k =
+ * 0 start of the step, 1 end of streaming (pass A) / statistics known (pass B), 2 partials delivered
+ * (A) / output written (B), 3 slab merged and published (A).  NULL switches it off (the default).
+ * Not thread-safe; no counterpart in the reference.
+ */
+void gnb200_debug_set_trace(void* device_buffer, size_t bytes);
+
 /* Number of kernel launches gnb200_fwd / gnb200_bwd enqueue for this problem. */
 int gnb200_launch_count(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction);
 

@@ -85,19 +85,22 @@ def test_workspace_is_required_when_the_plan_needs_one():
     ((2, 1024, 128, 32), torch.float32, "fused"),
     ((64, 4096, 256, 32), torch.bfloat16, "fused"),
     ((1, 4096, 320, 32), torch.float16, "fused"),
-    ((1, 1 << 20, 128, 32), torch.float16, "wave"),
-    ((1, 512 * 512, 256, 32), torch.float16, "wave"),
+    ((1, 1 << 20, 128, 32), torch.float16, "twopass"),
+    ((1, 512 * 512, 256, 32), torch.float16, "twopass/wave"),
     ((2, 25, 3909, 3), torch.float32, "twopass"),
 ])
 def test_planner_paths(shape, dtype, path):
     for direction in (0, 1):
         text = nt.describe_plan(*shape, dtype, direction)
-        assert (" " + path + " ") in text, text
+        # "a/b": forward takes plan a, backward plan b (the wave plan is the default only in the backward
+        # direction, where it measured faster than the multi-kernel plan)
+        want = path.split("/")[direction] if "/" in path else path
+        assert (" " + want + " ") in text, text
         fields = dict(kv.split("=") for kv in text.split()[2:])
         assert int(fields["threads"]) % 32 == 0 and int(fields["threads"]) <= 512
         assert int(fields["smem"]) <= 227 * 1024
         assert int(fields["cw"]) % int(fields["ve"]) == 0
-        if path == "fused":
+        if want == "fused":
             assert int(fields["k"]) in (1, 2, 4, 8)
             D = shape[2] // shape[3]
             assert int(fields["cw"]) % D == 0  # a cluster owns whole groups

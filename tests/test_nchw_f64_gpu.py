@@ -95,8 +95,8 @@ def test_nchw_and_nhwc_inputs_give_the_same_module_outputs(nt):
             with torch.no_grad():
                 m.weight.copy_(torch.rand(C, device="cuda", generator=gen) + 0.5)
                 m.bias.copy_(torch.randn(C, device="cuda", generator=gen) * 0.1)
-            x1 = x.to(dtype).requires_grad_(True)                                          # NCHW
-            x2 = x.to(dtype).to(memory_format=torch.channels_last).requires_grad_(True)   # NHWC
+            x1 = x.to(dtype).clone().detach().requires_grad_(True)                                           # NCHW
+            x2 = x.to(dtype).clone().to(memory_format=torch.channels_last).detach().requires_grad_(True)   # NHWC
             out1, out2 = m(x1), m(x2)
             assert out1.is_contiguous() and out2.stride(1) == 1
             out1.backward(dy.to(dtype))

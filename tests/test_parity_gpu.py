@@ -135,8 +135,15 @@ def test_cuda_fp64_reference_agrees_with_cpu_oracle(nt):
         assert O.rel_err(a[k], b[k]) < 1e-10
 
 
-@pytest.mark.parametrize("case", CFG3[1:] + CFG4[1:], ids=_id)
-def test_full_size_configs_on_device(nt, case):
+# (configuration, forced plan): every full-size configuration with the planner's choice, and the 1024-px
+# VAE shapes with the smallest and the largest slab also with each of the multi-pass plans forced
+FULL_SIZE = [(c, "auto") for c in CFG3[1:] + CFG4[1:]] + [(c, p) for c in (CFG3[1], CFG3[3]) for p in ("wave", "twopass")]
+
+
+@pytest.mark.parametrize("case,path", FULL_SIZE, ids=lambda v: v if isinstance(v, str) else _id(v))
+def test_full_size_configs_on_device(nt, case, path, monkeypatch):
+    if path != "auto":
+        monkeypatch.setenv("GNB200_FORCE_PATH", path)
     N, C, sp, G, eps, act, dt, dist, scale = case
     gen = torch.Generator(device="cuda").manual_seed(0)
     shape = (N, *sp, C)

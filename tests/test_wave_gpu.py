@@ -35,6 +35,9 @@ CASES = [
     (1, 96, (7, 7), 3, "float32", "relu", {}),                                                 # one short chunk per slab
     (2, 256, (96, 96), 32, "float16", "gelu", {"GNB200_WAVE_MB": "1", "GNB200_WAVE_OVERLAP": "1"}),  # pass A of wave w+1 before pass B of w
     (3, 128, (40, 56), 32, "float32", "silu", {"GNB200_WAVE_MB": "1", "GNB200_WAVE_OVERLAP": "1", "GNB200_WAVE_GRID": "9"}),
+    (2, 256, (96, 96), 32, "bfloat16", "silu", {"GNB200_WAVE_MB": "2", "GNB200_WAVE_TEAMS": "2"}),     # two teams take alternate waves
+    (3, 128, (40, 56), 32, "float16", "gelu", {"GNB200_WAVE_MB": "2", "GNB200_WAVE_TEAMS": "3", "GNB200_WAVE_OVERLAP": "1"}),
+    (5, 64, (33, 31), 8, "float32", "relu", {"GNB200_WAVE_MB": "1", "GNB200_WAVE_TEAMS": "3", "GNB200_WAVE_GRID": "7"}),
 ]
 
 
