@@ -893,6 +893,24 @@ def sweep(args):
             rec["ours_bwd_us"] = t * 1e6
             rec["ours_bwd_GBps"] = 3 * E * esize / t / 1e9
             rec["ours_bwd_frac"] = rec["ours_bwd_GBps"] / peak
+        # the same problem in channels-first storage through gnb200_fwd_nchw / gnb200_bwd_nchw
+        if not args.no_nchw:
+            code = ACT_CODES[act]
+            nsets = len(prob.sets)
+            xs_n = [s_["x"].permute(0, 3, 1, 2).contiguous().reshape(N, C, H * W) for s_ in prob.sets[:min(nsets, 4)]]
+            g_n, b_n = prob.ga, prob.be
+            t, _ = time_cuda(lambda i: nt.fwd_nchw_raw(xs_n[i % len(xs_n)], g_n, b_n, G, eps, code), iters=10, reps=3, warmup=3)
+            rec["nchw_fwd_us"] = t * 1e6
+            rec["nchw_fwd_frac"] = 2 * E * esize / t / 1e9 / peak
+            if bwd:
+                dys_n = [s_["dy"].permute(0, 3, 1, 2).contiguous().reshape(N, C, H * W) for s_ in prob.sets[:len(xs_n)]]
+                _, mean_n, rstd_n = nt.fwd_nchw_raw(xs_n[0], g_n, b_n, G, eps, code)
+                t, _ = time_cuda(lambda i: nt.bwd_nchw_raw(dys_n[i % len(xs_n)], xs_n[i % len(xs_n)], g_n, b_n, mean_n, rstd_n,
+                                                           G, code), iters=10, reps=3, warmup=3)
+                rec["nchw_bwd_us"] = t * 1e6
+                rec["nchw_bwd_frac"] = 3 * E * esize / t / 1e9 / peak
+                del dys_n
+            del xs_n
         # torch CUDA group_norm + activation (context)
         fn = torch_act(act)
         sets = prob.sets
@@ -986,6 +1004,7 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ref", action="store_true")
+    ap.add_argument("--no-nchw", action="store_true", help="sweep: skip the channels-first entry points")
     ap.add_argument("--no-parity", action="store_true", help="skip the value check that precedes the timed runs")
     ap.add_argument("--no-shapes", action="store_true", help="skip the table of VAE / SD shapes (1 GPU only)")
     ap.add_argument("--no-graph", action="store_true", help="time the eager loop instead of a CUDA-graph replay")

@@ -606,20 +606,22 @@ __global__ void __launch_bounds__(kMaxThreads)
 
 // two-pass, kernel 2: one CTA of 256 threads per (n, group).  The group's channels are taken in
 // blocks of W (a power of two <= 32 covering D); thread t owns channel t % W of the block and the
-// tiles t / W, t / W + 256 / W, ... (fixed), the tile lanes are then summed in order.  Writes
-// S1, S2 per channel of the sample and the group's A, B.
+// tiles t / W, t / W + 256 / W, ... (fixed); the lanes of a warp that hold the same channel are combined
+// by an xor butterfly and the eight warps in warp order.  Writes S1, S2 per channel of the sample and
+// the group's A, B.
 template <typename T>
 __global__ void __launch_bounds__(256)
     gn_bwd_finalize_kernel(const float* __restrict__ tpart, const T* __restrict__ gamma, float* __restrict__ sums,
                            float* __restrict__ coef, const Geom g) {
-  __shared__ float sm1[256], sm2[256];
+  __shared__ float sm1[8][32], sm2[8][32];
   __shared__ float scratch[8];
   const int n = blockIdx.x / g.G, grp = blockIdx.x - n * g.G;
   int sh = 0;
   while ((1 << sh) < g.D && sh < 5) ++sh;
   const int W = 1 << sh, J = 256 >> sh;
   const int lx = threadIdx.x & (W - 1), ly = threadIdx.x >> sh;
-  float w1 = 0.f, w2 = 0.f;  // gamma-weighted sums held by the ly == 0 threads
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float w1 = 0.f, w2 = 0.f;  // gamma-weighted sums held by the first W threads
   for (int cbase = 0; cbase < g.D; cbase += W) {
     const int cin = cbase + lx;
     const bool valid = cin < g.D;
@@ -633,14 +635,22 @@ __global__ void __launch_bounds__(256)
         a2 += v.y;
       }
     }
-    sm1[threadIdx.x] = a1;
-    sm2[threadIdx.x] = a2;
+    // lanes of a warp that hold the same channel (equal lane mod W), then the eight warps in order
+    for (int b = W; b < 32; b <<= 1) {
+      a1 += __shfl_xor_sync(0xffffffffu, a1, b);
+      a2 += __shfl_xor_sync(0xffffffffu, a2, b);
+    }
+    if (lane < W) {
+      sm1[warp][lane] = a1;
+      sm2[warp][lane] = a2;
+    }
     __syncthreads();
-    if (ly == 0 && valid) {
+    if (threadIdx.x < W && valid) {
       float t1 = 0.f, t2 = 0.f;
-      for (int j = 0; j < J; ++j) {
-        t1 += sm1[(j << sh) + lx];
-        t2 += sm2[(j << sh) + lx];
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        t1 += sm1[w][threadIdx.x];
+        t2 += sm2[w][threadIdx.x];
       }
       reinterpret_cast<float2*>(sums)[(size_t)n * g.C + c] = make_float2(t1, t2);
       const float ga = load_param<T>(gamma, c);

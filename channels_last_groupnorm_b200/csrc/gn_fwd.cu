@@ -558,42 +558,49 @@ __global__ void __launch_bounds__(kMaxThreads)
   }
 }
 
-// two-pass, kernel 2: one CTA per (n, group) merges all partials that cover the group, in two
-// sweeps (mean first, then squared deviations around it).  Every thread owns a fixed subset of
-// the partials and the CTA-wide sums use a fixed tree, so the result is reproducible.
+// two-pass, kernel 2: one CTA per (n, group) merges all partials that cover the group in ONE sweep:
+// sums about the first partial's mean (nothing cancels for a large |mean|), every thread's loads in
+// flight at once, one block reduction of the three sums (warp butterflies, then the warps in order) -
+// a fixed order, so the result is reproducible.
 __global__ void __launch_bounds__(256)
     gn_fwd_finalize_kernel(const float* __restrict__ wpart, float* __restrict__ mean_out,
                            float* __restrict__ rstd_out, float eps, const Geom g) {
-  __shared__ float scratch[8];
+  __shared__ float red[8][3];
   const int n = blockIdx.x / g.G, grp = blockIdx.x - n * g.G;
   const int cb_lo = (grp * g.D) / g.CW, cb_hi = ((grp + 1) * g.D - 1) / g.CW;
   const int ncov = cb_hi - cb_lo + 1;
   const int total = ncov * g.chunks;
-  float wsum = 0.f, ntot = 0.f;
-#pragma unroll 4
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+  auto partial = [&](int i) {
     const int chunk = i / ncov, cb = cb_lo + (i - chunk * ncov);
     const int s = grp - (cb * g.CW) / g.D;
-    const float* p = wpart + ((((size_t)n * g.chunks + chunk) * g.ncb + cb) * g.slots + s) * 3;
-    wsum = fmaf(p[2], p[0], wsum);
-    ntot += p[2];
-  }
-  wsum = block_sum(wsum, scratch);
-  ntot = block_sum(ntot, scratch);
-  const float mu = wsum / ntot;
-  float m2 = 0.f;
+    return wpart + ((((size_t)n * g.chunks + chunk) * g.ncb + cb) * g.slots + s) * 3;
+  };
+  const float K0 = partial(0)[0];  // the same word for every thread: one broadcast load
+  float an = 0.f, ad = 0.f, aq = 0.f;
 #pragma unroll 4
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
-    const int chunk = i / ncov, cb = cb_lo + (i - chunk * ncov);
-    const int s = grp - (cb * g.CW) / g.D;
-    const float* p = wpart + ((((size_t)n * g.chunks + chunk) * g.ncb + cb) * g.slots + s) * 3;
-    const float d = p[0] - mu;
-    m2 += fmaf(p[2] * d, d, p[1]);
+  for (int i = threadIdx.x; i < total; i += 256) {
+    const float* p = partial(i);
+    const float d = p[0] - K0, c = p[2];
+    an += c;
+    ad = fmaf(c, d, ad);
+    aq += fmaf(c * d, d, p[1]);
   }
-  m2 = block_sum(m2, scratch);
+#pragma unroll
+  for (int b = 16; b >= 1; b >>= 1) {
+    an += __shfl_xor_sync(0xffffffffu, an, b);
+    ad += __shfl_xor_sync(0xffffffffu, ad, b);
+    aq += __shfl_xor_sync(0xffffffffu, aq, b);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp][0] = an, red[warp][1] = ad, red[warp][2] = aq;
+  __syncthreads();
   if (threadIdx.x == 0) {
-    mean_out[blockIdx.x] = mu;
-    rstd_out[blockIdx.x] = rsqrtf(fmaxf(m2 / ntot, 0.f) + eps);
+    an = ad = aq = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) an += red[w][0], ad += red[w][1], aq += red[w][2];
+    const float dm = ad / an;
+    mean_out[blockIdx.x] = K0 + dm;
+    rstd_out[blockIdx.x] = rsqrtf(fmaxf(fmaf(-ad, dm, aq) / an, 0.f) + eps);
   }
 }
 

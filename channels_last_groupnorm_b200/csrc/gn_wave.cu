@@ -46,6 +46,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+// A consumer warp hands a stage back to the producer only after it has USED the vectors it read from
+// the stage.  The shared-memory loads are merely issued when the warp moves on; signalling the stage
+// as free right after them let the producer's next TMA copy into the stage (fast when the rows come from
+// L2) now and then overtake a load that was still queued, and a warp computed one stage's rows from
+// pieces of a later stage.  So the arrival follows the arithmetic in program order - instructions
+// issue in order and the arithmetic cannot issue before its operands have arrived - and pin_regs keeps
+// the compiler from moving that arithmetic behind the arrival (the output stores of pass B are
+// volatile asm statements and stay in front of it by themselves).
+template <int N>
+__device__ __forceinline__ void pin_regs(float (&a)[N]) {
+#pragma unroll
+  for (int e = 0; e < N; ++e) asm volatile("" : "+f"(a[e]));
+}
+__device__ __forceinline__ void release_stage(uint64_t* empty_bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(empty_bar);
+}
 // Block barrier of the consumer warps only (the producer warp never joins it).  The call sites
 // follow code in which single lanes of a warp act alone (lane 0 stores a partial, thread 0 counts a
 // delivery), so the warp is brought together first and the barrier is the form that counts threads
@@ -346,9 +363,6 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
           uint4 w[KR];
 #pragma unroll
           for (int j = 0; j < KR; ++j) w[j] = lds128(base + j * row_step);
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.empty[ring.s]);
-          ring.next(g.stages);
           if (streaming) {
 #pragma unroll
             for (int j = 0; j < KR; ++j) {
@@ -370,6 +384,10 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
               }
             }
           }
+          pin_regs(mean);
+          pin_regs(m2);
+          release_stage(&sm.empty[ring.s], lane);
+          ring.next(g.stages);
         }
         trace_mark(g, step, 1);
         if constexpr (kShifted) shifted_finish<VE, KN>(K, rows_done, mean, m2, cnt);
@@ -473,9 +491,6 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
           uint4 w[KR];
 #pragma unroll
           for (int j = 0; j < KR; ++j) w[j] = lds128(base + j * row_step);
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.empty[ring.s]);
-          ring.next(g.stages);
           if (streaming) {
 #pragma unroll
             for (int j = 0; j < KR; ++j) {
@@ -488,6 +503,8 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
               }
             }
           }
+          release_stage(&sm.empty[ring.s], lane);
+          ring.next(g.stages);
           yrow += (size_t)KR * ystep;
         }
         trace_mark(g, step, 2);
@@ -592,9 +609,6 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
             xw[j] = lds128(base + j * row_step);
             dw[j] = lds128(base + g.stage_bytes + j * row_step);
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.empty[ring.s]);
-          ring.next(g.stages);
           if (streaming) {
 #pragma unroll
             for (int j = 0; j < KR; ++j) {
@@ -610,6 +624,10 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
               }
             }
           }
+          pin_regs(s1);
+          pin_regs(s2);
+          release_stage(&sm.empty[ring.s], lane);
+          ring.next(g.stages);
         }
         if constexpr (kRaw) {  // S2 = sum dyh * xh = rstd * (sum dyh * x - mean * sum dyh)
           if (streaming) {
@@ -723,9 +741,6 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
             xw[j] = lds128(base + j * row_step);
             dw[j] = lds128(base + g.stage_bytes + j * row_step);
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.empty[ring.s]);
-          ring.next(g.stages);
           if (streaming) {
 #pragma unroll
             for (int j = 0; j < KR; ++j) {
@@ -749,6 +764,8 @@ __global__ void __launch_bounds__(kWaveThreads, 2)
               }
             }
           }
+          release_stage(&sm.empty[ring.s], lane);
+          ring.next(g.stages);
           orow += (size_t)KR * ostep;
         }
         consumer_sync(g.consumers);  // `scoef` is rewritten by the next unit
