@@ -502,6 +502,8 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
   }
   __syncthreads();
 
+  // the parameter-gradient kernel may be placed now; it waits for this grid before it reads the sums
+  grid_dep_launch_dependents();
   if (streaming) {
     float A[VE], B[VE];
     if constexpr (UNI) {
@@ -533,6 +535,8 @@ __global__ void __launch_bounds__(1024)
                         T* __restrict__ dgamma, T* __restrict__ dbeta) {
   constexpr int kLanes = 32;  // row lanes: block (32 channels, 32 row lanes)
   __shared__ float sm1[kLanes][33], sm2[kLanes][33];
+  grid_dep_launch_dependents();
+  grid_dep_wait();  // the sums of the kernel before
   const int c = blockIdx.x * 32 + threadIdx.x;
   float a1 = 0.f, a2 = 0.f;
   if (c < C) {
@@ -576,6 +580,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   float* red = reinterpret_cast<float*>(reinterpret_cast<char*>(smem_raw) + 2 * ring_bytes);
   float* part = red + g.red_floats;
   float* chan = part + 2 * max((int)blockDim.x, g.CW);
+  grid_dep_launch_dependents();  // the kernels after this one wait for this grid before they read its sums
   const int tile_id = blockIdx.x;
   const int t1 = g.div_ncb.div(tile_id), cb = tile_id - t1 * g.ncb;
   const int n = g.div_chunks.div(t1), chunk = t1 - n * g.chunks;
@@ -615,6 +620,8 @@ __global__ void __launch_bounds__(256)
                            float* __restrict__ coef, const Geom g) {
   __shared__ float sm1[8][32], sm2[8][32];
   __shared__ float scratch[8];
+  grid_dep_launch_dependents();
+  grid_dep_wait();  // the reduce kernel's channel sums
   const int n = blockIdx.x / g.G, grp = blockIdx.x - n * g.G;
   int sh = 0;
   while ((1 << sh) < g.D && sh < 5) ++sh;
@@ -687,6 +694,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   if (ty >= g.TY || c0 + tx * VE >= g.C) return;
   BwdLane<T, VE> L;
   lane_setup<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, c0 + tx * VE, g.div_D, L);
+  grid_dep_wait();  // the finalize kernel's coefficients (the parameters above are the caller's)
   float A[VE], B[VE];
   if constexpr (UNI) {
     const int grp = g.div_D.div(c0 + tx * VE);
@@ -711,11 +719,12 @@ __global__ void __launch_bounds__(kMaxThreads)
 // host-side launchers
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-static cudaError_t launch_param(const BwdCall& c, const float* sums, int rows, const Geom& g, cudaStream_t stream) {
+static cudaError_t launch_param(const BwdCall& c, const float* sums, int rows, const Geom& g, cudaStream_t stream,
+                                bool chained) {
   const dim3 block(32, 32, 1);
   const unsigned blocks = (unsigned)((g.C + 31) / 32);
-  gn_bwd_param_kernel<T><<<blocks, block, 0, stream>>>(sums, rows, g.C, c.dparam_f32, (T*)c.dgamma, (T*)c.dbeta);
-  return cudaGetLastError();
+  return launch_chained(gn_bwd_param_kernel<T>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
+                        (T*)c.dgamma, (T*)c.dbeta);
 }
 
 template <typename T, int VE, int ACT, bool UNI>
@@ -751,7 +760,7 @@ static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t st
     err = cudaLaunchKernelEx(&cfg, kern, (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean,
                              c.rstd, (T*)c.dx, sums, g);
     if (err != cudaSuccess) return err;
-    return launch_param<T>(c, sums, g.N * g.k, g, stream);
+    return launch_param<T>(c, sums, g.N * g.k, g, stream, p.chain);
   }
   // two-pass scratch: [tile partials N*chunks*C*2][sums N*C*2][coef N*G*2]
   float* tpart = reinterpret_cast<float*>(c.workspace);
@@ -763,15 +772,13 @@ static cudaError_t launch_bwd_u(const BwdCall& c, const Plan& p, cudaStream_t st
       (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, tpart, g);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  gn_bwd_finalize_kernel<T><<<(unsigned)(g.N * g.G), 256, 0, stream>>>(tpart, (const T*)c.gamma, sums, coef,
-                                                                                 g);
-  err = cudaGetLastError();
+  err = launch_chained(gn_bwd_finalize_kernel<T>, (unsigned)(g.N * g.G), dim3(256), 0, stream, p.chain, tpart,
+                       (const T*)c.gamma, sums, coef, g);
   if (err != cudaSuccess) return err;
-  err = launch_param<T>(c, sums, g.N, g, stream);
+  err = launch_param<T>(c, sums, g.N, g, stream, p.chain);
   if (err != cudaSuccess) return err;
-  gn_bwd_apply_kernel<T, VE, ACT, UNI><<<(unsigned)p.grid, p.threads, 0, stream>>>(
-      (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, coef, (T*)c.dx, g);
-  return cudaGetLastError();
+  return launch_chained(gn_bwd_apply_kernel<T, VE, ACT, UNI>, (unsigned)p.grid, dim3((unsigned)p.threads), 0, stream, p.chain,
+                        (const T*)c.dy, (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, coef, (T*)c.dx, g);
 }
 
 template <typename T, int VE, int ACT>
@@ -803,9 +810,9 @@ cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, in
   Geom g = {};
   g.C = C;
   switch (c.dtype) {
-    case 0: return launch_param<float>(c, sums, rows, g, stream);
-    case 1: return launch_param<__half>(c, sums, rows, g, stream);
-    default: return launch_param<__nv_bfloat16>(c, sums, rows, g, stream);
+    case 0: return launch_param<float>(c, sums, rows, g, stream, false);
+    case 1: return launch_param<__half>(c, sums, rows, g, stream, false);
+    default: return launch_param<__nv_bfloat16>(c, sums, rows, g, stream, false);
   }
 }
 

@@ -177,6 +177,15 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4 v) {
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
 }
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may become resident while its predecessor in the stream is still running: everything
+// it does before grid_dep_wait() overlaps the predecessor's tail, and grid_dep_wait() returns once
+// the predecessor grid has completed and its writes are visible.  grid_dep_launch_dependents() in
+// the predecessor says "my CTA no longer minds sharing the SM"; CTAs that never call it count as
+// having called it when they exit.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

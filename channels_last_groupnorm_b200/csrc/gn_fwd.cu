@@ -530,6 +530,9 @@ __global__ void __launch_bounds__(kMaxThreads)
   float* tmp = red + g.red_floats;
   float* slot = tmp + g.slots;
 
+  // the finalize and apply kernels may take their places on the SMs now; they wait for this grid
+  // before they read its partials
+  grid_dep_launch_dependents();
   const int tile_id = blockIdx.x;
   const int t1 = g.div_ncb.div(tile_id), cb = tile_id - t1 * g.ncb;
   const int n = g.div_chunks.div(t1), chunk = t1 - n * g.chunks;
@@ -566,6 +569,8 @@ __global__ void __launch_bounds__(256)
     gn_fwd_finalize_kernel(const float* __restrict__ wpart, float* __restrict__ mean_out,
                            float* __restrict__ rstd_out, float eps, const Geom g) {
   __shared__ float red[8][3];
+  grid_dep_launch_dependents();
+  grid_dep_wait();  // the statistics kernel's partials
   const int n = blockIdx.x / g.G, grp = blockIdx.x - n * g.G;
   const int cb_lo = (grp * g.D) / g.CW, cb_hi = ((grp + 1) * g.D - 1) / g.CW;
   const int ncov = cb_hi - cb_lo + 1;
@@ -621,6 +626,7 @@ __global__ void __launch_bounds__(kMaxThreads)
   const int tid = threadIdx.x;
   const int ty = g.div_CV.div(tid), tx = tid - ty * g.CV;
   if (ty >= g.TY || c0 + tx * VE >= g.C) return;
+  grid_dep_wait();  // the finalize kernel's statistics
   float a[VE], b[VE];
   lane_affine<T, VE, UNI>(gamma, beta, mean_in + (size_t)n * g.G, rstd_in + (size_t)n * g.G, 0, c0 + tx * VE, g.div_D, a, b);
   const size_t base = ((size_t)n * g.R + r0) * g.C + c0 + (size_t)tx * VE;
@@ -679,12 +685,11 @@ static cudaError_t launch_two_pass(const FwdCall& c, const Plan& p, cudaStream_t
   gn_fwd_stats_kernel<T, VE, UNI><<<(unsigned)p.grid, p.threads, p.smem_bytes, stream>>>((const T*)c.x, wpart, p.geom);
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  gn_fwd_finalize_kernel<<<(unsigned)(p.geom.N * p.geom.G), 256, 0, stream>>>(wpart, c.mean, c.rstd, c.eps, p.geom);
-  err = cudaGetLastError();
+  err = launch_chained(gn_fwd_finalize_kernel, (unsigned)(p.geom.N * p.geom.G), dim3(256), 0, stream, p.chain, wpart, c.mean,
+                       c.rstd, c.eps, p.geom);
   if (err != cudaSuccess) return err;
-  gn_fwd_apply_kernel<T, VE, ACT, UNI><<<(unsigned)p.grid, p.threads, 0, stream>>>(
-      (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, (T*)c.y, p.geom);
-  return cudaGetLastError();
+  return launch_chained(gn_fwd_apply_kernel<T, VE, ACT, UNI>, (unsigned)p.grid, dim3((unsigned)p.threads), 0, stream, p.chain,
+                        (const T*)c.x, (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, (T*)c.y, p.geom);
 }
 
 template <typename T, int VE, int ACT>

@@ -17,6 +17,7 @@ struct Plan {
   size_t smem_bytes;  // dynamic shared memory of the first streaming kernel
   size_t ws_bytes;    // scratch bytes this plan needs
   int launches;       // kernels enqueued per call
+  bool chain;         // kernels after the first are launched as programmatic dependents of their predecessor
   Geom geom;
   WaveGeom wgeom;
 };
@@ -98,6 +99,24 @@ cudaError_t launch_backward_f64(const double* dy, const double* x, const double*
                                 const double* mean, const double* rstd, long long N, long long R, long long C,
                                 long long G, int act, bool nhwc, double* dx, double* dgamma, double* dbeta,
                                 double* sums, cudaStream_t stream);
+
+// Launches `kern`; with `chained` as a programmatic dependent of the previous kernel in `stream`
+// (the kernel must call grid_dep_wait() before it touches anything that kernel wrote).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), unsigned grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  bool chained, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 cudaError_t launch_forward(const FwdCall& c, const Plan& p, cudaStream_t stream);
 cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream);

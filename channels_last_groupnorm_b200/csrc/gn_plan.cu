@@ -424,7 +424,16 @@ bool plan_wave(const Shape& sh, Plan* out) {
 
 }  // namespace
 
+static bool make_plan_inner(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction, bool aligned16, Plan* plan);
+
 bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction, bool aligned16, Plan* plan) {
+  if (!make_plan_inner(N, R, C, G, dtype, direction, aligned16, plan)) return false;
+  // GNB200_CHAIN = 0: every kernel of a call waits for the whole previous kernel (plain stream order)
+  plan->chain = env_int("GNB200_CHAIN", 1) != 0;
+  return true;
+}
+
+static bool make_plan_inner(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction, bool aligned16, Plan* plan) {
   if (N < 1 || R < 1 || C < 1 || G < 1 || C % G != 0) return false;
   if (N > 0x7fffffffLL || R > 0x7fffffffLL || C > (1 << 24) || (long long)N * G > 0x7fffffffLL) return false;
   if ((double)N * (double)R * (double)C > 9.0e15) return false;
