@@ -93,6 +93,11 @@ __device__ __forceinline__ void stream_bwd_sums(const T* __restrict__ gx, const 
 }
 
 constexpr int kXRing = 4;  // x rows in flight per thread in the fused backward kernel
+// All dy rows of a thread are issued before its loop starts (every row has its own tile slot), so
+// that the loop issues only the x refill.
+constexpr bool kDyUpfront = false;
+// Phase 2 reads x (L2 hits) straight into registers, four rows at a time, instead of through the ring.
+constexpr bool kDxDirect = false;
 
 // Phase 1 of the fused path.  dy rows are copied straight into the shared-memory tile, x rows go
 // through a kXRing-deep shared-memory ring (cp.async, one commit group per row, kXRing rows in
@@ -141,6 +146,9 @@ __device__ __forceinline__ BwdPipe<T> tile_fill_start(const T* __restrict__ gx, 
         p.wd += sstep_bytes;
         ++p.dy_issued;
       }
+      if constexpr (kDyUpfront) {  // dy rows 2 kXRing + d, 3 kXRing + d, ... ride in this group as well
+        for (int r = 2 * kXRing + d; r < iters; r += kXRing) cp_async16(sd + r * sstep_bytes, gd + (size_t)r * gstep_elems);
+      }
       cp_async_commit();
     }
   }
@@ -163,6 +171,7 @@ __device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep
     }
     uint32_t wd = pipe.wd;
     int dy_issued = pipe.dy_issued;
+    (void)wd, (void)dy_issued, (void)gd;
     uint32_t rd = sd;
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kXRing - 1>();
@@ -172,11 +181,13 @@ __device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep
         cp_async16(slot, gx);
         gx += gstep_elems;
       }
-      if (dy_issued < iters) {
-        cp_async16(wd, gd);
-        gd += gstep_elems;
-        wd += sstep_bytes;
-        ++dy_issued;
+      if constexpr (!kDyUpfront) {
+        if (dy_issued < iters) {
+          cp_async16(wd, gd);
+          gd += gstep_elems;
+          wd += sstep_bytes;
+          ++dy_issued;
+        }
       }
       cp_async_commit();
       if constexpr (kRaw) {
@@ -218,7 +229,7 @@ __device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep
 template <typename T, int VE>
 __device__ __forceinline__ void tile_bwd_dx_start(const T* __restrict__ gx, size_t gstep_elems, uint32_t ring,
                                                   uint32_t ring_stride, int iters) {
-  if constexpr (sizeof(T) * VE == 16) {
+  if constexpr (sizeof(T) * VE == 16 && !kDxDirect) {
 #pragma unroll
     for (int d = 0; d < kXRing; ++d) {
       if (d < iters) {
@@ -255,8 +266,43 @@ __device__ __forceinline__ void tile_bwd_dx(const T* __restrict__ gx, uint32_t r
       c1[e] = nb[e] * L.r[e];
       c2[e] = fmaf(nb[e], L.nmr[e], na[e]);
     }
-    gx += (size_t)min(iters, kXRing) * gstep_elems;  // tile_bwd_dx_start has issued these rows
     T* gp = gdst;
+    if constexpr (kDxDirect) {
+      constexpr int U = 4;
+      for (int i = 0; i < iters; i += U) {
+        uint4 xv[U], dv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i + u < iters) {
+            xv[u] = ldg128(gx + (size_t)u * gstep_elems);
+            dv[u] = lds128(sd + u * sstep_bytes);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i + u < iters) {
+            float fx[VE], fd[VE];
+            unpack16<T, VE>(xv[u], fx);
+            unpack16<T, VE>(dv[u], fd);
+#pragma unroll
+            for (int e = 0; e < VE; ++e) {
+              if constexpr (kFold) {
+                fx[e] = fmaf(ag[e], fd[e], fmaf(c1[e], fx[e], c2[e]));
+              } else {
+                const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
+                fx[e] = fmaf(ag[e], fd[e], fmaf(nb[e], xh, na[e]));
+              }
+            }
+            stg128(gp + (size_t)u * gstep_elems, pack16<T, VE>(fx));
+          }
+        }
+        gx += (size_t)U * gstep_elems;
+        gp += (size_t)U * gstep_elems;
+        sd += U * sstep_bytes;
+      }
+      return;
+    }
+    gx += (size_t)min(iters, kXRing) * gstep_elems;  // tile_bwd_dx_start has issued these rows
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kXRing - 1>();
       const uint32_t slot = ring + (i & (kXRing - 1)) * ring_stride;
@@ -806,13 +852,13 @@ static cudaError_t launch_bwd_ve(const BwdCall& c, const Plan& p, cudaStream_t s
   return p.ve == 1 ? launch_bwd_act<T, 1>(c, p, stream) : launch_bwd_act<T, VFULL>(c, p, stream);
 }
 
-cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, int C, cudaStream_t stream) {
+cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, int C, cudaStream_t stream, bool chained) {
   Geom g = {};
   g.C = C;
   switch (c.dtype) {
-    case 0: return launch_param<float>(c, sums, rows, g, stream, false);
-    case 1: return launch_param<__half>(c, sums, rows, g, stream, false);
-    default: return launch_param<__nv_bfloat16>(c, sums, rows, g, stream, false);
+    case 0: return launch_param<float>(c, sums, rows, g, stream, chained);
+    case 1: return launch_param<__half>(c, sums, rows, g, stream, chained);
+    default: return launch_param<__nv_bfloat16>(c, sums, rows, g, stream, chained);
   }
 }
 

@@ -83,7 +83,12 @@ size_t wave_workspace_bytes(const WaveGeom& g, int direction);
 cudaError_t launch_forward_wave(const FwdCall& c, const Plan& p, cudaStream_t stream);
 cudaError_t launch_backward_wave(const BwdCall& c, const Plan& p, cudaStream_t stream);
 // dgamma / dbeta from `rows` rows of per-channel (S1, S2) pairs (gn_bwd.cu)
-cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, int C, cudaStream_t stream);
+// `chained`: as a programmatic dependent of the kernel before it in the stream
+cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, int C, cudaStream_t stream,
+                               bool chained = false);
+// GNB200_CHAIN != 0 (the default): the kernels of a multi-kernel call are launched as programmatic
+// dependents of their predecessors
+bool chain_enabled();
 
 // channels-first tensors (gn_nchw.cu)
 bool nchw_shape_supported(int64_t N, int64_t R, int64_t C, int64_t G);

@@ -62,6 +62,7 @@ template <typename T, int VE>
 __global__ void __launch_bounds__(kThreads)
     gn_nchw_stats_kernel(const T* __restrict__ x, float4* __restrict__ part, const NchwGeom g) {
   __shared__ float scratch[kThreads / 32];
+  grid_dep_launch_dependents();  // the apply kernel may take its place; it waits for this grid's partials
   const long long slab = blockIdx.x / g.chunks;
   const int chunk = (int)(blockIdx.x - slab * g.chunks);
   const long long v0 = (long long)chunk * g.chunk_vecs;
@@ -136,6 +137,7 @@ __global__ void __launch_bounds__(kThreads)
   __shared__ float s_stat[2];
   const long long slab = blockIdx.x / g.chunks;
   const int chunk = (int)(blockIdx.x - slab * g.chunks);
+  grid_dep_wait();  // the statistics kernel's partials
   if (threadIdx.x < 32) {
     float mu, rs;
     merge_partials(part + slab * g.chunks, g.chunks, eps, mu, rs);
@@ -194,6 +196,7 @@ __global__ void __launch_bounds__(kThreads)
                           const T* __restrict__ beta, const float* __restrict__ mean_in,
                           const float* __restrict__ rstd_in, float2* __restrict__ tp, long long pieces,
                           const NchwGeom g) {
+  grid_dep_launch_dependents();  // the kernels after this one wait for this grid before they read its sums
   const int lane = threadIdx.x & 31;
   const long long piece = (long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
   if (piece >= pieces) return;
@@ -256,6 +259,8 @@ __global__ void __launch_bounds__(128)
     gn_nchw_finalize_kernel(const float2* __restrict__ tp, const T* __restrict__ gamma, float2* __restrict__ sums,
                             float* __restrict__ coef, const NchwGeom g) {
   __shared__ float scratch[4];
+  grid_dep_launch_dependents();
+  grid_dep_wait();  // the reduce kernel's sums
   const int n = blockIdx.x / g.G, grp = blockIdx.x - n * g.G;
   float w1 = 0.f, w2 = 0.f;
   for (int cl = threadIdx.x; cl < g.D; cl += 128) {
@@ -297,6 +302,7 @@ __global__ void __launch_bounds__(kThreads)
   const float nmr = -mean_in[(size_t)n * g.G + grp] * rs;
   const float ga = load_param<T>(gamma, c), be = load_param<T>(beta, c);
   const float ag = rs * ga;
+  grid_dep_wait();  // the finalize kernel's coefficients (everything above is the caller's)
   const float nb = -rs * coef[((size_t)n * g.G + grp) * 2 + 1];
   const float na = -rs * coef[((size_t)n * g.G + grp) * 2];
   const long long v0 = (long long)j * g.piece_vecs;
@@ -401,9 +407,8 @@ cudaError_t fwd_t(const FwdCall& c, const NchwGeom& g, cudaStream_t stream) {
   gn_nchw_stats_kernel<T, VE><<<grid, kThreads, 0, stream>>>((const T*)c.x, part, g);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  gn_nchw_apply_kernel<T, VE, ACT><<<grid, kThreads, 0, stream>>>((const T*)c.x, (const T*)c.gamma, (const T*)c.beta, part,
-                                                                 (T*)c.y, c.mean, c.rstd, c.eps, g);
-  return cudaGetLastError();
+  return launch_chained(gn_nchw_apply_kernel<T, VE, ACT>, grid, dim3(kThreads), 0, stream, chain_enabled(), (const T*)c.x,
+                        (const T*)c.gamma, (const T*)c.beta, part, (T*)c.y, c.mean, c.rstd, c.eps, g);
 }
 
 template <typename T, int VE, int ACT>
@@ -419,14 +424,14 @@ cudaError_t bwd_t(const BwdCall& c, const NchwGeom& g, cudaStream_t stream) {
                                                                    (const T*)c.beta, c.mean, c.rstd, tp, pieces, g);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  gn_nchw_finalize_kernel<T><<<(unsigned)(g.N * g.G), 128, 0, stream>>>(tp, (const T*)c.gamma, sums, coef, g);
-  err = cudaGetLastError();
+  const bool chain = chain_enabled();
+  err = launch_chained(gn_nchw_finalize_kernel<T>, (unsigned)(g.N * g.G), dim3(128), 0, stream, chain, tp, (const T*)c.gamma,
+                       sums, coef, g);
   if (err != cudaSuccess) return err;
-  err = launch_param_grads(c, reinterpret_cast<const float*>(sums), g.N, g.C, stream);
+  err = launch_param_grads(c, reinterpret_cast<const float*>(sums), g.N, g.C, stream, chain);
   if (err != cudaSuccess) return err;
-  gn_nchw_dx_kernel<T, VE, ACT><<<grid, kThreads, 0, stream>>>((const T*)c.dy, (const T*)c.x, (const T*)c.gamma,
-                                                               (const T*)c.beta, c.mean, c.rstd, coef, (T*)c.dx, pieces, g);
-  return cudaGetLastError();
+  return launch_chained(gn_nchw_dx_kernel<T, VE, ACT>, grid, dim3(kThreads), 0, stream, chain, (const T*)c.dy, (const T*)c.x,
+                        (const T*)c.gamma, (const T*)c.beta, c.mean, c.rstd, coef, (T*)c.dx, pieces, g);
 }
 
 template <typename T, int VE>

@@ -429,9 +429,11 @@ static bool make_plan_inner(int64_t N, int64_t R, int64_t C, int64_t G, int dtyp
 bool make_plan(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction, bool aligned16, Plan* plan) {
   if (!make_plan_inner(N, R, C, G, dtype, direction, aligned16, plan)) return false;
   // GNB200_CHAIN = 0: every kernel of a call waits for the whole previous kernel (plain stream order)
-  plan->chain = env_int("GNB200_CHAIN", 1) != 0;
+  plan->chain = chain_enabled();
   return true;
 }
+
+bool chain_enabled() { return env_int("GNB200_CHAIN", 1) != 0; }
 
 static bool make_plan_inner(int64_t N, int64_t R, int64_t C, int64_t G, int dtype, int direction, bool aligned16, Plan* plan) {
   if (N < 1 || R < 1 || C < 1 || G < 1 || C % G != 0) return false;

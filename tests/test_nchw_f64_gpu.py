@@ -72,6 +72,19 @@ def test_nchw_kernels_against_oracle(nt, shape, dt):
             assert torch.equal(out[k], again[k]), k
 
 
+def test_nchw_chained_launches_change_no_bit(nt, monkeypatch):
+    """GNB200_CHAIN=0 (plain stream order) and the default (programmatic dependent launches) give the same bits."""
+    x, ga, be, dy = O.make_inputs(2, 128, (32, 32), torch.float16, seed=3)
+    outs = []
+    for chain in ("1", "0"):
+        monkeypatch.setenv("GNB200_CHAIN", chain)
+        for _ in range(3):
+            out = run_nchw(nt, x, ga, be, dy, 32, 1e-5, "silu")
+        outs.append(out)
+    for k in ("y", "dx", "mean", "rstd", "dparam"):
+        assert torch.equal(outs[0][k], outs[1][k]), k
+
+
 @pytest.mark.parametrize("act", O.ACT_NAMES)
 def test_nchw_every_activation(nt, act):
     for dt in ("float32", "float16", "bfloat16"):

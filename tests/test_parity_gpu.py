@@ -97,6 +97,25 @@ def test_baseline_configs_against_oracle(nt, case, path, monkeypatch):
     assert O.rel_err(out["dparam"][1], want["dbeta"]) <= O.TOLERANCE[dtype]
 
 
+@pytest.mark.parametrize("path", ["auto", "twopass"])
+def test_chained_launches_change_no_bit(nt, path, monkeypatch):
+    """Kernels after the first of a call are launched as programmatic dependents of their predecessor
+    (they may become resident early and wait for it on the device).  With GNB200_CHAIN=0 they are
+    launched in plain stream order; the results must be the same bits, also when calls follow each
+    other back to back."""
+    if path != "auto":
+        monkeypatch.setenv("GNB200_FORCE_PATH", path)
+    x, ga, be, dy, G, eps, act, dtype = _case_inputs(CFG4[0])
+    outs = []
+    for chain in ("1", "0"):
+        monkeypatch.setenv("GNB200_CHAIN", chain)
+        for _ in range(3):
+            out = run_cabi(nt, x, ga, be, dy, G, eps, act)
+        outs.append(out)
+    for k in ("y", "dx", "mean", "rstd", "dparam", "dgamma", "dbeta"):
+        assert torch.equal(outs[0][k], outs[1][k]), k
+
+
 @pytest.mark.parametrize("act", O.ACT_NAMES)
 @pytest.mark.parametrize("dt", ["float32", "float16", "bfloat16"])
 def test_every_activation_and_dtype(nt, act, dt):
