@@ -259,10 +259,18 @@ def workload_config(wl, gpus):
 class DeviceProblem:
     """Preallocated buffers for one workload on the current device, rotated to defeat L2 reuse."""
 
-    def __init__(self, wl, n_local, x, ga, be, dy, min_total_bytes=1 << 30):
+    def __init__(self, wl, n_local, x, ga, be, dy, min_total_bytes=1 << 30, peer=None, peer_mode="peer"):
         from channels_last_groupnorm_b200 import _native as nt
 
         self.nt = nt
+        # dist.PeerExchange.  peer_mode "peer-inline": the backward posts [dgamma | dbeta] into the ranks' exchange
+        # buffers from its own kernels and collects the sums in the same call; "peer": posts, and collects one step
+        # later; "peer-side": plain backward, then the library's exchange kernel on a side stream (where the NCCL
+        # variant runs its all-reduce)
+        self.peer = peer
+        self.peer_mode = peer_mode
+        self.peer_inline = peer_mode == "peer-inline"
+        self.peer_table = nt._peer_table(peer.peer_ptrs) if peer is not None else None
         N, C, H, W, G, eps, act, dt, xs, bwd, dist = WORKLOADS[wl]
         self.n, self.C, self.R, self.G, self.eps, self.act, self.bwd = n_local, C, H * W, G, eps, ACT_CODES[act], bwd
         self.dtype = DT[dt]
@@ -303,16 +311,46 @@ class DeviceProblem:
                                      self.G, self.eps, self.act, self.code, s["y"].data_ptr(), self.mean.data_ptr(),
                                      self.rstd.data_ptr(), self.ws_f.data_ptr() if self.wf else None, self.wf, stream))
 
-    def bwd_(self, i, stream, typed, slot=0):
+    def bwd_(self, i, stream, typed, slot=0, peer=False):
         s = self.sets[i % self.nsets]
         lib = self.nt.lib
         dparam = self.dparams[slot]
+        if peer and self.peer_inline:
+            self.nt.check(lib.gnb200_bwd_peer(s["dy"].data_ptr(), s["x"].data_ptr(), self.ga.data_ptr(), self.be.data_ptr(),
+                                              self.mean.data_ptr(), self.rstd.data_ptr(), self.n, self.R, self.C, self.G,
+                                              self.act, self.code, s["dx"].data_ptr(), dparam.data_ptr(),
+                                              self.dgamma.data_ptr() if typed else None,
+                                              self.dbeta.data_ptr() if typed else None,
+                                              self.ws_b.data_ptr() if self.wb else None, self.wb,
+                                              self.peer_table, self.peer.rank, self.peer.world, stream))
+            return
+        if peer:
+            self.nt.check(lib.gnb200_bwd_peer_push(s["dy"].data_ptr(), s["x"].data_ptr(), self.ga.data_ptr(),
+                                                   self.be.data_ptr(), self.mean.data_ptr(), self.rstd.data_ptr(), self.n,
+                                                   self.R, self.C, self.G, self.act, self.code, s["dx"].data_ptr(),
+                                                   dparam.data_ptr(), self.ws_b.data_ptr() if self.wb else None, self.wb,
+                                                   self.peer_table, self.peer.rank, self.peer.world, stream))
+            return
         self.nt.check(lib.gnb200_bwd(s["dy"].data_ptr(), s["x"].data_ptr(), self.ga.data_ptr(), self.be.data_ptr(),
                                      self.mean.data_ptr(), self.rstd.data_ptr(), self.n, self.R, self.C, self.G,
                                      self.act, self.code, s["dx"].data_ptr(), dparam.data_ptr(),
                                      self.dgamma.data_ptr() if typed else None,
                                      self.dbeta.data_ptr() if typed else None,
                                      self.ws_b.data_ptr() if self.wb else None, self.wb, stream))
+
+
+def _collect(prob, slot, stream):
+    """Sums over the ranks of the oldest posted gradients -> prob.dparams[slot] and the typed copies."""
+    prob.nt.check(prob.nt.lib.gnb200_peer_collect(prob.dparams[slot].data_ptr(), prob.dgdb[slot][0].data_ptr(),
+                                                  prob.dgdb[slot][1].data_ptr(), prob.C, prob.code, prob.peer_table,
+                                                  prob.peer.rank, prob.peer.world, stream))
+
+
+def _allreduce_peer(prob, slot, stream):
+    """prob.dparams[slot] (this rank's sums) -> sums over the ranks, in place, plus the typed copies."""
+    prob.nt.check(prob.nt.lib.gnb200_allreduce_param_grads(prob.dparams[slot].data_ptr(), prob.dgdb[slot][0].data_ptr(),
+                                                           prob.dgdb[slot][1].data_ptr(), prob.C, prob.code,
+                                                           prob.peer_table, prob.peer.rank, prob.peer.world, stream))
 
 
 def _capture(fn, count):
@@ -361,6 +399,7 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
 
     side = torch.cuda.Stream() if world > 1 else None
     done = [None, None]  # per slot: event after which its all-reduced gradients are complete
+    pending = [None]     # peer exchange: slot whose gradients are posted but not collected yet
 
     def one(i):
         """Forward, backward and - on more than one rank - the all-reduce of the packed fp32
@@ -369,7 +408,17 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
         gradient all-reduce overlaps the rest of a backward pass in training."""
         b = i & 1
         prob.fwd(i, cur())
-        if prob.bwd:
+        if prob.bwd and prob.peer is not None and prob.peer_mode != "peer-side":
+            # the kernels of the backward post the gradients into every rank's exchange buffer (no library
+            # collective); their sums are collected inside the same call, or - the default - one step later,
+            # when every rank's contribution has long arrived, as a gradient all-reduce is awaited only before
+            # the optimizer step
+            prob.bwd_(i, cur(), typed=True, slot=b, peer=True)
+            if not prob.peer_inline:
+                if pending[0] is not None:
+                    _collect(prob, pending[0], cur())
+                pending[0] = b
+        elif prob.bwd:
             if world > 1 and done[b] is not None:
                 torch.cuda.current_stream().wait_event(done[b])  # slot b is free again
             prob.bwd_(i, cur(), typed=(world == 1), slot=b)
@@ -378,13 +427,20 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
                 ready.record(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
                     side.wait_event(ready)
-                    dist.all_reduce(prob.dparams[b])
-                    prob.dgdb[b].copy_(prob.dparams[b])
+                    if prob.peer is not None:   # the library's own exchange kernel instead of NCCL + cast
+                        _allreduce_peer(prob, b, side.cuda_stream)
+                    else:
+                        dist.all_reduce(prob.dparams[b])
+                        prob.dgdb[b].copy_(prob.dparams[b])
                     done[b] = torch.cuda.Event()
                     done[b].record(side)
 
     def join():
-        """Makes the current stream wait for the collectives still running on the side stream."""
+        """Makes the current stream wait for the collectives still running on the side stream (NCCL), or
+        collects the gradients posted last (peer exchange)."""
+        if pending[0] is not None:
+            _collect(prob, pending[0], cur())
+            pending[0] = None
         for b in (0, 1):
             if done[b] is not None:
                 torch.cuda.current_stream().wait_event(done[b])
@@ -454,7 +510,14 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
         evs[i][0].record()
         prob.fwd(warmup + i, cur())
         evs[i][1].record()
-        if prob.bwd:
+        if prob.bwd and prob.peer is not None and prob.peer_mode != "peer-side":
+            prob.bwd_(warmup + i, cur(), typed=True, slot=b, peer=True)
+            evs[i][2].record()
+            if not prob.peer_inline:
+                if pending[0] is not None:
+                    _collect(prob, pending[0], cur())
+                pending[0] = b
+        elif prob.bwd:
             if world > 1 and done[b] is not None:
                 torch.cuda.current_stream().wait_event(done[b])
             prob.bwd_(warmup + i, cur(), typed=(world == 1), slot=b)
@@ -464,8 +527,11 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
                 ready.record(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
                     side.wait_event(ready)
-                    dist.all_reduce(prob.dparams[b])
-                    prob.dgdb[b].copy_(prob.dparams[b])
+                    if prob.peer is not None:
+                        _allreduce_peer(prob, b, side.cuda_stream)
+                    else:
+                        dist.all_reduce(prob.dparams[b])
+                        prob.dgdb[b].copy_(prob.dparams[b])
                     done[b] = torch.cuda.Event()
                     done[b].record(side)
     join()
@@ -483,7 +549,7 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
 run_device_steps.eager_per_step = None
 
 
-def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
+def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier, peer=None):
     """Public API (module + autograd) with host buffers; every step copies its x and dy from pinned
     host memory and its y, dx, dgamma, dbeta back, all inside the timed region.
 
@@ -499,7 +565,7 @@ def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier):
     dtype = DT[dt]
     dev = torch.device("cuda", torch.cuda.current_device())
     m = pkg.GN_NHWC(G, C, activation=act, eps=eps,
-                    process_group=(dist.group.WORLD if world > 1 else None)).to(dev).to(dtype)
+                    process_group=(peer if peer is not None else dist.group.WORLD if world > 1 else None)).to(dev).to(dtype)
     with torch.no_grad():
         m.weight.copy_(ga)
         m.bias.copy_(be)
@@ -590,7 +656,7 @@ def _rel_err(a, b):
     return float((a - b).abs().max() / max(1.0, float(b.abs().max())))
 
 
-def run_parity_check(wl, rank, world, x_full, ga, be, dy_full, lo, hi):
+def run_parity_check(wl, rank, world, x_full, ga, be, dy_full, lo, hi, peer=None):
     """Value check of the sharded run on this hardware, outside every timed region.
 
     Every rank runs the full global batch once on its own GPU, then its shard; the shard's y and dx must
@@ -627,12 +693,35 @@ def run_parity_check(wl, rank, world, x_full, ga, be, dy_full, lo, hi):
         dx_s, dparam_s, _, _ = nt.bwd_raw(dys_, xs_, gad, bed, mean_s, rstd_s, G, code)
         bitwise = bitwise and bool(torch.equal(dx_s, dx_f[lo:hi]))
         errs["dx_shard_vs_full"] = _rel_err(dx_s, dx_f[lo:hi])
+        if peer is not None:
+            # the in-kernel exchange: the summed gradients must equal the full-batch ones within tolerance, the
+            # NCCL-summed ones closely, and be the same bits on every rank (they are added in rank order)
+            _, dparam_p = nt.bwd_peer_raw(dys_, xs_, gad, bed, mean_s, rstd_s, G, code, peer.peer_ptrs, peer.rank)
+            errs["dparam_peer_vs_full"] = _rel_err(dparam_p, dparam_f)
+            first = dparam_p.clone()
+            dist.broadcast(first, src=0)
+            if not torch.equal(first, dparam_p):
+                ok = False
+                errs["dparam_peer_differs_between_ranks"] = _rel_err(dparam_p, first) + 1.0
+            again = peer.allreduce_(dparam_s.clone())   # the exchange alone, on the local gradients
+            errs["dparam_peer_standalone_vs_fused"] = _rel_err(again, dparam_p)
+            # push and collect apart, two pushes outstanding (both slot parities), then a third round that has to
+            # see the acknowledgements of the first: every collect must return the bits of the one-call form
+            worst = 0.0
+            for _ in range(2):
+                locals_ = [nt.bwd_peer_raw(dys_, xs_, gad, bed, mean_s, rstd_s, G, code, peer.peer_ptrs, peer.rank,
+                                           collect=False)[1] for _ in range(2)]
+                worst = max(worst, max(_rel_err(t, dparam_s) for t in locals_))   # pushing leaves the local sums
+                for _ in range(2):
+                    got = peer.collect_(torch.empty_like(dparam_p))
+                    worst = max(worst, 0.0 if torch.equal(got, dparam_p) else 1.0 + _rel_err(got, dparam_p))
+            errs["dparam_peer_push_collect_vs_fused"] = worst
         if world > 1:
             dist.all_reduce(dparam_s)
         errs["dparam_allreduced_vs_full"] = _rel_err(dparam_s, dparam_f)
         # the public module with process_group: one step on the shard
         m = pkg.GN_NHWC(G, C, activation=act, eps=eps,
-                        process_group=(dist.group.WORLD if world > 1 else None)).to(dev).to(dtype)
+                        process_group=(peer if peer is not None else dist.group.WORLD if world > 1 else None)).to(dev).to(dtype)
         with torch.no_grad():
             m.weight.copy_(ga)
             m.bias.copy_(be)
@@ -728,7 +817,25 @@ def _device_arm(args):
     dtype = DT[dt]
     x, ga, be, dy = make_inputs(N, C, H, W, dtype, 0, xs, dist_name)  # the global seeded batch
     lo, hi = shard_bounds(N, rank, world)
-    parity = None if args.no_parity else run_parity_check(wl, rank, world, x, ga, be, dy, lo, hi)
+    # more than one rank: the parameter gradients are summed inside the backward kernels over peer-mapped
+    # exchange buffers (--collective peer, the default where symmetric memory can be set up) or by an NCCL
+    # all-reduce on a side stream (--collective nccl)
+    peer, collective = None, ("none" if world == 1 else "nccl")
+    if world > 1 and bwd and args.collective in ("auto", "peer", "peer-inline", "peer-side"):
+        try:
+            from channels_last_groupnorm_b200.dist import PeerExchange
+            peer = PeerExchange(C)
+            collective = args.collective if args.collective != "auto" else "peer"
+        except Exception as exc:
+            if args.collective != "auto":
+                raise
+            sys.stderr.write("bench: no peer exchange (%s); using NCCL\n" % str(exc)[:300])
+        # the choice must be the same on every rank
+        flag = torch.tensor([1 if peer is not None else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            peer, collective = None, "nccl"
+    parity = None if args.no_parity else run_parity_check(wl, rank, world, x, ga, be, dy, lo, hi, peer)
     torch.cuda.empty_cache()
     x, dy = x[lo:hi].contiguous(), dy[lo:hi].contiguous()
     n_local = hi - lo
@@ -736,14 +843,14 @@ def _device_arm(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    prob = DeviceProblem(wl, n_local, x, ga, be, dy)
+    prob = DeviceProblem(wl, n_local, x, ga, be, dy, peer=peer, peer_mode=collective)
     per_step, fwd_t, bwd_t, wall, issue_mode = run_device_steps(prob, args.steps, args.warmup, world, barrier,
                                                                 use_graph=not args.no_graph)
     clocks = sampler.stop(*wall) if rank == 0 else None
     del prob
     torch.cuda.empty_cache()
     e2e_steps = max(3, min(args.steps, 20))
-    e2e_t, h2d, d2h = run_e2e(wl, n_local, x, ga, be, dy, e2e_steps, max(3, min(args.warmup, 5)), world, barrier)
+    e2e_t, h2d, d2h = run_e2e(wl, n_local, x, ga, be, dy, e2e_steps, max(3, min(args.warmup, 5)), world, barrier, peer)
 
     if rank == 0:
         esize = x.element_size()
@@ -770,7 +877,7 @@ def _device_arm(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
             "us_per_call": per_step * 1e6, "us_fwd": fwd_t * 1e6, "us_bwd": bwd_t * 1e6,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DT_SHORT[dt],
-            "data": "synthetic", "config": workload_config(wl, world),
+            "data": "synthetic", "config": dict(workload_config(wl, world), collective=collective),
             "frac_of_hbm_peak": alg_global / per_step / 1e9 / (peak * world),
             "roofline": roof, "roofline_fwd": roof_fwd,
             "e2e": {"value": alg_global / e2e_t / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
@@ -1007,6 +1114,11 @@ def main():
     ap.add_argument("--no-nchw", action="store_true", help="sweep: skip the channels-first entry points")
     ap.add_argument("--no-parity", action="store_true", help="skip the value check that precedes the timed runs")
     ap.add_argument("--no-shapes", action="store_true", help="skip the table of VAE / SD shapes (1 GPU only)")
+    ap.add_argument("--collective", default="auto", choices=["auto", "peer", "peer-inline", "peer-side", "nccl"],
+                    help="more than one GPU: the backward kernels post the parameter gradients into the ranks' exchange "
+                         "buffers over peer memory and the sums are collected one step later (peer, the default where "
+                         "symmetric memory can be set up) or inside the same call (peer-inline); or an NCCL all-reduce "
+                         "on a side stream (nccl)")
     ap.add_argument("--no-graph", action="store_true", help="time the eager loop instead of a CUDA-graph replay")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--profile", type=int, default=0, metavar="CALLS",

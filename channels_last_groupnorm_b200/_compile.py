@@ -38,6 +38,11 @@ def _bwd_f32_fake(dy, X, weight, bias, means, rstds, G, act):
     return _like(X), X.new_empty((2, X.shape[1]), dtype=_stats_dtype(X))
 
 
+@torch.library.register_fake("gnb200::bwd_f32_peer")
+def _bwd_f32_peer_fake(dy, X, weight, bias, means, rstds, G, act, peer_ptrs, rank):
+    return _like(X), X.new_empty((2, X.shape[1]), dtype=_stats_dtype(X))
+
+
 def _fwd_setup_context(ctx, inputs, output):
     X, weight, bias, G, eps, act = inputs
     _, means, rstds = output

@@ -47,6 +47,18 @@ lib.gnb200_bwd.restype = ctypes.c_int
 lib.gnb200_bwd.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                            _c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
                            _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_size_t, _c_void_p]
+lib.gnb200_peer_exchange_bytes.restype = ctypes.c_size_t
+lib.gnb200_peer_exchange_bytes.argtypes = [_c_int64, ctypes.c_int]
+lib.gnb200_bwd_peer.restype = ctypes.c_int
+lib.gnb200_bwd_peer.argtypes = lib.gnb200_bwd.argtypes[:-1] + [ctypes.POINTER(_c_void_p), ctypes.c_int, ctypes.c_int,
+                                                                _c_void_p]
+lib.gnb200_bwd_peer_push.restype = ctypes.c_int
+lib.gnb200_bwd_peer_push.argtypes = lib.gnb200_bwd.argtypes[:14] + [_c_void_p, ctypes.c_size_t, ctypes.POINTER(_c_void_p),
+                                                                    ctypes.c_int, ctypes.c_int, _c_void_p]
+for _name in ("gnb200_allreduce_param_grads", "gnb200_peer_collect"):
+    getattr(lib, _name).restype = ctypes.c_int
+    getattr(lib, _name).argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int64, ctypes.c_int,
+                                    ctypes.POINTER(_c_void_p), ctypes.c_int, ctypes.c_int, _c_void_p]
 lib.gnb200_bwd_static_scratch.restype = ctypes.c_int
 lib.gnb200_bwd_static_scratch.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                           _c_int64, _c_int64, _c_int64, _c_int64, ctypes.c_int, ctypes.c_int,
@@ -169,6 +181,60 @@ def bwd_raw(dy_nhwc, x_nhwc, gamma, beta, mean, rstd, G, act, dx=None, workspace
                          _ptr(workspace) if need else None,
                          workspace.numel() if (need and workspace is not None) else 0, s))
     return dx, dparam, dgamma, dbeta
+
+
+def peer_exchange_bytes(num_channels, world):
+    """Bytes of one rank's exchange buffer for gnb200_bwd_peer / gnb200_allreduce_param_grads."""
+    return int(lib.gnb200_peer_exchange_bytes(int(num_channels), int(world)))
+
+
+def _peer_table(peer_ptrs):
+    return (_c_void_p * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
+
+
+def bwd_peer_raw(dy_nhwc, x_nhwc, gamma, beta, mean, rstd, G, act, peer_ptrs, rank, dx=None, dparam=None,
+                 workspace=None, stream=None, collect=True):
+    """Calls gnb200_bwd_peer (collect=True: [dgamma | dbeta] summed over the ranks inside the call) or
+    gnb200_bwd_peer_push (collect=False: this rank's sums are posted; peer_collect_raw sums them later).
+    peer_ptrs[q] = address of rank q's exchange buffer in this process.  Returns (dx, dparam_f32[2, C])."""
+    N, R, C = x_nhwc.shape
+    code = DTYPE_CODES[x_nhwc.dtype]
+    if dx is None:
+        dx = torch.empty_like(x_nhwc)
+    if dparam is None:
+        dparam = torch.empty((2, C), device=x_nhwc.device, dtype=torch.float32)
+    need = lib.gnb200_bwd_workspace_bytes(N, R, C, G, code)
+    if workspace is None and need:
+        workspace = torch.empty(need, device=x_nhwc.device, dtype=torch.uint8)
+    s = torch.cuda.current_stream(x_nhwc.device).cuda_stream if stream is None else stream
+    ws_args = (_ptr(workspace) if need else None, workspace.numel() if (need and workspace is not None) else 0)
+    if collect:
+        check(lib.gnb200_bwd_peer(_ptr(dy_nhwc), _ptr(x_nhwc), _ptr(gamma), _ptr(beta), _ptr(mean), _ptr(rstd),
+                                  N, R, C, G, int(act), code, _ptr(dx), _ptr(dparam), None, None, *ws_args,
+                                  _peer_table(peer_ptrs), int(rank), len(peer_ptrs), s))
+    else:
+        check(lib.gnb200_bwd_peer_push(_ptr(dy_nhwc), _ptr(x_nhwc), _ptr(gamma), _ptr(beta), _ptr(mean), _ptr(rstd),
+                                       N, R, C, G, int(act), code, _ptr(dx), _ptr(dparam), *ws_args,
+                                       _peer_table(peer_ptrs), int(rank), len(peer_ptrs), s))
+    return dx, dparam
+
+
+def peer_collect_raw(dparam, peer_ptrs, rank, stream=None):
+    """Calls gnb200_peer_collect: dparam (float32 [2, C]) receives the sums over the ranks of the oldest push
+    that has not been collected yet."""
+    C = dparam.shape[1]
+    s = torch.cuda.current_stream(dparam.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_peer_collect(_ptr(dparam), None, None, C, 0, _peer_table(peer_ptrs), int(rank), len(peer_ptrs), s))
+    return dparam
+
+
+def allreduce_param_grads_peer_raw(dparam, peer_ptrs, rank, stream=None):
+    """Calls gnb200_allreduce_param_grads in place on a float32 [2, C] buffer."""
+    C = dparam.shape[1]
+    s = torch.cuda.current_stream(dparam.device).cuda_stream if stream is None else stream
+    check(lib.gnb200_allreduce_param_grads(_ptr(dparam), None, None, C, 0, _peer_table(peer_ptrs), int(rank),
+                                           len(peer_ptrs), s))
+    return dparam
 
 
 def bwd_static_scratch_raw(dy_nhwc, x_nhwc, gamma, beta, mean, rstd, G, act, dx, dparam, dgamma, dbeta, stream=None):

@@ -22,7 +22,7 @@ CORE_LIB = os.path.join(LIB_DIR, "libgnb200.so")
 TORCH_LIB = os.path.join(LIB_DIR, "gnb200_torch.so")
 
 CUDA_SOURCES = ["gn_fwd.cu", "gn_bwd.cu", "gn_wave.cu", "gn_nchw.cu", "gn_f64.cu", "gn_plan.cu", "gn_capi.cu", "gn_static_scratch.cu"]
-CUDA_HEADERS = ["gn_common.cuh", "gn_math.cuh", "gn_kernels.h", os.path.join(INCLUDE_DIR, "gnb200.h")]
+CUDA_HEADERS = ["gn_common.cuh", "gn_math.cuh", "gn_peer.cuh", "gn_kernels.h", os.path.join(INCLUDE_DIR, "gnb200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -93,11 +93,6 @@ __device__ __forceinline__ void stream_bwd_sums(const T* __restrict__ gx, const 
 }
 
 constexpr int kXRing = 4;  // x rows in flight per thread in the fused backward kernel
-// All dy rows of a thread are issued before its loop starts (every row has its own tile slot), so
-// that the loop issues only the x refill.
-constexpr bool kDyUpfront = false;
-// Phase 2 reads x (L2 hits) straight into registers, four rows at a time, instead of through the ring.
-constexpr bool kDxDirect = false;
 
 // Phase 1 of the fused path.  dy rows are copied straight into the shared-memory tile, x rows go
 // through a kXRing-deep shared-memory ring (cp.async, one commit group per row, kXRing rows in
@@ -146,9 +141,6 @@ __device__ __forceinline__ BwdPipe<T> tile_fill_start(const T* __restrict__ gx, 
         p.wd += sstep_bytes;
         ++p.dy_issued;
       }
-      if constexpr (kDyUpfront) {  // dy rows 2 kXRing + d, 3 kXRing + d, ... ride in this group as well
-        for (int r = 2 * kXRing + d; r < iters; r += kXRing) cp_async16(sd + r * sstep_bytes, gd + (size_t)r * gstep_elems);
-      }
       cp_async_commit();
     }
   }
@@ -171,7 +163,6 @@ __device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep
     }
     uint32_t wd = pipe.wd;
     int dy_issued = pipe.dy_issued;
-    (void)wd, (void)dy_issued, (void)gd;
     uint32_t rd = sd;
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kXRing - 1>();
@@ -181,13 +172,11 @@ __device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep
         cp_async16(slot, gx);
         gx += gstep_elems;
       }
-      if constexpr (!kDyUpfront) {
-        if (dy_issued < iters) {
-          cp_async16(wd, gd);
-          gd += gstep_elems;
-          wd += sstep_bytes;
-          ++dy_issued;
-        }
+      if (dy_issued < iters) {
+        cp_async16(wd, gd);
+        gd += gstep_elems;
+        wd += sstep_bytes;
+        ++dy_issued;
       }
       cp_async_commit();
       if constexpr (kRaw) {
@@ -229,7 +218,7 @@ __device__ __forceinline__ void tile_fill_bwd_sums(BwdPipe<T> pipe, size_t gstep
 template <typename T, int VE>
 __device__ __forceinline__ void tile_bwd_dx_start(const T* __restrict__ gx, size_t gstep_elems, uint32_t ring,
                                                   uint32_t ring_stride, int iters) {
-  if constexpr (sizeof(T) * VE == 16 && !kDxDirect) {
+  if constexpr (sizeof(T) * VE == 16) {
 #pragma unroll
     for (int d = 0; d < kXRing; ++d) {
       if (d < iters) {
@@ -267,41 +256,6 @@ __device__ __forceinline__ void tile_bwd_dx(const T* __restrict__ gx, uint32_t r
       c2[e] = fmaf(nb[e], L.nmr[e], na[e]);
     }
     T* gp = gdst;
-    if constexpr (kDxDirect) {
-      constexpr int U = 4;
-      for (int i = 0; i < iters; i += U) {
-        uint4 xv[U], dv[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (i + u < iters) {
-            xv[u] = ldg128(gx + (size_t)u * gstep_elems);
-            dv[u] = lds128(sd + u * sstep_bytes);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (i + u < iters) {
-            float fx[VE], fd[VE];
-            unpack16<T, VE>(xv[u], fx);
-            unpack16<T, VE>(dv[u], fd);
-#pragma unroll
-            for (int e = 0; e < VE; ++e) {
-              if constexpr (kFold) {
-                fx[e] = fmaf(ag[e], fd[e], fmaf(c1[e], fx[e], c2[e]));
-              } else {
-                const float xh = fmaf(fx[e], L.r[e], L.nmr[e]);
-                fx[e] = fmaf(ag[e], fd[e], fmaf(nb[e], xh, na[e]));
-              }
-            }
-            stg128(gp + (size_t)u * gstep_elems, pack16<T, VE>(fx));
-          }
-        }
-        gx += (size_t)U * gstep_elems;
-        gp += (size_t)U * gstep_elems;
-        sd += U * sstep_bytes;
-      }
-      return;
-    }
     gx += (size_t)min(iters, kXRing) * gstep_elems;  // tile_bwd_dx_start has issued these rows
     for (int i = 0; i < iters; ++i) {
       cp_async_wait<kXRing - 1>();
@@ -578,7 +532,7 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
 template <typename T>
 __global__ void __launch_bounds__(1024)
     gn_bwd_param_kernel(const float* __restrict__ sums, int N, int C, float* __restrict__ dparam_f32,
-                        T* __restrict__ dgamma, T* __restrict__ dbeta) {
+                        T* __restrict__ dgamma, T* __restrict__ dbeta, const PeerExchange px) {
   constexpr int kLanes = 32;  // row lanes: block (32 channels, 32 row lanes)
   __shared__ float sm1[kLanes][33], sm2[kLanes][33];
   grid_dep_launch_dependents();
@@ -596,17 +550,51 @@ __global__ void __launch_bounds__(1024)
   sm1[threadIdx.y][threadIdx.x] = a1;
   sm2[threadIdx.y][threadIdx.x] = a2;
   __syncthreads();
-  if (threadIdx.y == 0 && c < C) {
+  if (threadIdx.y == 0) {  // one full warp: lane = channel of the block
     float t1 = 0.f, t2 = 0.f;
 #pragma unroll
     for (int j = 0; j < kLanes; ++j) {
       t1 += sm1[j][threadIdx.x];
       t2 += sm2[j][threadIdx.x];
     }
-    dparam_f32[c] = t2;      // dgamma
-    dparam_f32[C + c] = t1;  // dbeta
-    if (dgamma) dgamma[c] = store_param<T>(t2);
-    if (dbeta) dbeta[c] = store_param<T>(t1);
+    // data-parallel ranks of one node: post this rank's sums into every rank's exchange buffer and,
+    // unless the caller collects later, wait for the others' and add them up in rank order
+    if (px.world > 1) {
+      const bool pushed = peer_push_block(px, blockIdx.x, c < C, t2, t1);
+      if (px.collect) peer_collect_block(px, blockIdx.x, c < C, t2, t1);
+      else if (!pushed) t1 = t2 = __int_as_float(0x7fc00000);
+    }
+    if (c < C) {
+      dparam_f32[c] = t2;      // dgamma
+      dparam_f32[C + c] = t1;  // dbeta
+      if (dgamma) dgamma[c] = store_param<T>(t2);
+      if (dbeta) dbeta[c] = store_param<T>(t1);
+    }
+  }
+}
+
+// The exchange without the sums, on a [dgamma | dbeta] buffer of this rank: block (32), grid
+// ceil(C / 32).  push: post the buffer's values; collect: replace them by the sums over the ranks.
+template <typename T>
+__global__ void __launch_bounds__(32)
+    gn_param_exchange_kernel(int C, float* __restrict__ dparam_f32, T* __restrict__ dgamma, T* __restrict__ dbeta,
+                             bool push, bool collect, const PeerExchange px) {
+  grid_dep_wait();  // the kernel that wrote dparam_f32
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float dg = 0.f, db = 0.f;
+  if (push && c < C) {
+    dg = dparam_f32[c];
+    db = dparam_f32[C + c];
+  }
+  bool ok = true;
+  if (push) ok = peer_push_block(px, blockIdx.x, c < C, dg, db);
+  if (collect) peer_collect_block(px, blockIdx.x, c < C, dg, db);
+  if (!collect && !ok) dg = db = __int_as_float(0x7fc00000);
+  if (c < C && (collect || !ok)) {
+    dparam_f32[c] = dg;
+    dparam_f32[C + c] = db;
+    if (dgamma) dgamma[c] = store_param<T>(dg);
+    if (dbeta) dbeta[c] = store_param<T>(db);
   }
 }
 
@@ -769,8 +757,16 @@ static cudaError_t launch_param(const BwdCall& c, const float* sums, int rows, c
                                 bool chained) {
   const dim3 block(32, 32, 1);
   const unsigned blocks = (unsigned)((g.C + 31) / 32);
+  PeerExchange px = {};
+  if (c.peer) px = *c.peer;
   return launch_chained(gn_bwd_param_kernel<T>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
-                        (T*)c.dgamma, (T*)c.dbeta);
+                        (T*)c.dgamma, (T*)c.dbeta, px);
+}
+
+template <typename T>
+static cudaError_t launch_exchange(const BwdCall& c, int C, cudaStream_t stream, bool chained, bool push, bool collect) {
+  return launch_chained(gn_param_exchange_kernel<T>, (unsigned)((C + 31) / 32), dim3(32), 0, stream, chained, C,
+                        c.dparam_f32, (T*)c.dgamma, (T*)c.dbeta, push, collect, *c.peer);
 }
 
 template <typename T, int VE, int ACT, bool UNI>
@@ -862,8 +858,22 @@ cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, in
   }
 }
 
+cudaError_t launch_param_exchange(const BwdCall& c, int C, cudaStream_t stream, bool chained, bool push, bool collect) {
+  if (!c.peer || c.peer->world <= 1) return cudaSuccess;
+  switch (c.dtype) {
+    case 0: return launch_exchange<float>(c, C, stream, chained, push, collect);
+    case 1: return launch_exchange<__half>(c, C, stream, chained, push, collect);
+    default: return launch_exchange<__nv_bfloat16>(c, C, stream, chained, push, collect);
+  }
+}
+
 cudaError_t launch_backward(const BwdCall& c, const Plan& p, cudaStream_t stream) {
-  if (p.wave) return launch_backward_wave(c, p, stream);
+  if (p.wave) {
+    // the wave kernel finishes dgamma / dbeta itself; the exchange over the ranks follows it
+    const cudaError_t err = launch_backward_wave(c, p, stream);
+    if (err != cudaSuccess) return err;
+    return launch_param_exchange(c, p.wgeom.C, stream, false, true, c.peer && c.peer->collect);
+  }
   switch (c.dtype) {
     case 0: return launch_bwd_ve<float>(c, p, stream);
     case 1: return launch_bwd_ve<__half>(c, p, stream);

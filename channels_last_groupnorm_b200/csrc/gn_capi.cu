@@ -173,29 +173,130 @@ int gnb200_fwd(const void* x, const void* gamma, const void* beta, int64_t N, in
   return GNB200_OK;
 }
 
+// Fills *px from the caller's table of exchange buffers; `who` names the entry point in messages.
+static int make_peer_exchange(const void* const* peer_bufs, int rank, int world, int64_t C, bool collect, const char* who,
+                              gnb200::PeerExchange* px) {
+  if (world < 1 || world > gnb200::kMaxPeers || rank < 0 || rank >= world)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: rank %d of %d ranks (1 .. %d ranks supported)", who, rank, world,
+                gnb200::kMaxPeers);
+  if (C < 1 || C > (1 << 24)) return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: C = %lld", who, (long long)C);
+  *px = gnb200::PeerExchange{};
+  px->world = world;
+  px->rank = rank;
+  px->C = (int)C;
+  px->nblk = (int)((C + gnb200::kPeerBlock - 1) / gnb200::kPeerBlock);
+  px->collect = collect ? 1 : 0;
+  if (world == 1) return GNB200_OK;
+  if (!peer_bufs) return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: null table of exchange buffers", who);
+  for (int q = 0; q < world; ++q) {
+    if (!peer_bufs[q] || !aligned16(peer_bufs[q]))
+      return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: exchange buffer of rank %d is null or not 16-byte aligned (%p)", who, q,
+                  peer_bufs[q]);
+    px->base[q] = static_cast<char*>(const_cast<void*>(peer_bufs[q]));
+  }
+  const cudaError_t err = gnb200::wait_limit_for_device(&px->wait);
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(GNB200_ERR_CUDA, "%s: CUDA error: %s", who, cudaGetErrorString(err));
+  }
+  return GNB200_OK;
+}
+
+static int bwd_impl(const char* who, const void* dy, const void* x, const void* gamma, const void* beta, const float* mean,
+                    const float* rstd, int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype, void* dx,
+                    float* dgamma_dbeta_f32, void* dgamma, void* dbeta, void* workspace, size_t workspace_bytes,
+                    const gnb200::PeerExchange* px, void* stream) {
+  int rc = check_common(N, R, C, G, act, dtype);
+  if (rc != GNB200_OK) return rc;
+  if (!dy || !x || !gamma || !beta || !mean || !rstd || !dx || !dgamma_dbeta_f32)
+    return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: null tensor pointer", who);
+  gnb200::Plan plan;
+  const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(gamma) && aligned16(beta);
+  if (!gnb200::make_plan(N, R, C, G, dtype, 1, al, &plan))
+    return fail(GNB200_ERR_UNSUPPORTED, "%s: shape N=%lld R=%lld C=%lld G=%lld is outside the supported index range", who,
+                (long long)N, (long long)R, (long long)C, (long long)G);
+  if (plan.ws_bytes > 0 && (!workspace || workspace_bytes < plan.ws_bytes || !aligned16(workspace)))
+    return fail(GNB200_ERR_WORKSPACE, "%s: needs a 16-byte aligned workspace of %zu bytes, got %zu at %p", who,
+                plan.ws_bytes, workspace_bytes, workspace);
+  gnb200::BwdCall call = {dy, x, gamma, beta, mean, rstd, dx, dgamma_dbeta_f32, dgamma, dbeta, workspace, act, dtype};
+  call.peer = px;
+  const cudaError_t err = gnb200::launch_backward(call, plan, reinterpret_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(GNB200_ERR_CUDA, "%s: CUDA error: %s", who, cudaGetErrorString(err));
+  }
+  return GNB200_OK;
+}
+
 int gnb200_bwd(const void* dy, const void* x, const void* gamma, const void* beta, const float* mean,
                const float* rstd, int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype, void* dx,
                float* dgamma_dbeta_f32, void* dgamma, void* dbeta, void* workspace, size_t workspace_bytes,
                void* stream) {
-  int rc = check_common(N, R, C, G, act, dtype);
+  return bwd_impl("gnb200_bwd", dy, x, gamma, beta, mean, rstd, N, R, C, G, act, dtype, dx, dgamma_dbeta_f32, dgamma, dbeta,
+                  workspace, workspace_bytes, nullptr, stream);
+}
+
+size_t gnb200_peer_exchange_bytes(int64_t C, int world) {
+  if (C < 1 || C > (1 << 24) || world < 1 || world > gnb200::kMaxPeers) return 0;
+  return gnb200::peer_exchange_bytes(world, (int)C);
+}
+
+int gnb200_bwd_peer(const void* dy, const void* x, const void* gamma, const void* beta, const float* mean,
+                    const float* rstd, int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype, void* dx,
+                    float* dgamma_dbeta_f32, void* dgamma, void* dbeta, void* workspace, size_t workspace_bytes,
+                    const void* const* peer_bufs, int rank, int world, void* stream) {
+  gnb200::PeerExchange px;
+  const int rc = make_peer_exchange(peer_bufs, rank, world, C, true, "gnb200_bwd_peer", &px);
   if (rc != GNB200_OK) return rc;
-  if (!dy || !x || !gamma || !beta || !mean || !rstd || !dx || !dgamma_dbeta_f32)
-    return fail(GNB200_ERR_INVALID_ARGUMENT, "gnb200_bwd: null tensor pointer");
-  gnb200::Plan plan;
-  const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(gamma) && aligned16(beta);
-  if (!gnb200::make_plan(N, R, C, G, dtype, 1, al, &plan))
-    return fail(GNB200_ERR_UNSUPPORTED, "gnb200_bwd: shape N=%lld R=%lld C=%lld G=%lld is outside the supported index range",
-                (long long)N, (long long)R, (long long)C, (long long)G);
-  if (plan.ws_bytes > 0 && (!workspace || workspace_bytes < plan.ws_bytes || !aligned16(workspace)))
-    return fail(GNB200_ERR_WORKSPACE, "gnb200_bwd: needs a 16-byte aligned workspace of %zu bytes, got %zu at %p",
-                plan.ws_bytes, workspace_bytes, workspace);
-  gnb200::BwdCall call = {dy, x, gamma, beta, mean, rstd, dx, dgamma_dbeta_f32, dgamma, dbeta, workspace, act, dtype};
-  const cudaError_t err = gnb200::launch_backward(call, plan, reinterpret_cast<cudaStream_t>(stream));
+  return bwd_impl("gnb200_bwd_peer", dy, x, gamma, beta, mean, rstd, N, R, C, G, act, dtype, dx, dgamma_dbeta_f32, dgamma,
+                  dbeta, workspace, workspace_bytes, &px, stream);
+}
+
+int gnb200_bwd_peer_push(const void* dy, const void* x, const void* gamma, const void* beta, const float* mean,
+                         const float* rstd, int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype, void* dx,
+                         float* dgamma_dbeta_f32, void* workspace, size_t workspace_bytes, const void* const* peer_bufs,
+                         int rank, int world, void* stream) {
+  gnb200::PeerExchange px;
+  const int rc = make_peer_exchange(peer_bufs, rank, world, C, false, "gnb200_bwd_peer_push", &px);
+  if (rc != GNB200_OK) return rc;
+  return bwd_impl("gnb200_bwd_peer_push", dy, x, gamma, beta, mean, rstd, N, R, C, G, act, dtype, dx, dgamma_dbeta_f32,
+                  nullptr, nullptr, workspace, workspace_bytes, &px, stream);
+}
+
+// push and / or collect on a gradient buffer, as a kernel of its own
+static int exchange_impl(const char* who, float* dgamma_dbeta_f32, void* dgamma, void* dbeta, int64_t C, int dtype,
+                         const void* const* peer_bufs, int rank, int world, bool push, bool collect, void* stream) {
+  if (dtype < GNB200_F32 || dtype > GNB200_BF16) return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: unknown dtype code %d", who, dtype);
+  if (!dgamma_dbeta_f32) return fail(GNB200_ERR_INVALID_ARGUMENT, "%s: null gradient buffer", who);
+  if (gnb200::wait_gave_up_on_current_device())
+    return fail(GNB200_ERR_EXCHANGE_TIMEOUT, "%s: an earlier bounded wait on this device gave up", who);
+  gnb200::PeerExchange px;
+  const int rc = make_peer_exchange(peer_bufs, rank, world, C, collect, who, &px);
+  if (rc != GNB200_OK) return rc;
+  gnb200::BwdCall call = {};
+  call.dparam_f32 = dgamma_dbeta_f32;
+  call.dgamma = dgamma;
+  call.dbeta = dbeta;
+  call.dtype = dtype;
+  call.peer = &px;
+  const cudaError_t err = gnb200::launch_param_exchange(call, (int)C, reinterpret_cast<cudaStream_t>(stream), false, push, collect);
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
-    return fail(GNB200_ERR_CUDA, "gnb200_bwd: CUDA error: %s", cudaGetErrorString(err));
+    return fail(GNB200_ERR_CUDA, "%s: CUDA error: %s", who, cudaGetErrorString(err));
   }
   return GNB200_OK;
+}
+
+int gnb200_peer_collect(float* dgamma_dbeta_f32, void* dgamma, void* dbeta, int64_t C, int dtype,
+                        const void* const* peer_bufs, int rank, int world, void* stream) {
+  return exchange_impl("gnb200_peer_collect", dgamma_dbeta_f32, dgamma, dbeta, C, dtype, peer_bufs, rank, world, false, true,
+                       stream);
+}
+
+int gnb200_allreduce_param_grads(float* dgamma_dbeta_f32, void* dgamma, void* dbeta, int64_t C, int dtype,
+                                 const void* const* peer_bufs, int rank, int world, void* stream) {
+  return exchange_impl("gnb200_allreduce_param_grads", dgamma_dbeta_f32, dgamma, dbeta, C, dtype, peer_bufs, rank, world,
+                       true, true, stream);
 }
 
 size_t gnb200_fwd_nchw_workspace_bytes(int64_t N, int64_t R, int64_t C, int64_t G, int dtype) {

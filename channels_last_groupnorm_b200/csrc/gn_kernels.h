@@ -4,6 +4,7 @@
 #include <stdint.h>
 
 #include "gn_common.cuh"
+#include "gn_peer.cuh"
 
 namespace gnb200 {
 
@@ -53,6 +54,9 @@ struct BwdCall {
   void* workspace;
   int act;
   int dtype;
+  // optional: the parameter gradients are summed over the ranks of one node inside the kernel that
+  // produces them (gn_peer.cuh); null or world <= 1: the gradients of this rank only
+  const PeerExchange* peer = nullptr;
 };
 
 // direction: 0 forward, 1 backward.  `aligned16`: every tensor pointer is 16-byte aligned.
@@ -86,6 +90,9 @@ cudaError_t launch_backward_wave(const BwdCall& c, const Plan& p, cudaStream_t s
 // `chained`: as a programmatic dependent of the kernel before it in the stream
 cudaError_t launch_param_grads(const BwdCall& c, const float* sums, int rows, int C, cudaStream_t stream,
                                bool chained = false);
+// Exchange of a finished [dgamma | dbeta] buffer over the ranks of c.peer (gn_bwd.cu): `push` posts the
+// buffer's values, `collect` replaces them (and the typed copies) by the sums over the ranks
+cudaError_t launch_param_exchange(const BwdCall& c, int C, cudaStream_t stream, bool chained, bool push, bool collect);
 // GNB200_CHAIN != 0 (the default): the kernels of a multi-kernel call are launched as programmatic
 // dependents of their predecessors
 bool chain_enabled();

@@ -21,6 +21,8 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <vector>
+
 #include "../../include/gnb200.h"
 
 namespace {
@@ -116,7 +118,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> gnb200_fwd_op(const at::Tensor& X
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bwd_impl(const at::Tensor& dy, const at::Tensor& X,
                                                                     const at::Tensor& weight, const at::Tensor& bias,
                                                                     const at::Tensor& means, const at::Tensor& rstds,
-                                                                    int64_t G, int64_t act, bool want_typed) {
+                                                                    int64_t G, int64_t act, bool want_typed,
+                                                                    c10::ArrayRef<int64_t> peer_ptrs = {}, int64_t rank = 0) {
   const Layout layout = layout_of(X, "X");
   const int64_t N = X.size(0), C = X.size(1), R = X.size(2);
   const int dtype = dtype_code(X, "X");
@@ -147,6 +150,12 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bwd_impl(const at::Te
     return {dX, dparam, dweight, dbias};
   }
   auto stream = c10::cuda::getCurrentCUDAStream().stream();
+  // data-parallel ranks of one node: the sum over the ranks happens inside the library's kernels,
+  // through the ranks' exchange buffers (peer_ptrs[q] = rank q's buffer as mapped into this process)
+  const int world = (int)peer_ptrs.size();
+  std::vector<const void*> peers(world);
+  for (int q = 0; q < world; ++q) peers[q] = reinterpret_cast<const void*>(static_cast<uintptr_t>(peer_ptrs[q]));
+  TORCH_CHECK(world == 0 || dtype != kF64, "gnb200: the in-kernel exchange of parameter gradients is for fp32 / fp16 / bf16 tensors");
   if (dtype == kF64) {
     // the packed buffer is the result: its two rows are dgamma and dbeta
     const size_t ws_bytes = gnb200_bwd_f64_workspace_bytes(N, R, C, G);
@@ -166,12 +175,23 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bwd_impl(const at::Te
   const size_t ws_bytes = layout == kNHWC ? gnb200_bwd_workspace_bytes(N, R, C, G, dtype)
                                           : gnb200_bwd_nchw_workspace_bytes(N, R, C, G, dtype);
   at::Tensor ws = at::empty({(int64_t)ws_bytes}, X.options().dtype(at::kByte));
+  void* dw = want_typed ? dweight.mutable_data_ptr() : nullptr;
+  void* db = want_typed ? dbias.mutable_data_ptr() : nullptr;
+  if (world > 1 && layout == kNHWC) {
+    check_status(gnb200_bwd_peer(dy.const_data_ptr(), X.const_data_ptr(), weight.const_data_ptr(), bias.const_data_ptr(),
+                                 means.const_data_ptr<float>(), rstds.const_data_ptr<float>(), N, R, C, G, (int)act, dtype,
+                                 dX.mutable_data_ptr(), dparam.mutable_data_ptr<float>(), dw, db,
+                                 ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes, peers.data(), (int)rank, world, stream));
+    return {dX, dparam, dweight, dbias};
+  }
   auto fn = layout == kNHWC ? &gnb200_bwd : &gnb200_bwd_nchw;
   check_status(fn(dy.const_data_ptr(), X.const_data_ptr(), weight.const_data_ptr(), bias.const_data_ptr(),
                   means.const_data_ptr<float>(), rstds.const_data_ptr<float>(), N, R, C, G, (int)act, dtype,
-                  dX.mutable_data_ptr(), dparam.mutable_data_ptr<float>(),
-                  want_typed ? dweight.mutable_data_ptr() : nullptr, want_typed ? dbias.mutable_data_ptr() : nullptr,
+                  dX.mutable_data_ptr(), dparam.mutable_data_ptr<float>(), dw, db,
                   ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes, stream));
+  if (world > 1)  // channels-first: the exchange follows the backward as a kernel of its own
+    check_status(gnb200_allreduce_param_grads(dparam.mutable_data_ptr<float>(), dw, db, C, dtype, peers.data(), (int)rank,
+                                              world, stream));
   return {dX, dparam, dweight, dbias};
 }
 
@@ -191,6 +211,19 @@ std::tuple<at::Tensor, at::Tensor> gnb200_bwd_f32_op(const at::Tensor& dy, const
   return {std::get<0>(r), std::get<1>(r)};
 }
 
+// bwd_f32 with the sum of the parameter gradients over the data-parallel ranks of one node done
+// inside the kernels (gnb200_bwd_peer): peer_ptrs[q] is the address of rank q's exchange buffer in
+// this process, `rank` this process's index in that list.
+std::tuple<at::Tensor, at::Tensor> gnb200_bwd_f32_peer_op(const at::Tensor& dy, const at::Tensor& X,
+                                                          const at::Tensor& weight, const at::Tensor& bias,
+                                                          const at::Tensor& means, const at::Tensor& rstds, int64_t G,
+                                                          int64_t act, c10::ArrayRef<int64_t> peer_ptrs, int64_t rank) {
+  TORCH_CHECK(peer_ptrs.size() >= 1 && rank >= 0 && rank < (int64_t)peer_ptrs.size(),
+              "gnb200: rank ", rank, " is not an index into the ", peer_ptrs.size(), " exchange buffers");
+  auto r = bwd_impl(dy, X, weight, bias, means, rstds, G, act, false, peer_ptrs, rank);
+  return {std::get<0>(r), std::get<1>(r)};
+}
+
 }  // namespace
 
 // Schemas are declared apart from the implementations so that Python can attach fake-tensor
@@ -203,12 +236,15 @@ TORCH_LIBRARY(gnb200, m) {
         "(Tensor, Tensor, Tensor)");
   m.def("bwd_f32(Tensor dy, Tensor X, Tensor weight, Tensor bias, Tensor means, Tensor rstds, int G, int act) -> "
         "(Tensor, Tensor)");
+  m.def("bwd_f32_peer(Tensor dy, Tensor X, Tensor weight, Tensor bias, Tensor means, Tensor rstds, int G, int act, "
+        "int[] peer_ptrs, int rank) -> (Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(gnb200, CUDA, m) {
   m.impl("fwd", &gnb200_fwd_op);
   m.impl("bwd", &gnb200_bwd_op);
   m.impl("bwd_f32", &gnb200_bwd_f32_op);
+  m.impl("bwd_f32_peer", &gnb200_bwd_f32_peer_op);
 }
 
 TORCH_LIBRARY_IMPL(gnb200, CPU, m) {

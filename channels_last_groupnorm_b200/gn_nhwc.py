@@ -100,9 +100,17 @@ class GN_NHWC_Func(torch.autograd.Function):
         same = w_dtype == X_flat.dtype and b_dtype == X_flat.dtype
         if ctx.process_group is None and same:
             dx, dgamma, dbeta = torch.ops.gnb200.bwd(dy_flat, X_flat, weight, bias, means, rstds, ctx.G, ctx.activation)
+        elif isinstance(ctx.process_group, _dist.PeerExchange) and X_flat.dtype != torch.float64:
+            # ranks on the GPUs of one node: the sum over the ranks happens inside the backward kernels
+            px = ctx.process_group
+            dx, dparam = torch.ops.gnb200.bwd_f32_peer(dy_flat, X_flat, weight, bias, means, rstds, ctx.G, ctx.activation,
+                                                       px.peer_ptrs, px.rank)
+            dgamma, dbeta = dparam[0].to(w_dtype), dparam[1].to(b_dtype)
         else:
             dx, dparam = torch.ops.gnb200.bwd_f32(dy_flat, X_flat, weight, bias, means, rstds, ctx.G, ctx.activation)
-            if ctx.process_group is not None:
+            if isinstance(ctx.process_group, _dist.PeerExchange):
+                _dist.allreduce_param_grads(dparam, ctx.process_group.group)  # fp64: library collective
+            elif ctx.process_group is not None:
                 _dist.allreduce_param_grads(dparam, ctx.process_group)
             dgamma, dbeta = dparam[0].to(w_dtype), dparam[1].to(b_dtype)
         return _restore_shape(dx, ctx.x_shape, ctx.channels_last), dgamma, dbeta, None, None, None, None

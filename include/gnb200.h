@@ -164,6 +164,58 @@ int gnb200_bwd_static_scratch(const void* dy, const void* x, const void* gamma, 
                               void* dx, float* dgamma_dbeta_f32, void* dgamma, void* dbeta, void* stream);
 
 /*
+ * Data-parallel ranks on the GPUs of one node (the batch is split over the ranks; statistics are per
+ * sample, so only dgamma / dbeta need the other ranks).  The sum over the ranks is done by the
+ * library's own kernels over peer-mapped memory - no library collective, no multicast object:
+ *   push     inside the kernel that produces [dgamma | dbeta], every rank stores its 2 * C floats
+ *            into its slot of EVERY rank's exchange buffer (plain stores through peer-mapped pointers,
+ *            NVLink) and raises a flag beside them;
+ *   collect  a rank waits for all ranks' flags in its OWN buffer, adds the slots in rank order (all
+ *            ranks get the same bits) and acknowledges, which frees the slots for the push after next.
+ * gnb200_bwd_peer       = gnb200_bwd + push + collect in one call: dgamma_dbeta_f32 / dgamma / dbeta
+ *                         hold the sums over the ranks (one NVLink round trip inside the call).
+ * gnb200_bwd_peer_push  = gnb200_bwd + push: dgamma_dbeta_f32 holds this rank's own sums and the call
+ *                         waits for nobody; gnb200_peer_collect, any time later on the same stream or
+ *                         one ordered after it (typically before the optimizer step, when every
+ *                         contribution has long arrived), writes the sums over the ranks.  At most two
+ *                         pushes may be outstanding (pushed, not yet collected) per buffer set.
+ * gnb200_allreduce_param_grads = push + collect on a finished buffer, in place (for the channels-first
+ *                         entry points, or for gradients accumulated over several calls).
+ * The reference has no multi-GPU code; these entry points have no counterpart there (they stand
+ * where a framework would call an all-reduce after run_gn_bwd_kernels,
+ * src/gnnhwc/csrc/gn_kernel.h:26-41).
+ *   peer_bufs : host array of `world` device pointers; peer_bufs[q] is rank q's exchange buffer as
+ *               mapped into THIS process (peer_bufs[rank] is this rank's own buffer).  Every buffer
+ *               has gnb200_peer_exchange_bytes(C, world) bytes, is 16-byte aligned, was zeroed once
+ *               before its first use and belongs to one (C, world) pair.  How the buffers are
+ *               allocated and mapped (symmetric memory, CUDA IPC, cuMem) is the caller's business.
+ *   dgamma, dbeta : optional typed copies (C elements of `dtype`) of the summed buffer.
+ *   Every rank must make the same sequence of pushes and collects on a buffer set.  Waits for other
+ *   ranks are bounded like every wait of the library (about a second): a rank that waits longer gets
+ *   NaN gradients and GNB200_ERR_EXCHANGE_TIMEOUT from the next call on (see gnb200_wait_timeouts
+ *   below).  With push and collect apart the ranks need not be in step during the backward pass;
+ *   with gnb200_bwd_peer they must be within that second of each other.
+ *   world == 1: no exchange (gnb200_bwd; collect leaves the buffer as it is).  1 <= world <= 16.
+ */
+size_t gnb200_peer_exchange_bytes(int64_t C, int world);
+int gnb200_bwd_peer(const void* dy, const void* x, const void* gamma, const void* beta,
+                    const float* mean, const float* rstd,
+                    int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype,
+                    void* dx, float* dgamma_dbeta_f32, void* dgamma, void* dbeta,
+                    void* workspace, size_t workspace_bytes,
+                    const void* const* peer_bufs, int rank, int world, void* stream);
+int gnb200_bwd_peer_push(const void* dy, const void* x, const void* gamma, const void* beta,
+                         const float* mean, const float* rstd,
+                         int64_t N, int64_t R, int64_t C, int64_t G, int act, int dtype,
+                         void* dx, float* dgamma_dbeta_f32,
+                         void* workspace, size_t workspace_bytes,
+                         const void* const* peer_bufs, int rank, int world, void* stream);
+int gnb200_peer_collect(float* dgamma_dbeta_f32, void* dgamma, void* dbeta, int64_t C, int dtype,
+                        const void* const* peer_bufs, int rank, int world, void* stream);
+int gnb200_allreduce_param_grads(float* dgamma_dbeta_f32, void* dgamma, void* dbeta, int64_t C, int dtype,
+                                 const void* const* peer_bufs, int rank, int world, void* stream);
+
+/*
  * Describes the launch plan chosen for a problem ("fwd fused k=4 cw=64 ..."), for logs, tests
  * and benchmarks.  Writes at most buf_len bytes including the terminating NUL; returns the
  * number of bytes the full text needs.  direction: 0 = forward, 1 = backward.

@@ -70,6 +70,31 @@ def test_invalid_arguments_are_rejected_before_any_cuda_call():
         nt.check(-1)
 
 
+def test_peer_exchange_buffer_size_and_argument_checks():
+    """The in-kernel all-reduce of [dgamma | dbeta]: two parities x world slots of 2 * C (value, number) pairs of
+    8 bytes, world x blocks acknowledgement words and two counter words per block of 32 channels, rounded up
+    to 256 bytes."""
+    nbytes = nt.peer_exchange_bytes(256, 8)
+    assert nbytes == (2 * 8 * 512 * 8 + (8 * 8 + 2 * 8) * 4 + 255) // 256 * 256
+    assert nt.peer_exchange_bytes(256, 1) > 0 and nt.peer_exchange_bytes(40, 2) % 256 == 0
+    assert nt.peer_exchange_bytes(256, 0) == 0 and nt.peer_exchange_bytes(256, 17) == 0 and nt.peer_exchange_bytes(0, 2) == 0
+    one = _buffer(4096)
+    table = (ctypes.c_void_p * 2)(one, one)
+    f = nt.lib.gnb200_bwd_peer
+    args = (one, one, one, one, one, one, 2, 4, 8, 4, 0, 0, one, one, None, None, None, 0)
+    assert f(*args, table, 2, 2, None) == -1 and "rank 2 of 2" in nt.lib.gnb200_last_error().decode()
+    assert f(*args, table, 0, 17, None) == -1
+    assert f(*args, None, 0, 2, None) == -1 and "null table" in nt.lib.gnb200_last_error().decode()
+    bad = (ctypes.c_void_p * 2)(one, None)
+    assert f(*args, bad, 0, 2, None) == -1 and "rank 1" in nt.lib.gnb200_last_error().decode()
+    push = nt.lib.gnb200_bwd_peer_push
+    assert push(*args[:14], None, 0, table, 5, 2, None) == -1 and "rank 5 of 2" in nt.lib.gnb200_last_error().decode()
+    for g in (nt.lib.gnb200_allreduce_param_grads, nt.lib.gnb200_peer_collect):
+        assert g(one, None, None, 8, 9, table, 0, 2, None) == -1  # bad dtype code
+        assert g(None, None, None, 8, 0, table, 0, 2, None) == -1  # null buffer
+    _KEEP.clear()
+
+
 def test_workspace_is_required_when_the_plan_needs_one():
     # a slab far too large for a cluster: multi-kernel path, scratch needed
     N, R, C, G = 1, 1 << 20, 128, 32
@@ -192,3 +217,5 @@ def test_fake_tensor_kernels_describe_the_outputs():
         assert dX.stride() == X.stride() and dw.shape == (8,) and db.dtype == torch.bfloat16
         dX, dparam = torch.ops.gnb200.bwd_f32(Y, X, w, b, means, rstds, 2, 3)
         assert dparam.shape == (2, 8) and dparam.dtype == torch.float32
+        dX, dparam = torch.ops.gnb200.bwd_f32_peer(Y, X, w, b, means, rstds, 2, 3, [1 << 20, 2 << 20], 1)
+        assert dX.stride() == X.stride() and dparam.shape == (2, 8) and dparam.dtype == torch.float32

@@ -116,6 +116,28 @@ def test_chained_launches_change_no_bit(nt, path, monkeypatch):
         assert torch.equal(outs[0][k], outs[1][k]), k
 
 
+def test_peer_entry_points_with_one_rank_are_the_plain_backward(nt):
+    """gnb200_bwd_peer / gnb200_bwd_peer_push / gnb200_peer_collect / gnb200_allreduce_param_grads with a single
+    rank exchange nothing: same bits as gnb200_bwd, buffers untouched by the exchange calls.  (With several
+    ranks the exchange is checked on the hardware by bench.py's parity_check, which needs one GPU per rank.)"""
+    x, ga, be, dy, G, eps, act, dtype = _case_inputs(CFG4[0])
+    code = O.ACT_CODES[act]
+    xd, gd, bd, dyd = _flat(x.cuda()), ga.cuda(), be.cuda(), _flat(dy.cuda())
+    y, mean, rstd = nt.fwd_raw(xd, gd, bd, G, eps, code)
+    dx, dparam, _, _ = nt.bwd_raw(dyd, xd, gd, bd, mean, rstd, G, code)
+    buf = torch.zeros(nt.peer_exchange_bytes(x.shape[1], 1) // 4, dtype=torch.float32, device="cuda")
+    ptrs = [buf.data_ptr()]
+    for collect in (True, False):
+        dx2, dparam2 = nt.bwd_peer_raw(dyd, xd, gd, bd, mean, rstd, G, code, ptrs, 0, collect=collect)
+        assert torch.equal(dx, dx2) and torch.equal(dparam, dparam2)
+    keep = dparam.clone()
+    nt.peer_collect_raw(dparam, ptrs, 0)
+    nt.allreduce_param_grads_peer_raw(dparam, ptrs, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(dparam, keep) and int(buf.abs().sum().item()) == 0
+    assert nt.wait_timeouts() == 0
+
+
 @pytest.mark.parametrize("act", O.ACT_NAMES)
 @pytest.mark.parametrize("dt", ["float32", "float16", "bfloat16"])
 def test_every_activation_and_dtype(nt, act, dt):
