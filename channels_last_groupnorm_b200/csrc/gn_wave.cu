@@ -518,7 +518,7 @@ __global__ void __launch_bounds__(kWaveThreads, 3)
 // backward
 // scratch: tpart[(n * chunks + chunk) * C + c] = (S1, S2) of channel c over the rows of chunk `chunk`
 //          gpart[(item * chunks + chunk) * slots + s] = gamma-weighted sums of the unit's group slot s
-//          coef[(n * G + g) * 2] = A, B
+//          coef_words[item * slots + s] = (A, B) of group slot s as one 64-bit word, all ones until the slab's last chunk is merged
 // Only the small group sums are on the path between the passes; the channel sums are added up - for
 // dgamma / dbeta - by all CTAs together when they have finished their last unit.
 // ------------------------------------------------------------------------------------------------

@@ -19,8 +19,10 @@ against `gnnhwc` only has to change its import.  What differs, on purpose:
   `torch._dynamo.disable`, custom_gn.py:63): the ops have fake-tensor kernels and an autograd
   formula (`_compile.py`), so `torch.compile` traces through them.
 * `process_group`: for batch-sharded data-parallel training the packed fp32 `[dgamma | dbeta]`
-  buffer written by the backward kernels is summed across the ranks of that group with one
-  all-reduce; forward needs no communication.
+  buffer written by the backward kernels is summed across the ranks; forward needs no
+  communication.  A `torch.distributed` process group means one NCCL all-reduce in backward; a
+  `dist.PeerExchange` (ranks on the GPUs of one node) means that the backward kernels exchange
+  and sum the gradients themselves through peer-mapped memory, with no library collective.
 """
 import torch
 import torch.nn as nn
@@ -132,7 +134,8 @@ class GN_NHWC(nn.GroupNorm):
     GN_NHWC(num_groups, num_channels, activation='identity', eps=1e-5, affine=True, device=None,
     dtype=None, process_group=None).  `activation` is one of identity, relu, silu (alias swish),
     gelu, gelu_tanh; an unknown name raises KeyError like the reference (custom_gn.py:52-61).
-    state_dict keys are those of `nn.GroupNorm` (`weight`, `bias`).
+    state_dict keys are those of `nn.GroupNorm` (`weight`, `bias`).  `process_group`: a
+    torch.distributed process group or a `dist.PeerExchange` whose ranks share the parameter gradients.
     """
 
     def __init__(self, num_groups: int, num_channels: int, activation="identity", process_group=None, **kwargs):

@@ -79,6 +79,7 @@ def build(ref_root, force=False, verbose=True):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # default: a checkout of the reference beside this repository
+    root = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     lib = build(root, force="--force" in sys.argv)
     print("reference library:", lib)
