@@ -529,10 +529,13 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
 // (one per sample, or per sample and cluster rank; ascending per lane,
 // then the 32 row lanes in order).  block (32, 32), grid ceil(C / 32).
 // ------------------------------------------------------------------------------------------------
-template <typename T>
+// PEER: the exchange over the ranks is compiled in.  (Its table of peer pointers is indexed at run
+// time: the descriptor is a __grid_constant__ so that it is read in place, and single-GPU launches
+// take the instantiation without it - a by-value copy into every thread's local memory cost 2 us.)
+template <typename T, bool PEER>
 __global__ void __launch_bounds__(1024)
     gn_bwd_param_kernel(const float* __restrict__ sums, int N, int C, float* __restrict__ dparam_f32,
-                        T* __restrict__ dgamma, T* __restrict__ dbeta, const PeerExchange px) {
+                        T* __restrict__ dgamma, T* __restrict__ dbeta, const __grid_constant__ PeerExchange px) {
   constexpr int kLanes = 32;  // row lanes: block (32 channels, 32 row lanes)
   __shared__ float sm1[kLanes][33], sm2[kLanes][33];
   grid_dep_launch_dependents();
@@ -559,7 +562,7 @@ __global__ void __launch_bounds__(1024)
     }
     // data-parallel ranks of one node: post this rank's sums into every rank's exchange buffer and,
     // unless the caller collects later, wait for the others' and add them up in rank order
-    if (px.world > 1) {
+    if constexpr (PEER) {
       const bool pushed = peer_push_block(px, blockIdx.x, c < C, t2, t1);
       if (px.collect) peer_collect_block(px, blockIdx.x, c < C, t2, t1);
       else if (!pushed) t1 = t2 = __int_as_float(0x7fc00000);
@@ -578,7 +581,7 @@ __global__ void __launch_bounds__(1024)
 template <typename T>
 __global__ void __launch_bounds__(32)
     gn_param_exchange_kernel(int C, float* __restrict__ dparam_f32, T* __restrict__ dgamma, T* __restrict__ dbeta,
-                             bool push, bool collect, const PeerExchange px) {
+                             bool push, bool collect, const __grid_constant__ PeerExchange px) {
   grid_dep_wait();  // the kernel that wrote dparam_f32
   const int c = blockIdx.x * 32 + threadIdx.x;
   float dg = 0.f, db = 0.f;
@@ -757,10 +760,11 @@ static cudaError_t launch_param(const BwdCall& c, const float* sums, int rows, c
                                 bool chained) {
   const dim3 block(32, 32, 1);
   const unsigned blocks = (unsigned)((g.C + 31) / 32);
-  PeerExchange px = {};
-  if (c.peer) px = *c.peer;
-  return launch_chained(gn_bwd_param_kernel<T>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
-                        (T*)c.dgamma, (T*)c.dbeta, px);
+  if (c.peer && c.peer->world > 1)
+    return launch_chained(gn_bwd_param_kernel<T, true>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
+                          (T*)c.dgamma, (T*)c.dbeta, *c.peer);
+  return launch_chained(gn_bwd_param_kernel<T, false>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
+                        (T*)c.dgamma, (T*)c.dbeta, PeerExchange{});
 }
 
 template <typename T>

@@ -332,7 +332,14 @@ bool plan_wave(const Shape& sh, Plan* out) {
   // L2 budget of one wave: `teams` waves are in flight at once
   // (defaults from sweeps over the 1024-px VAE-decoder shapes on B200: two teams, overlapped order, 96 MB
   // forward / 144 MB backward in flight - somewhat more than L2 holds measured best)
-  const double budget = (double)env_int("GNB200_WAVE_MB", sh.direction == 0 ? 96 : 144) * 1024.0 * 1024.0 / teams_req;
+  double budget = (double)env_int("GNB200_WAVE_MB", sh.direction == 0 ? 96 : 144) * 1024.0 * 1024.0 / teams_req;
+  // ... and at least four waves, so that the teams' passes interleave (512@256^2 backward: 69 us with four
+  // waves of 33 MB, 79 us with two of 67 MB), as long as that does not shorten the row segments below 128 bytes
+  if (env_int("GNB200_WAVE_MB", 0) == 0) {
+    const double quarter = (double)sh.N * sh.R * sh.C * s * tensors / 4.0;
+    const double seg128 = (double)sh.R * 128.0 * tensors;  // a slab with 128-byte row segments
+    if (quarter < budget && quarter >= seg128) budget = quarter;
+  }
   const int units = (int)(sh.C / U);
   int cw = 0, cw_min64 = 0, cw_fit = 0, cw_first = 0;
   for (int m = 1; m <= units; ++m) {
