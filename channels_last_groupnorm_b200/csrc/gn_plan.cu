@@ -333,9 +333,10 @@ bool plan_wave(const Shape& sh, Plan* out) {
   // (defaults from sweeps over the 1024-px VAE-decoder shapes on B200: two teams, overlapped order, 96 MB
   // forward / 144 MB backward in flight - somewhat more than L2 holds measured best)
   double budget = (double)env_int("GNB200_WAVE_MB", sh.direction == 0 ? 96 : 144) * 1024.0 * 1024.0 / teams_req;
-  // ... and at least four waves, so that the teams' passes interleave (512@256^2 backward: 69 us with four
+  // ... and, backward, at least four waves, so that the teams' passes interleave (512@256^2: 69 us with four
   // waves of 33 MB, 79 us with two of 67 MB), as long as that does not shorten the row segments below 128 bytes
-  if (env_int("GNB200_WAVE_MB", 0) == 0) {
+  // (the forward kernel measured better with two waves: 49 against 54 us)
+  if (sh.direction == 1 && env_int("GNB200_WAVE_MB", 0) == 0) {
     const double quarter = (double)sh.N * sh.R * sh.C * s * tensors / 4.0;
     const double seg128 = (double)sh.R * 128.0 * tensors;  // a slab with 128-byte row segments
     if (quarter < budget && quarter >= seg128) budget = quarter;
