@@ -20,6 +20,8 @@
 //          -> parameter-gradient kernel -> apply kernel (reverse tile order for L2 reuse).
 //
 // Every sum is formed in an order fixed by the launch geometry: no atomics, bit-identical reruns.
+#include <stdlib.h>
+
 #include "gn_kernels.h"
 #include "gn_math.cuh"
 
@@ -527,16 +529,19 @@ __global__ void __launch_bounds__(MAXT, MAXT == 128 ? 5 : 1)
 // ------------------------------------------------------------------------------------------------
 // parameter gradients:  dbeta_c = sum_n S1[n,c],  dgamma_c = sum_n S2[n,c]  over the N rows of `sums`
 // (one per sample, or per sample and cluster rank; ascending per lane,
-// then the 32 row lanes in order).  block (32, 32), grid ceil(C / 32).
+// then the row lanes in order).  block (32, row lanes), grid ceil(C / 32).
 // ------------------------------------------------------------------------------------------------
 // PEER: the exchange over the ranks is compiled in.  (Its table of peer pointers is indexed at run
 // time: the descriptor is a __grid_constant__ so that it is read in place, and single-GPU launches
 // take the instantiation without it - a by-value copy into every thread's local memory cost 2 us.)
-template <typename T, bool PEER>
-__global__ void __launch_bounds__(1024)
+// LANES row lanes: 32, or 8 for the PEER instantiation when there are few rows to add - its CTAs are
+// programmatic dependents of the backward kernel, and 256 threads with the exchange's registers find room
+// on an SM as soon as one CTA of that kernel has left, where 1024 threads need the SM all but empty.
+template <typename T, bool PEER, int LANES>
+__global__ void __launch_bounds__(32 * LANES)
     gn_bwd_param_kernel(const float* __restrict__ sums, int N, int C, float* __restrict__ dparam_f32,
                         T* __restrict__ dgamma, T* __restrict__ dbeta, const __grid_constant__ PeerExchange px) {
-  constexpr int kLanes = 32;  // row lanes: block (32 channels, 32 row lanes)
+  constexpr int kLanes = LANES;  // row lanes: block (32 channels, kLanes row lanes)
   __shared__ float sm1[kLanes][33], sm2[kLanes][33];
   grid_dep_launch_dependents();
   grid_dep_wait();  // the sums of the kernel before
@@ -760,10 +765,18 @@ static cudaError_t launch_param(const BwdCall& c, const float* sums, int rows, c
                                 bool chained) {
   const dim3 block(32, 32, 1);
   const unsigned blocks = (unsigned)((g.C + 31) / 32);
-  if (c.peer && c.peer->world > 1)
-    return launch_chained(gn_bwd_param_kernel<T, true>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
+  if (c.peer && c.peer->world > 1) {
+    // (the order in which the samples' sums are added depends on the lane count, which depends only on the
+    // row count: the ranks of a group have equal batches, so every rank adds in the same order)
+    const char* forced = getenv("GNB200_PEER_LANES");  // experiments: 8 or 32
+    const int few = forced && *forced ? atoi(forced) : (rows < 128 ? 8 : 32);
+    if (few == 8)
+      return launch_chained(gn_bwd_param_kernel<T, true, 8>, blocks, dim3(32, 8, 1), 0, stream, chained, sums, rows, g.C,
+                            c.dparam_f32, (T*)c.dgamma, (T*)c.dbeta, *c.peer);
+    return launch_chained(gn_bwd_param_kernel<T, true, 32>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
                           (T*)c.dgamma, (T*)c.dbeta, *c.peer);
-  return launch_chained(gn_bwd_param_kernel<T, false>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
+  }
+  return launch_chained(gn_bwd_param_kernel<T, false, 32>, blocks, block, 0, stream, chained, sums, rows, g.C, c.dparam_f32,
                         (T*)c.dgamma, (T*)c.dbeta, PeerExchange{});
 }
 

@@ -18,15 +18,22 @@
 // Exchange buffer of one rank (same layout on every rank; `world` ranks, nblk = ceil(C / 32) blocks):
 //   uint2    slot[2][world][2 * C]    slot[p][q][i] = (bits of rank q's float i, number of the push), parity p
 //   unsigned ack[world][nblk]         ack[q][b] = number of the last call whose block b rank q has collected
-//   unsigned pushed[nblk]             this rank's push counter per block   (never written by peers)
-//   unsigned collected[nblk]          this rank's collect counter per block (never written by peers)
+//   unsigned pushed[nblk]             this rank's push counter per block        (the last four arrays are
+//   unsigned collected[nblk]          this rank's collect counter per block      never written by peers)
+//   unsigned done[nblk]               number of the last collect that has finished reading its slots
+//   unsigned acked[nblk]              number of the last collect this rank has acknowledged to the peers
 // The buffer must be zero before the first call.  Pushes and collects are numbered per block, 1, 2, ...
 // Every value travels with the number of its push in ONE 8-byte store, which arrives whole: a reader that
 // sees the number sees the value, so neither side needs a fence or a separate flag on the way in (the
 // scheme of low-latency collectives).  Slot reuse: push s overwrites the slots of push s - 2, so it first
-// waits (bounded; in practice never) until every rank has acknowledged collect s - 2; the acknowledgement
-// is a release store after the slots have been read.  Every rank must make the same sequence of pushes
-// and collects; a buffer set serves 2^32 - 1 of them (the numbers are 32-bit and 0 means "never written").
+// waits (bounded; in practice never) until every rank has acknowledged collect s - 2.  A collect only
+// notes locally (release, GPU scope) that it has read its slots; the word goes to the peers at the
+// start of the rank's NEXT push as a plain store - a system-scope release at the end of
+// the collect would wait about 2 us for this kernel's own stores to the peers to be confirmed, on the
+// critical path of every call.  The loads being acknowledged belong to an earlier kernel, or precede a
+// GPU-scope acquire of `done` in program order: they have returned their values before the store issues.
+// (A collect that is never followed by a push needs no acknowledgement.)  Every rank must make the same
+// sequence of pushes and collects; a buffer set serves 2^32 - 1 of them (the numbers are 32-bit and 0 means "never written").
 #pragma once
 #include "gn_common.cuh"
 
@@ -48,19 +55,21 @@ struct PeerExchange {
 __host__ __device__ inline size_t peer_slot_words(int world, int C) { return (size_t)2 * world * 2 * C; }  // 8 bytes each
 __host__ __device__ inline size_t peer_exchange_bytes(int world, int C) {
   const int nblk = (C + kPeerBlock - 1) / kPeerBlock;
-  const size_t words = (size_t)world * nblk + 2 * (size_t)nblk;
+  const size_t words = (size_t)world * nblk + 4 * (size_t)nblk;
   return (peer_slot_words(world, C) * 8 + words * sizeof(unsigned) + 255) & ~(size_t)255;
 }
 
 // Word arrays of the exchange buffer at `base`
 struct PeerWords {
-  unsigned *ack, *pushed, *collected;
+  unsigned *ack, *pushed, *collected, *done, *acked;
 };
 __device__ __forceinline__ PeerWords peer_words(char* base, int world, int C, int nblk) {
   PeerWords w;
   w.ack = reinterpret_cast<unsigned*>(base + peer_slot_words(world, C) * 8);
   w.pushed = w.ack + (size_t)world * nblk;
   w.collected = w.pushed + nblk;
+  w.done = w.collected + nblk;
+  w.acked = w.done + nblk;
   return w;
 }
 
@@ -70,6 +79,17 @@ __device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
 __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
   unsigned v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ void st_relaxed_sys_v2(uint2* p, unsigned a, unsigned b) {
@@ -113,13 +133,24 @@ __device__ __forceinline__ bool peer_push_block(const PeerExchange& px, int blk,
   const int lane = threadIdx.x & 31;
   const int world = px.world, C = px.C, nblk = px.nblk;
   const PeerWords mine = peer_words(px.base[px.rank], world, C, nblk);
-  unsigned seq = 0;
+  unsigned seq = 0, fin = 0, ack = 0;
   if (lane == 0) {
     seq = mine.pushed[blk] + 1;
+    fin = ld_acquire_gpu_u32(mine.done + blk);  // collects that have read their slots (possibly on another stream)
+    ack = mine.acked[blk];
     mine.pushed[blk] = seq;
+    mine.acked[blk] = fin;
   }
   seq = __shfl_sync(0xffffffffu, seq, 0);
+  fin = __shfl_sync(0xffffffffu, fin, 0);
+  ack = __shfl_sync(0xffffffffu, ack, 0);
   const unsigned par = seq & 1u;
+  // first, which of the peers' slots this rank has finished reading (before the wait below: every rank
+  // may be waiting for exactly this word)
+  if (fin != ack && lane < world) {
+    const PeerWords theirs = peer_words(px.base[lane], world, C, nblk);
+    st_relaxed_sys_u32(theirs.ack + (size_t)px.rank * nblk + blk, fin);
+  }
   // the slots of push seq - 2 are free once every rank has collected it
   if (seq > 2 && !peer_wait_words(mine.ack + blk, (size_t)nblk, seq - 2, world, px.wait)) return false;
   const int c = blk * kPeerBlock + lane;
@@ -190,13 +221,11 @@ __device__ __forceinline__ void peer_collect_block(const PeerExchange& px, int b
   }
   dg = sg;
   db = sb;
-  // Acknowledge (also after a give-up, so that the peers' next pushes are not held up).  The loads
-  // above come before the barrier in every lane's program order and the release stores after it.
+  // Note that the slots have been read (also after a give-up, so that the peers' pushes are not held
+  // up): the loads above come before the barrier in every lane's program order, the release after it.
+  // This rank's next push passes the number on to the peers.
   __syncwarp();
-  if (lane < world) {
-    const PeerWords theirs = peer_words(px.base[lane], world, C, nblk);
-    st_release_sys_u32(theirs.ack + (size_t)px.rank * nblk + blk, seq);
-  }
+  if (lane == 0) st_release_gpu_u32(mine.done + blk, seq);
 }
 
 }  // namespace gnb200

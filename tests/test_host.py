@@ -72,10 +72,10 @@ def test_invalid_arguments_are_rejected_before_any_cuda_call():
 
 def test_peer_exchange_buffer_size_and_argument_checks():
     """The in-kernel all-reduce of [dgamma | dbeta]: two parities x world slots of 2 * C (value, number) pairs of
-    8 bytes, world x blocks acknowledgement words and two counter words per block of 32 channels, rounded up
+    8 bytes, world x blocks acknowledgement words and four counter words per block of 32 channels, rounded up
     to 256 bytes."""
     nbytes = nt.peer_exchange_bytes(256, 8)
-    assert nbytes == (2 * 8 * 512 * 8 + (8 * 8 + 2 * 8) * 4 + 255) // 256 * 256
+    assert nbytes == (2 * 8 * 512 * 8 + (8 * 8 + 4 * 8) * 4 + 255) // 256 * 256
     assert nt.peer_exchange_bytes(256, 1) > 0 and nt.peer_exchange_bytes(40, 2) % 256 == 0
     assert nt.peer_exchange_bytes(256, 0) == 0 and nt.peer_exchange_bytes(256, 17) == 0 and nt.peer_exchange_bytes(0, 2) == 0
     one = _buffer(4096)

@@ -71,13 +71,14 @@ def _worker(rank, world, port, ret):
             first = fused.clone()
             dist.broadcast(first, src=0)
             assert torch.equal(first, fused), "ranks differ"
-            # the exchange alone
-            assert torch.equal(px.allreduce_(local.clone()), fused)
+            # the exchange alone, on the sums of the plain backward (whose kernel adds the samples with 32 row
+            # lanes where the exchanging one uses 8: the same numbers up to the order of fp32 additions)
+            assert O.rel_err(px.allreduce_(local.clone()), fused) <= 1e-6
             # push and collect apart, two pushes outstanding, three rounds (slot reuse and acknowledgements)
             for _ in range(3):
                 for _ in range(2):
                     _, loc = nt.bwd_peer_raw(dys, xs, gd_, bd_, mean, rstd, G, code, px.peer_ptrs, px.rank, collect=False)
-                    assert torch.equal(loc, local)
+                    assert O.rel_err(loc, local) <= 1e-6
                 for _ in range(2):
                     assert torch.equal(px.collect_(torch.empty_like(fused)), fused)
             # the module
