@@ -544,6 +544,10 @@ __global__ void __launch_bounds__(32 * LANES)
   constexpr int kLanes = LANES;  // row lanes: block (32 channels, kLanes row lanes)
   __shared__ float sm1[kLanes][33], sm2[kLanes][33];
   grid_dep_launch_dependents();
+  PeerPush pp = {};
+  if constexpr (PEER) {  // the bookkeeping of the exchange does not depend on the kernel before
+    if (threadIdx.y == 0) pp = peer_push_begin(px, blockIdx.x);
+  }
   grid_dep_wait();  // the sums of the kernel before
   const int c = blockIdx.x * 32 + threadIdx.x;
   float a1 = 0.f, a2 = 0.f;
@@ -568,8 +572,8 @@ __global__ void __launch_bounds__(32 * LANES)
     // data-parallel ranks of one node: post this rank's sums into every rank's exchange buffer and,
     // unless the caller collects later, wait for the others' and add them up in rank order
     if constexpr (PEER) {
-      const bool pushed = peer_push_block(px, blockIdx.x, c < C, t2, t1);
-      if (px.collect) peer_collect_block(px, blockIdx.x, c < C, t2, t1);
+      const bool pushed = peer_push_block(px, blockIdx.x, c < C, t2, t1, pp);
+      if (px.collect) peer_collect_block<(LANES <= 8 ? 8 : 4)>(px, blockIdx.x, c < C, t2, t1);
       else if (!pushed) t1 = t2 = __int_as_float(0x7fc00000);
     }
     if (c < C) {
@@ -587,6 +591,8 @@ template <typename T>
 __global__ void __launch_bounds__(32)
     gn_param_exchange_kernel(int C, float* __restrict__ dparam_f32, T* __restrict__ dgamma, T* __restrict__ dbeta,
                              bool push, bool collect, const __grid_constant__ PeerExchange px) {
+  PeerPush pp = {};
+  if (push) pp = peer_push_begin(px, blockIdx.x);
   grid_dep_wait();  // the kernel that wrote dparam_f32
   const int c = blockIdx.x * 32 + threadIdx.x;
   float dg = 0.f, db = 0.f;
@@ -595,8 +601,8 @@ __global__ void __launch_bounds__(32)
     db = dparam_f32[C + c];
   }
   bool ok = true;
-  if (push) ok = peer_push_block(px, blockIdx.x, c < C, dg, db);
-  if (collect) peer_collect_block(px, blockIdx.x, c < C, dg, db);
+  if (push) ok = peer_push_block(px, blockIdx.x, c < C, dg, db, pp);
+  if (collect) peer_collect_block<8>(px, blockIdx.x, c < C, dg, db);
   if (!collect && !ok) dg = db = __int_as_float(0x7fc00000);
   if (c < C && (collect || !ok)) {
     dparam_f32[c] = dg;

@@ -126,10 +126,14 @@ __device__ __forceinline__ bool peer_wait_words(const unsigned* word, size_t str
   return ok;
 }
 
-// Push of one block by one full warp; lane l holds (dg, db) of channel blk * 32 + l (`valid`: the
-// channel exists).  Returns false if the wait for the slots to become free gave up (nothing is
-// stored then: the peers' collect of this call will give up too, and report it).
-__device__ __forceinline__ bool peer_push_block(const PeerExchange& px, int blk, bool valid, float dg, float db) {
+// First half of a push, by one full warp: numbers the push, passes this rank's acknowledgement on and
+// looks once whether the slots are free.  It touches nothing but the exchange buffers, so a kernel
+// calls it before it waits for the values it is going to push.
+struct PeerPush {
+  unsigned seq;
+  bool ready;  // every rank has acknowledged push seq - 2
+};
+__device__ __forceinline__ PeerPush peer_push_begin(const PeerExchange& px, int blk) {
   const int lane = threadIdx.x & 31;
   const int world = px.world, C = px.C, nblk = px.nblk;
   const PeerWords mine = peer_words(px.base[px.rank], world, C, nblk);
@@ -144,15 +148,31 @@ __device__ __forceinline__ bool peer_push_block(const PeerExchange& px, int blk,
   seq = __shfl_sync(0xffffffffu, seq, 0);
   fin = __shfl_sync(0xffffffffu, fin, 0);
   ack = __shfl_sync(0xffffffffu, ack, 0);
-  const unsigned par = seq & 1u;
-  // first, which of the peers' slots this rank has finished reading (before the wait below: every rank
-  // may be waiting for exactly this word)
+  // first, which of the peers' slots this rank has finished reading (before any wait: every rank may be
+  // waiting for exactly this word)
   if (fin != ack && lane < world) {
     const PeerWords theirs = peer_words(px.base[lane], world, C, nblk);
     st_relaxed_sys_u32(theirs.ack + (size_t)px.rank * nblk + blk, fin);
   }
   // the slots of push seq - 2 are free once every rank has collected it
-  if (seq > 2 && !peer_wait_words(mine.ack + blk, (size_t)nblk, seq - 2, world, px.wait)) return false;
+  bool free_now = true;
+  if (seq > 2 && lane < world) free_now = (int)(ld_acquire_sys_u32(mine.ack + (size_t)lane * nblk + blk) - (seq - 2)) >= 0;
+  PeerPush pp;
+  pp.seq = seq;
+  pp.ready = __all_sync(0xffffffffu, free_now);
+  return pp;
+}
+
+// Second half: lane l holds (dg, db) of channel blk * 32 + l (`valid`: the channel exists).  Returns
+// false if the wait for the slots to become free gave up (nothing is stored then: the peers' collect
+// of this call will give up too, and report it).
+__device__ __forceinline__ bool peer_push_block(const PeerExchange& px, int blk, bool valid, float dg, float db,
+                                                const PeerPush& pp) {
+  const int lane = threadIdx.x & 31;
+  const int world = px.world, C = px.C, nblk = px.nblk;
+  const PeerWords mine = peer_words(px.base[px.rank], world, C, nblk);
+  const unsigned seq = pp.seq, par = seq & 1u;
+  if (!pp.ready && !peer_wait_words(mine.ack + blk, (size_t)nblk, seq - 2, world, px.wait)) return false;
   const int c = blk * kPeerBlock + lane;
   if (valid) {
     for (int q = 0; q < world; ++q) {  // my slot [par][rank] in every rank's buffer (my own included)
@@ -165,7 +185,9 @@ __device__ __forceinline__ bool peer_push_block(const PeerExchange& px, int blk,
 }
 
 // Collect of one block by one full warp: dg, db become the sums over all ranks (NaN after a wait
-// that gave up), in rank order.
+// that gave up), in rank order.  kBatch: ranks whose values are requested together (independent
+// loads; 16 registers per 4 ranks).
+template <int kBatch = 4>
 __device__ __forceinline__ void peer_collect_block(const PeerExchange& px, int blk, bool valid, float& dg, float& db) {
   const int lane = threadIdx.x & 31;
   const int world = px.world, C = px.C, nblk = px.nblk;
@@ -184,7 +206,6 @@ __device__ __forceinline__ void peer_collect_block(const PeerExchange& px, int b
   if (valid) {
     const long long t0 = clock64();
     unsigned polls = 0;
-    constexpr int kBatch = 4;  // ranks whose values are requested together (independent loads)
     for (int q0 = 0; q0 < world && ok; q0 += kBatch) {
       uint2 vg[kBatch], vb[kBatch];
 #pragma unroll
