@@ -819,9 +819,10 @@ def _device_arm(args):
     lo, hi = shard_bounds(N, rank, world)
     # more than one rank: the parameter gradients are summed inside the backward kernels over peer-mapped
     # exchange buffers (--collective peer-inline / peer / peer-side) or by an NCCL all-reduce on a side stream
-    # (--collective nccl).  auto: both the in-kernel exchange and NCCL are timed, each with the full protocol, the
-    # faster one gives the headline and both are reported ("collectives" in the line); the in-kernel exchange is
-    # value-checked on the hardware in either case.
+    # (--collective nccl).  auto: the in-kernel exchange (collected inside the backward call, or by the library's
+    # exchange kernel on a side stream, where the NCCL arrangement runs its all-reduce) and NCCL are timed, each with
+    # the full protocol; the fastest gives the headline and all are reported ("collectives" in the line); the
+    # in-kernel exchange is value-checked on the hardware in every case.
     peer, collective = None, ("none" if world == 1 else "nccl")
     if world > 1 and bwd and args.collective in ("auto", "peer", "peer-inline", "peer-side"):
         try:
@@ -848,7 +849,7 @@ def _device_arm(args):
     collectives = {}
     modes = [collective]
     if args.collective == "auto" and peer is not None:
-        modes = ["peer-inline", "nccl"]
+        modes = ["peer-inline", "peer-side", "nccl"]
     best = None
     for mode in modes:
         prob = DeviceProblem(wl, n_local, x, ga, be, dy, peer=(peer if mode.startswith("peer") else None), peer_mode=mode)
