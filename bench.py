@@ -445,6 +445,9 @@ def run_device_steps(prob, steps, warmup, world, barrier, use_graph=True):
             if done[b] is not None:
                 torch.cuda.current_stream().wait_event(done[b])
 
+    # the ranks enter together: the kernels of the in-kernel exchange wait only about a second for one another
+    torch.cuda.synchronize()
+    barrier()
     for i in range(warmup):
         one(i)
     join()
@@ -617,6 +620,8 @@ def run_e2e(wl, n_local, x, ga, be, dy, steps, warmup, world, barrier, peer=None
         for st in (s_in, s_comp, s_out):
             torch.cuda.current_stream().wait_stream(st)
 
+    torch.cuda.synchronize()
+    barrier()  # the ranks enter together (allocating pinned memory takes a different time on every rank)
     for i in range(warmup):
         one(i)
     drain()
@@ -694,6 +699,8 @@ def run_parity_check(wl, rank, world, x_full, ga, be, dy_full, lo, hi, peer=None
         bitwise = bitwise and bool(torch.equal(dx_s, dx_f[lo:hi]))
         errs["dx_shard_vs_full"] = _rel_err(dx_s, dx_f[lo:hi])
         if peer is not None:
+            torch.cuda.synchronize()
+            dist.barrier()  # the ranks enter the exchange together (its waits are bounded at about a second)
             # the in-kernel exchange: the summed gradients must equal the full-batch ones within tolerance, the
             # NCCL-summed ones closely, and be the same bits on every rank (they are added in rank order)
             _, dparam_p = nt.bwd_peer_raw(dys_, xs_, gad, bed, mean_s, rstd_s, G, code, peer.peer_ptrs, peer.rank)
