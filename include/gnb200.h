@@ -169,9 +169,10 @@ int gnb200_bwd_static_scratch(const void* dy, const void* x, const void* gamma, 
  * library's own kernels over peer-mapped memory - no library collective, no multicast object:
  *   push     inside the kernel that produces [dgamma | dbeta], every rank stores its 2 * C floats
  *            into its slot of EVERY rank's exchange buffer (plain stores through peer-mapped pointers,
- *            NVLink) and raises a flag beside them;
- *   collect  a rank waits for all ranks' flags in its OWN buffer, adds the slots in rank order (all
- *            ranks get the same bits) and acknowledges, which frees the slots for the push after next.
+ *            NVLink), each value in one 8-byte store together with the number of the push;
+ *   collect  a rank waits until all ranks' values with the expected number stand in its OWN buffer, adds
+ *            them in rank order (all ranks get the same bits) and notes that the slots have been read,
+ *            which its next push passes on to the peers and which frees the slots for the push after next.
  * gnb200_bwd_peer       = gnb200_bwd + push + collect in one call: dgamma_dbeta_f32 / dgamma / dbeta
  *                         hold the sums over the ranks (one NVLink round trip inside the call).
  * gnb200_bwd_peer_push  = gnb200_bwd + push: dgamma_dbeta_f32 holds this rank's own sums and the call
