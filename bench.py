@@ -7,8 +7,10 @@
 
 Workload of the headline line ("cfg4"): GroupNorm + GELU(erf), bf16, NHWC, global batch 64 of
 256 x 64 x 64, 32 groups, eps 1e-5, forward + backward; the batch is split evenly over the ranks
-(strong scaling) and the packed fp32 [dgamma | dbeta] buffer is all-reduced with NCCL.  A step is
-one forward + one backward over the rank's samples.  Inputs are seeded synthetic tensors
+(strong scaling) and the packed fp32 [dgamma | dbeta] buffer is summed over the ranks - by the
+library's own kernels over peer-mapped memory or by an NCCL all-reduce (--collective; `auto` times
+the arrangements, reports them under "collectives" and takes the fastest).  A step is one forward
++ one backward over the rank's samples.  Inputs are seeded synthetic tensors
 (x ~ N(0,1), gamma ~ U(0.5,1.5), beta ~ N(0,0.01), dy ~ N(0,1)).
 
 value      aggregate algorithmic bytes (5 * E * sizeof: read x, write y | read x, dy, write dx)
@@ -23,6 +25,11 @@ roofline   the backward call (the dominant kernel plus its 2-microsecond paramet
            duration against the measured copy bandwidth in MEASURED_PEAKS.json.
 cpu_baseline  torch.nn.functional.group_norm + activation on the host cores (channels_last, same
            dtype, autograd backward) on a bounded sample of the same workload.
+parity_check  values of the sharded run, checked on this hardware before anything is timed (shard
+           against full batch bit for bit, summed gradients against the full-batch ones, the
+           in-kernel exchange in every form, the module, torch's fp64); a failure exits non-zero.
+vae_sd_shapes  device times and roofline fractions of the VAE-decoder and SD-UNet shapes (1 GPU),
+           cold (rotating buffers) and, labelled `_hot`, with one buffer set.
 """
 import argparse
 import json
