@@ -73,6 +73,10 @@ class GN_NHWC_Func(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, X, weight, bias, G, eps, activation, process_group=None):
+        if isinstance(process_group, _dist.PeerExchange) and process_group.num_channels != (X.shape[1] if X.ndim > 1 else -1):
+            # the exchange buffers are laid out for one channel count: a mismatch would write outside them
+            raise ValueError("GN_NHWC_Func: the PeerExchange was made for %d channels, X has %d"
+                             % (process_group.num_channels, (X.shape[1] if X.ndim > 1 else -1)))
         if not X.is_cuda:
             raise ValueError("GN_NHWC_Func: X must be a CUDA tensor; this package has no CPU path")
         if X.ndim < 3:

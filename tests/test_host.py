@@ -191,6 +191,16 @@ def test_module_refuses_cpu_and_channels_first_inputs():
         pkg.GN_NHWC_Func.apply(torch.randn(2, 8, 4, 4), m.weight, m.bias, 4, 1e-5, 0)
 
 
+def test_module_refuses_a_peer_exchange_made_for_another_channel_count():
+    from channels_last_groupnorm_b200 import dist as gd
+
+    px = object.__new__(gd.PeerExchange)  # no process group here: only the attribute the check reads
+    px.num_channels = 16
+    m = pkg.GN_NHWC(4, 8, process_group=px)
+    with pytest.raises(ValueError, match="made for 16 channels"):
+        pkg.GN_NHWC_Func.apply(torch.randn(2, 8, 4, 4), m.weight, m.bias, 4, 1e-5, 0, px)
+
+
 def test_torch_ops_are_registered_with_reference_schemas():
     fwd = torch.ops.gnb200.fwd.default._schema
     bwd = torch.ops.gnb200.bwd.default._schema
