@@ -1105,6 +1105,20 @@ def profile_target(args):
     torch.cuda.set_device(0)
     N, C, H, W, G, eps, act, dt, xs, bwd, dist_name = WORKLOADS[args.workload]
     x, ga, be, dy = make_inputs(N, C, H, W, DT[dt], 0, xs, dist_name)
+    if args.nchw:  # the channels-first entry points on NCHW-contiguous copies of the same tensors
+        from channels_last_groupnorm_b200 import _native as nt
+
+        code = ACT_CODES[act]
+        xn = x.cuda().permute(0, 3, 1, 2).contiguous().reshape(N, C, H * W)
+        dn = dy.cuda().permute(0, 3, 1, 2).contiguous().reshape(N, C, H * W)
+        gd, bd = ga.cuda(), be.cuda()
+        for i in range(args.profile):
+            y, mean, rstd = nt.fwd_nchw_raw(xn, gd, bd, G, eps, code)
+            if bwd:
+                nt.bwd_nchw_raw(dn, xn, gd, bd, mean, rstd, G, code)
+        torch.cuda.synchronize()
+        print("profiled", args.workload, "channels-first", args.profile, "calls")
+        return
     prob = DeviceProblem(args.workload, N, x, ga, be, dy, min_total_bytes=1)
     stream = torch.cuda.current_stream().cuda_stream
     for i in range(args.profile):
@@ -1154,6 +1168,7 @@ def main():
                          "on a side stream (peer-side); or an NCCL all-reduce on a side stream (nccl)")
     ap.add_argument("--no-graph", action="store_true", help="time the eager loop instead of a CUDA-graph replay")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--nchw", action="store_true", help="--profile: the channels-first entry points")
     ap.add_argument("--profile", type=int, default=0, metavar="CALLS",
                     help="profiling target: CALLS forward(+backward) calls of --workload through the C ABI, nothing else")
     args = ap.parse_args()
